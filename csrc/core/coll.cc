@@ -1,0 +1,540 @@
+// Public collective entry points, group semantics, and the launch logic that
+// turns one API call into kernel launches on the caller's stream.
+//
+// Each call takes one of four routes (the reference has the same four-way
+// split, flagcx/flagcx.cc:699-1848, but its "device" route is a call into the
+// vendor library):
+//   host     - communicator without a GPU, or FLAGCX_USE_HOST_COMM=1: TCP ring
+//              algorithms on host memory (hostcoll.cc);
+//   grouped  - between flagcxGroupStart/End: queued, then send/recv are fused
+//              into one kernel launch and collectives are issued in order;
+//   hybrid   - more than one cluster: the C2C planner (c2c/planner.cc);
+//   direct   - a kernel of collectives.cu, variant picked by the tuner.
+#include "comm.h"
+#include "hostcoll.h"
+#include "hosttypes.h"
+#include "log.h"
+#include "../kernels/launch.h"
+
+#include <algorithm>
+#include <cstring>
+#include <cuda_runtime.h>
+
+namespace fcx {
+
+flagcxResult_t c2cExecute(flagcxComm *c, const PendingOp &op, bool *handled);  // c2c/planner.cc
+
+static thread_local int tGroupDepth = 0;
+static thread_local std::vector<flagcxComm *> tGroupComms;
+int groupDepth() { return tGroupDepth; }
+
+static cudaStream_t streamOf(flagcxStream_t s) { return s ? s->base : (cudaStream_t)0; }
+
+static void count(flagcxComm *c, flagcxCommOp_t op, size_t bytes) {
+  c->counters.calls[op]++;
+  c->counters.bytes[op] += bytes;
+}
+
+// ------------------------------------------------------------------ host route
+
+flagcxResult_t hostCollective(flagcxComm *c, const PendingOp &o) {
+  const int n = c->nranks;
+  const size_t es = dtypeSize(o.dt);
+  const void *send = o.send;
+  void *recv = o.recv;
+  std::vector<char> hs, hr;
+  size_t sendBytes = 0, recvBytes = 0;
+  const size_t *t = o.tables.data();
+  switch (o.op) {
+    case flagcxCommOpAllReduce: case flagcxCommOpBroadcast: case flagcxCommOpReduce: sendBytes = recvBytes = o.count * es; break;
+    case flagcxCommOpAllGather: sendBytes = o.count * es; recvBytes = n * o.count * es; break;
+    case flagcxCommOpReduceScatter: sendBytes = n * o.count * es; recvBytes = o.count * es; break;
+    case flagcxCommOpGather: sendBytes = o.count * es; recvBytes = c->rank == o.root ? n * o.count * es : 0; break;
+    case flagcxCommOpScatter: sendBytes = c->rank == o.root ? n * o.count * es : 0; recvBytes = o.count * es; break;
+    case flagcxCommOpAlltoAll: sendBytes = recvBytes = n * o.count * es; break;
+    case flagcxCommOpAlltoAllv:
+      for (int i = 0; i < n; i++) {
+        sendBytes = std::max(sendBytes, (t[n + i] + t[i]) * es);
+        recvBytes = std::max(recvBytes, (t[3 * n + i] + t[2 * n + i]) * es);
+      }
+      break;
+    case flagcxCommOpSend: sendBytes = o.count * es; break;
+    case flagcxCommOpRecv: recvBytes = o.count * es; break;
+    default: break;
+  }
+  if (o.op == flagcxCommOpBroadcast && c->rank != o.root) sendBytes = 0;
+  if (o.op == flagcxCommOpReduce && c->rank != o.root) recvBytes = 0;
+  const bool viaCopies = c->hostFallback;
+  if (viaCopies) {
+    // device buffers: stage through host memory (whole message, synchronous)
+    FCX_CHECK(cudaToResult(cudaStreamSynchronize(o.stream), "host path"));
+    hs.resize(sendBytes);
+    hr.resize(std::max(recvBytes, (size_t)1));
+    if (sendBytes) FCX_CHECK(cudaToResult(cudaMemcpy(hs.data(), o.send, sendBytes, cudaMemcpyDeviceToHost), "host path D2H"));
+    if (o.op == flagcxCommOpAllGather || o.op == flagcxCommOpGather || o.op == flagcxCommOpAlltoAllv) {
+      // these may leave parts of recv untouched or are written in place: start from the device contents
+      if (recvBytes) FCX_CHECK(cudaToResult(cudaMemcpy(hr.data(), o.recv, recvBytes, cudaMemcpyDeviceToHost), "host path D2H"));
+    }
+    send = hs.data();
+    recv = hr.data();
+  }
+  flagcxResult_t r = flagcxSuccess;
+  switch (o.op) {
+    case flagcxCommOpAllReduce: r = hostAllReduce(c->bs, send, recv, o.count, o.dt, o.red); break;
+    case flagcxCommOpReduceScatter: r = hostReduceScatter(c->bs, send, recv, o.count, o.dt, o.red); break;
+    case flagcxCommOpAllGather: r = hostAllGather(c->bs, send, recv, o.count, o.dt); break;
+    case flagcxCommOpBroadcast: r = hostBroadcast(c->bs, send, recv, o.count, o.dt, o.root); break;
+    case flagcxCommOpReduce: r = hostReduce(c->bs, send, recv, o.count, o.dt, o.red, o.root); break;
+    case flagcxCommOpGather: r = hostGather(c->bs, send, recv, o.count, o.dt, o.root); break;
+    case flagcxCommOpScatter: r = hostScatter(c->bs, send, recv, o.count, o.dt, o.root); break;
+    case flagcxCommOpAlltoAll: r = hostAlltoAll(c->bs, send, recv, o.count, o.dt); break;
+    case flagcxCommOpAlltoAllv: r = hostAlltoAllv(c->bs, send, t, t + n, recv, t + 2 * n, t + 3 * n, o.dt); break;
+    case flagcxCommOpSend: r = hostSend(c->bs, send, o.count, o.dt, o.root); break;
+    case flagcxCommOpRecv: r = hostRecv(c->bs, recv, o.count, o.dt, o.root); break;
+    default: r = flagcxInvalidArgument;
+  }
+  FCX_CHECK(r);
+  if (viaCopies && recvBytes) FCX_CHECK(cudaToResult(cudaMemcpy(o.recv, hr.data(), recvBytes, cudaMemcpyHostToDevice), "host path H2D"));
+  return flagcxSuccess;
+}
+
+// Host-route group: pair the i-th send with the i-th receive so that two
+// ranks exchanging large messages progress both directions at once.
+static flagcxResult_t hostGroup(flagcxComm *c, std::vector<PendingOp> &ops) {
+  std::vector<PendingOp *> sends, recvs;
+  for (auto &o : ops) {
+    if (o.op == flagcxCommOpSend) sends.push_back(&o);
+    else if (o.op == flagcxCommOpRecv) recvs.push_back(&o);
+  }
+  if (c->hostFallback && (!sends.empty() || !recvs.empty())) {
+    // keep it simple on the copy route: receives run on a helper thread
+    std::vector<flagcxResult_t> rr(recvs.size(), flagcxSuccess);
+    std::thread th([&] { for (size_t i = 0; i < recvs.size(); i++) rr[i] = hostCollective(c, *recvs[i]); });
+    flagcxResult_t r = flagcxSuccess;
+    for (auto *s : sends) { flagcxResult_t x = hostCollective(c, *s); if (x != flagcxSuccess) r = x; }
+    th.join();
+    for (auto x : rr) if (x != flagcxSuccess) r = x;
+    FCX_CHECK(r);
+  } else {
+    size_t np = std::min(sends.size(), recvs.size());
+    for (size_t i = 0; i < np; i++) {
+      PendingOp *s = sends[i], *r = recvs[i];
+      FCX_CHECK(c->bs.sendrecv(s->root, 0x170000, s->send, s->count * dtypeSize(s->dt), r->root, 0x170000, r->recv,
+                               r->count * dtypeSize(r->dt)));
+    }
+    for (size_t i = np; i < sends.size(); i++) FCX_CHECK(hostCollective(c, *sends[i]));
+    for (size_t i = np; i < recvs.size(); i++) FCX_CHECK(hostCollective(c, *recvs[i]));
+  }
+  for (auto &o : ops)
+    if (o.op != flagcxCommOpSend && o.op != flagcxCommOpRecv) FCX_CHECK(hostCollective(c, o));
+  return flagcxSuccess;
+}
+
+// ------------------------------------------------------------------ direct route
+
+static uint64_t heapOffOf(flagcxComm *c, const void *p, size_t bytes) {
+  const char *base = c->heap.base[c->rank];
+  if (p && (const char *)p >= base && (const char *)p + bytes <= base + c->heap.bytes) return (const char *)p - base;
+  return ~0ull;
+}
+
+static flagcxResult_t launchOne(flagcxComm *c, FcxCollArgs &a, const Plan &plan, cudaStream_t st, bool timed) {
+  a.kind = plan.kind;
+  a.seq = ++c->seq;
+  int nctas = std::max(1, std::min(plan.nctas, FCX_MAX_CTAS));
+  if (timed) c->tuner->beginTiming(st);
+  cudaError_t e = fcxLaunchColl(&c->dev, &a, nctas, st);
+  if (timed) c->tuner->endTiming(st);
+  c->counters.launches++;
+  if (plan.kind >= 0 && plan.kind < 16) c->counters.kindLaunches[plan.kind]++;
+  return cudaToResult(e, "collective kernel launch");
+}
+
+flagcxResult_t launchCollective(flagcxComm *c, const PendingOp &o) {
+  const int n = c->nranks;
+  const size_t es = dtypeSize(o.dt), eso = dtypeSize(o.outDt);
+  const size_t stage = c->dev.stageBytes;
+  FcxCollArgs a;
+  memset(&a, 0, sizeof a);
+  a.dtype = o.dt;
+  a.outDtype = o.outDt;
+  a.redop = o.red;
+  a.root = o.root;
+  a.elemSize = (int)es;
+  a.scale = o.scale;
+  a.sendHeapOff = a.recvHeapOff = ~0ull;
+  a.useMc = c->dev.mcHeap != nullptr;
+  const bool cast = o.outDt != o.dt || o.scale != 1.0f;
+  const char *send = (const char *)o.send;
+  char *recv = (char *)o.recv;
+
+  if (o.op == flagcxCommNoOp) {  // barrier
+    a.elemSize = 1;
+    Plan p{FCX_K_BARRIER, 1};
+    return launchOne(c, a, p, o.stream, false);
+  }
+
+  if (o.op == flagcxCommOpAlltoAllv) {
+    const size_t *t = o.tables.data();
+    size_t maxPair = 0;
+    for (int i = 0; i < n; i++) {
+      a.scounts[i] = t[i];
+      a.sdispls[i] = t[n + i];
+      a.rcounts[i] = t[2 * n + i];
+      a.rdispls[i] = t[3 * n + i];
+      maxPair = std::max(maxPair, std::max(t[i], t[2 * n + i]) * es);
+    }
+    a.send = send;
+    a.recv = recv;
+    // like the reference (flagcx/flagcx.cc:1613-1616) the variable all-to-all is not searched online
+    Plan p = c->tuner->peek(o.op, std::max<size_t>(maxPair, 16), o.dt, o.red, false);
+    return launchOne(c, a, p, o.stream, false);
+  }
+
+  // Elements one launch can take, limited by the staging area.
+  size_t cap;
+  switch (o.op) {
+    case flagcxCommOpAllReduce:
+    case flagcxCommOpReduce: cap = (stage - 256 * (size_t)n) / (es + eso); break;
+    case flagcxCommOpBroadcast:
+    case flagcxCommOpScatter: cap = (stage - 64) / es; break;
+    default: cap = (stage / n - 64) / es; break;  // per-rank piece
+  }
+  cap &= ~(size_t)63;
+  size_t done = 0;
+  do {
+    size_t cnt = std::min(cap, o.count - done);
+    size_t bytes = cnt * es;
+    bool timed = false;
+    Plan p = c->tuner->choose(o.op, std::max<size_t>(bytes, 1), o.dt, o.red, cast, &timed);
+    a.count = cnt;
+    switch (o.op) {
+      case flagcxCommOpAllReduce:
+      case flagcxCommOpReduce:
+      case flagcxCommOpBroadcast:
+        a.send = send + done * es;
+        a.recv = recv ? recv + done * eso : nullptr;
+        break;
+      case flagcxCommOpAllGather:
+      case flagcxCommOpGather:
+        a.send = send + done * es;
+        a.recv = recv ? recv + done * es : nullptr;
+        a.recvStride = o.count;
+        break;
+      case flagcxCommOpReduceScatter:
+      case flagcxCommOpScatter:
+        a.send = send ? send + done * es : nullptr;
+        a.recv = recv + done * es;
+        a.sendStride = o.count;
+        break;
+      case flagcxCommOpAlltoAll:
+        a.send = send + done * es;
+        a.recv = recv + done * es;
+        a.sendStride = a.recvStride = o.count;
+        break;
+      default: return flagcxInvalidArgument;
+    }
+    FCX_CHECK(launchOne(c, a, p, o.stream, timed));
+    done += cnt;
+  } while (done < o.count);
+  return flagcxSuccess;
+}
+
+// One fused launch for a batch of sends and receives.
+flagcxResult_t launchP2pBatch(flagcxComm *c, const std::vector<PendingOp> &ops) {
+  if (ops.empty()) return flagcxSuccess;
+  cudaStream_t st = ops[0].stream;
+  // other streams join the first one's timeline and wait for the result
+  std::vector<cudaStream_t> others;
+  for (auto &o : ops)
+    if (o.stream != st && std::find(others.begin(), others.end(), o.stream) == others.end()) others.push_back(o.stream);
+  cudaEvent_t ev = nullptr;
+  if (!others.empty()) {
+    cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+    for (auto s : others) { cudaEventRecord(ev, s); cudaStreamWaitEvent(st, ev, 0); }
+  }
+  // match self-sends with self-receives in order
+  std::vector<const PendingOp *> selfS, selfR;
+  for (auto &o : ops)
+    if (o.root == c->rank) (o.op == flagcxCommOpSend ? selfS : selfR).push_back(&o);
+  if (selfS.size() != selfR.size()) {
+    FCX_WARN("a group holds %zu sends to self but %zu receives from self", selfS.size(), selfR.size());
+    return flagcxInvalidUsage;
+  }
+  std::vector<FcxP2pOp> dops;
+  size_t maxBytes = 0;
+  for (size_t i = 0; i < selfS.size(); i++) {
+    size_t sb = selfS[i]->count * dtypeSize(selfS[i]->dt), rb = selfR[i]->count * dtypeSize(selfR[i]->dt);
+    if (sb != rb) { FCX_WARN("self send/recv %zu differ in size (%zu vs %zu bytes)", i, sb, rb); return flagcxInvalidArgument; }
+    FcxP2pOp d{};
+    d.isRecv = 2;
+    d.peer = c->rank;
+    d.buf = selfR[i]->recv;
+    d.bytes = rb;
+    d.heapOff = (uint64_t)(uintptr_t)selfS[i]->send;
+    dops.push_back(d);
+    maxBytes = std::max(maxBytes, rb);
+  }
+  const size_t chunk = c->dev.p2pChunkBytes;
+  for (auto &o : ops) {
+    if (o.root == c->rank) continue;
+    FcxP2pOp d{};
+    size_t bytes = o.count * dtypeSize(o.dt);
+    uint64_t nch = bytes ? (bytes + chunk - 1) / chunk : 1;
+    d.peer = o.root;
+    d.bytes = bytes;
+    if (o.op == flagcxCommOpSend) {
+      d.isRecv = 0;
+      d.buf = (void *)o.send;
+      d.firstChunk = c->sendChunks[o.root];
+      c->sendChunks[o.root] += nch;
+      d.heapOff = bytes ? heapOffOf(c, o.send, bytes) : ~0ull;
+    } else {
+      d.isRecv = 1;
+      d.buf = o.recv;
+      d.firstChunk = c->recvChunks[o.root];
+      c->recvChunks[o.root] += nch;
+      d.heapOff = ~0ull;
+    }
+    dops.push_back(d);
+    maxBytes = std::max(maxBytes, bytes);
+  }
+  int per = maxBytes <= (64u << 10) ? 1 : maxBytes <= (1u << 20) ? 4 : 8;
+  for (size_t i = 0; i < dops.size(); i += FCX_MAX_GROUP_OPS) {
+    FcxP2pArgs g;
+    memset(&g, 0, sizeof g);
+    g.nops = (int)std::min<size_t>(FCX_MAX_GROUP_OPS, dops.size() - i);
+    g.ctasPerOp = std::max(1, std::min(per, FCX_MAX_CTAS / g.nops));
+    memcpy(g.ops, &dops[i], g.nops * sizeof(FcxP2pOp));
+    FCX_CHECK(cudaToResult(fcxLaunchP2p(&c->dev, &g, st), "send/recv kernel launch"));
+    c->counters.launches++;
+  }
+  if (ev) {
+    cudaEventRecord(ev, st);
+    for (auto s : others) cudaStreamWaitEvent(s, ev, 0);
+    cudaEventDestroy(ev);
+  }
+  return flagcxSuccess;
+}
+
+// ------------------------------------------------------------------ dispatch
+
+static flagcxResult_t validate(flagcxComm_t c, const PendingOp &o) {
+  if (!validComm(c)) return flagcxInvalidArgument;
+  if (!dtypeSize(o.dt) || !dtypeSize(o.outDt)) { FCX_WARN("unknown data type %d", (int)o.dt); return flagcxInvalidArgument; }
+  const bool reduces = o.op == flagcxCommOpAllReduce || o.op == flagcxCommOpReduce || o.op == flagcxCommOpReduceScatter;
+  if (reduces && (o.red < flagcxSum || o.red > flagcxAvg)) { FCX_WARN("unknown reduction %d", (int)o.red); return flagcxInvalidArgument; }
+  const bool rooted = o.op == flagcxCommOpBroadcast || o.op == flagcxCommOpReduce || o.op == flagcxCommOpGather ||
+                      o.op == flagcxCommOpScatter || o.op == flagcxCommOpSend || o.op == flagcxCommOpRecv;
+  if (rooted && (o.root < 0 || o.root >= c->nranks)) { FCX_WARN("rank %d out of range", o.root); return flagcxInvalidArgument; }
+  if (o.count > 0 && o.op != flagcxCommNoOp) {
+    bool needSend = o.op != flagcxCommOpRecv && !(o.op == flagcxCommOpScatter && c->rank != o.root) &&
+                    !(o.op == flagcxCommOpBroadcast && c->rank != o.root);
+    bool needRecv = o.op != flagcxCommOpSend && !(o.op == flagcxCommOpGather && c->rank != o.root) &&
+                    !(o.op == flagcxCommOpReduce && c->rank != o.root);
+    if ((needSend && !o.send) || (needRecv && !o.recv)) { FCX_WARN("null buffer"); return flagcxInvalidArgument; }
+  }
+  return flagcxSuccess;
+}
+
+static flagcxResult_t submit(flagcxComm_t c, PendingOp &&o) {
+  FCX_CHECK(validate(c, o));
+  size_t bytes = o.count * dtypeSize(o.dt);
+  if (o.op != flagcxCommNoOp) count(c, o.op, bytes);
+  FCX_TRACE(SUB_CALL, "op %d count %zu dtype %d red %d root %d", (int)o.op, o.count, (int)o.dt, (int)o.red, o.root);
+  if (tGroupDepth > 0) {
+    if (std::find(tGroupComms.begin(), tGroupComms.end(), c) == tGroupComms.end()) tGroupComms.push_back(c);
+    c->pending.push_back(std::move(o));
+    return flagcxSuccess;
+  }
+  if (c->hostOnly || c->hostFallback) return hostCollective(c, o);
+  if (o.op == flagcxCommOpSend || o.op == flagcxCommOpRecv) return launchP2pBatch(c, {o});
+  if (o.count == 0 && o.op != flagcxCommNoOp && o.op != flagcxCommOpAlltoAllv) return flagcxSuccess;
+  if (c->nranks == 1) {
+    // nothing to exchange: a device copy when the buffers differ
+    size_t nb = o.count * dtypeSize(o.dt);
+    if (o.op == flagcxCommOpAlltoAllv) {
+      const size_t *t = o.tables.data();
+      nb = t[0] * dtypeSize(o.dt);
+      const char *s = (const char *)o.send + t[1] * dtypeSize(o.dt);
+      char *d = (char *)o.recv + t[3] * dtypeSize(o.dt);
+      if (s != d && nb) return cudaToResult(cudaMemcpyAsync(d, s, nb, cudaMemcpyDeviceToDevice, o.stream), "single-rank copy");
+      return flagcxSuccess;
+    }
+    if (o.op != flagcxCommNoOp && (o.outDt != o.dt || o.scale != 1.0f || o.red == flagcxAvg)) return launchCollective(c, o);
+    if (o.op != flagcxCommNoOp && o.send != o.recv && nb)
+      return cudaToResult(cudaMemcpyAsync(o.recv, o.send, nb, cudaMemcpyDeviceToDevice, o.stream), "single-rank copy");
+    return flagcxSuccess;
+  }
+  if (c->nclusters > 1 && o.op != flagcxCommNoOp) {
+    bool handled = false;
+    FCX_CHECK(c2cExecute(c, o, &handled));
+    if (handled) return flagcxSuccess;
+  }
+  return launchCollective(c, o);
+}
+
+static PendingOp mk(flagcxCommOp_t op, const void *s, void *r, size_t cnt, flagcxDataType_t dt, flagcxRedOp_t red, int root,
+                    flagcxStream_t st) {
+  PendingOp o;
+  o.op = op;
+  o.send = s;
+  o.recv = r;
+  o.count = cnt;
+  o.dt = o.outDt = dt;
+  o.red = red;
+  o.root = root;
+  o.scale = 1.0f;
+  o.stream = streamOf(st);
+  return o;
+}
+
+}  // namespace fcx
+
+using namespace fcx;
+
+extern "C" {
+
+flagcxResult_t flagcxBarrier(flagcxComm_t comm, flagcxStream_t stream) {
+  if (!validComm(comm)) return flagcxInvalidArgument;
+  if (comm->hostOnly || comm->hostFallback) {
+    if (comm->hostFallback) cudaStreamSynchronize(streamOf(stream));
+    return comm->bs.barrier();
+  }
+  PendingOp o = mk(flagcxCommNoOp, nullptr, nullptr, 0, flagcxInt8, flagcxSum, 0, stream);
+  if (comm->nranks > 1) FCX_CHECK(launchCollective(comm, o));
+  // the reference's barrier returns only after the stream has drained (flagcx/flagcx.cc:699-710)
+  return cudaToResult(cudaStreamSynchronize(streamOf(stream)), "barrier");
+}
+
+flagcxResult_t flagcxReduce(const void *sendbuff, void *recvbuff, size_t count, flagcxDataType_t datatype, flagcxRedOp_t op, int root,
+                            flagcxComm_t comm, flagcxStream_t stream) {
+  return submit(comm, mk(flagcxCommOpReduce, sendbuff, recvbuff, count, datatype, op, root, stream));
+}
+flagcxResult_t flagcxGather(const void *sendbuff, void *recvbuff, size_t count, flagcxDataType_t datatype, int root,
+                            flagcxComm_t comm, flagcxStream_t stream) {
+  return submit(comm, mk(flagcxCommOpGather, sendbuff, recvbuff, count, datatype, flagcxSum, root, stream));
+}
+flagcxResult_t flagcxScatter(const void *sendbuff, void *recvbuff, size_t count, flagcxDataType_t datatype, int root,
+                             flagcxComm_t comm, flagcxStream_t stream) {
+  return submit(comm, mk(flagcxCommOpScatter, sendbuff, recvbuff, count, datatype, flagcxSum, root, stream));
+}
+flagcxResult_t flagcxBroadcast(const void *sendbuff, void *recvbuff, size_t count, flagcxDataType_t datatype, int root,
+                               flagcxComm_t comm, flagcxStream_t stream) {
+  return submit(comm, mk(flagcxCommOpBroadcast, sendbuff, recvbuff, count, datatype, flagcxSum, root, stream));
+}
+flagcxResult_t flagcxAllReduce(const void *sendbuff, void *recvbuff, size_t count, flagcxDataType_t datatype, flagcxRedOp_t op,
+                               flagcxComm_t comm, flagcxStream_t stream) {
+  return submit(comm, mk(flagcxCommOpAllReduce, sendbuff, recvbuff, count, datatype, op, 0, stream));
+}
+flagcxResult_t flagcxAllReduceCast(const void *sendbuff, void *recvbuff, size_t count, flagcxDataType_t inType,
+                                   flagcxDataType_t outType, float scale, flagcxRedOp_t op, flagcxComm_t comm,
+                                   flagcxStream_t stream) {
+  PendingOp o = mk(flagcxCommOpAllReduce, sendbuff, recvbuff, count, inType, op, 0, stream);
+  o.outDt = outType;
+  o.scale = scale;
+  if (validComm(comm) && (comm->hostOnly || comm->hostFallback) && (outType != inType || scale != 1.0f)) return flagcxNotSupported;
+  return submit(comm, std::move(o));
+}
+flagcxResult_t flagcxReduceScatter(const void *sendbuff, void *recvbuff, size_t recvcount, flagcxDataType_t datatype, flagcxRedOp_t op,
+                                   flagcxComm_t comm, flagcxStream_t stream) {
+  return submit(comm, mk(flagcxCommOpReduceScatter, sendbuff, recvbuff, recvcount, datatype, op, 0, stream));
+}
+flagcxResult_t flagcxAllGather(const void *sendbuff, void *recvbuff, size_t sendcount, flagcxDataType_t datatype, flagcxComm_t comm,
+                               flagcxStream_t stream) {
+  return submit(comm, mk(flagcxCommOpAllGather, sendbuff, recvbuff, sendcount, datatype, flagcxSum, 0, stream));
+}
+flagcxResult_t flagcxAlltoAll(const void *sendbuff, void *recvbuff, size_t count, flagcxDataType_t datatype, flagcxComm_t comm,
+                              flagcxStream_t stream) {
+  return submit(comm, mk(flagcxCommOpAlltoAll, sendbuff, recvbuff, count, datatype, flagcxSum, 0, stream));
+}
+flagcxResult_t flagcxAlltoAllv(const void *sendbuff, size_t *sendcounts, size_t *sdispls, void *recvbuff, size_t *recvcounts,
+                               size_t *rdispls, flagcxDataType_t datatype, flagcxComm_t comm, flagcxStream_t stream) {
+  if (!validComm(comm) || !sendcounts || !sdispls || !recvcounts || !rdispls) return flagcxInvalidArgument;
+  PendingOp o = mk(flagcxCommOpAlltoAllv, sendbuff, recvbuff, 1, datatype, flagcxSum, 0, stream);
+  const int n = comm->nranks;
+  o.tables.resize(4 * n);
+  size_t total = 0;
+  for (int i = 0; i < n; i++) {
+    o.tables[i] = sendcounts[i];
+    o.tables[n + i] = sdispls[i];
+    o.tables[2 * n + i] = recvcounts[i];
+    o.tables[3 * n + i] = rdispls[i];
+    total += sendcounts[i];
+  }
+  o.count = total;
+  return submit(comm, std::move(o));
+}
+flagcxResult_t flagcxSend(const void *sendbuff, size_t count, flagcxDataType_t datatype, int peer, flagcxComm_t comm,
+                          flagcxStream_t stream) {
+  return submit(comm, mk(flagcxCommOpSend, sendbuff, nullptr, count, datatype, flagcxSum, peer, stream));
+}
+flagcxResult_t flagcxRecv(void *recvbuff, size_t count, flagcxDataType_t datatype, int peer, flagcxComm_t comm,
+                          flagcxStream_t stream) {
+  return submit(comm, mk(flagcxCommOpRecv, nullptr, recvbuff, count, datatype, flagcxSum, peer, stream));
+}
+
+flagcxResult_t flagcxGroupStart(flagcxComm_t) {
+  tGroupDepth++;
+  return flagcxSuccess;
+}
+
+flagcxResult_t flagcxGroupEnd(flagcxComm_t) {
+  if (tGroupDepth <= 0) { FCX_WARN("flagcxGroupEnd without flagcxGroupStart"); return flagcxInvalidUsage; }
+  if (--tGroupDepth > 0) return flagcxSuccess;
+  std::vector<flagcxComm *> comms;
+  comms.swap(tGroupComms);
+  flagcxResult_t res = flagcxSuccess;
+  for (flagcxComm *c : comms) {
+    std::vector<PendingOp> ops;
+    ops.swap(c->pending);
+    if (res != flagcxSuccess) continue;
+    if (c->hostOnly || c->hostFallback) { res = hostGroup(c, ops); continue; }
+    std::vector<PendingOp> p2p;
+    for (auto &o : ops)
+      if (o.op == flagcxCommOpSend || o.op == flagcxCommOpRecv) p2p.push_back(o);
+    if (!p2p.empty()) res = launchP2pBatch(c, p2p);
+    for (auto &o : ops) {
+      if (res != flagcxSuccess) break;
+      if (o.op == flagcxCommOpSend || o.op == flagcxCommOpRecv) continue;
+      if (o.count == 0 && o.op != flagcxCommOpAlltoAllv) continue;
+      if (c->nranks == 1 || c->nclusters > 1) {
+        // re-enter the ungrouped path for the special cases
+        PendingOp copy = o;
+        res = submit(c, std::move(copy));
+        c->counters.calls[o.op]--;
+        c->counters.bytes[o.op] -= o.count * dtypeSize(o.dt);
+      } else {
+        res = launchCollective(c, o);
+      }
+    }
+  }
+  return res;
+}
+
+flagcxResult_t flagcxTunerPin(flagcxComm_t comm, const char *kind, int nctas) {
+  if (!validComm(comm)) return flagcxInvalidArgument;
+  if (!kind) { comm->tuner->pin(nullptr); return flagcxSuccess; }
+  int k = kindFromName(kind);
+  if (k < 0) return flagcxInvalidArgument;
+  Plan p{k, std::max(1, nctas)};
+  comm->tuner->pin(&p);
+  return flagcxSuccess;
+}
+
+flagcxResult_t flagcxTunerQuery(flagcxComm_t comm, flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red,
+                                char *kindOut, size_t kindOutBytes, int *nctas, double *estimate) {
+  if (!validComm(comm)) return flagcxInvalidArgument;
+  Plan p = comm->tuner->peek(op, bytes, dt, red, false);
+  if (kindOut && kindOutBytes) snprintf(kindOut, kindOutBytes, "%s", kindName(p.kind));
+  if (nctas) *nctas = p.nctas;
+  if (estimate) *estimate = comm->tuner->estimate(p, op, bytes, dt);
+  return flagcxSuccess;
+}
+
+flagcxResult_t flagcxCommWaitTest(flagcxComm_t comm, flagcxStream_t stream) {
+  if (!validComm(comm) || comm->hostOnly || !comm->heap.bytes) return flagcxInvalidArgument;
+  return cudaToResult(fcxLaunchWaitTest(&comm->dev, ~0ull, streamOf(stream)), "wait test launch");
+}
+
+}  // extern "C"

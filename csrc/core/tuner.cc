@@ -1,0 +1,297 @@
+#include "tuner.h"
+#include "hosttypes.h"
+#include "log.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <sstream>
+
+namespace fcx {
+
+static const char *kKindNames[FCX_K_NUM] = {"barrier", "ar_ll", "ar_oneshot", "ar_twoshot", "ar_nvls", "rs", "rs_nvls", "ag",
+                                            "ag_nvls", "bcast", "reduce", "gather", "scatter", "a2a", "a2av"};
+
+const char *kindName(int kind) { return kind >= 0 && kind < FCX_K_NUM ? kKindNames[kind] : "?"; }
+
+int kindFromName(const std::string &s) {
+  for (int i = 0; i < FCX_K_NUM; i++)
+    if (s == kKindNames[i]) return i;
+  return -1;
+}
+
+// ------------------------------------------------------------------ cost model
+
+// Rates in bytes per microsecond.  Link and HBM figures are the measured
+// ones for this class of machine (peer copy ~770 GB/s per direction, device
+// copy ~6.5 TB/s read+write); per-CTA figures bound what few CTAs can move.
+namespace {
+constexpr double kLaunchUs = 2.2, kBarrierUs = 1.8, kLLUs = 1.6;
+constexpr double kLinkRate = 700e3, kCtaPushRate = 26e3, kCtaMmRate = 45e3;
+constexpr double kHbmRate = 5500e3, kCtaLocalRate = 90e3;
+
+double pushUs(double bytes, int nctas) { return bytes / std::min(kLinkRate, nctas * kCtaPushRate); }
+double mmUs(double bytes, int nctas) { return bytes / std::min(kLinkRate, nctas * kCtaMmRate); }
+double localUs(double bytes, int nctas) { return bytes / std::min(kHbmRate, nctas * kCtaLocalRate); }
+}  // namespace
+
+double estimateUs(const Plan &p, flagcxCommOp_t, size_t bytesIn, int, const TunerCaps &caps) {
+  const double b = (double)bytesIn, n = caps.nranks;
+  const int c = p.nctas;
+  switch (p.kind) {
+    case FCX_K_BARRIER: return kLaunchUs + kBarrierUs;
+    case FCX_K_AR_LL: return kLaunchUs + kLLUs + pushUs(2 * (n - 1) * b, c) + localUs(2 * n * b, c);
+    case FCX_K_AR_ONESHOT: return kLaunchUs + kBarrierUs + pushUs((n - 1) * b, c) + localUs((n + 1) * b, c);
+    case FCX_K_AR_TWOSHOT: return kLaunchUs + 2 * kBarrierUs + pushUs(2 * (n - 1) / n * b, c) + localUs(4 * b, c);
+    case FCX_K_AR_NVLS: return kLaunchUs + 2 * kBarrierUs + mmUs(b, c) + localUs(4 * b, c);
+    case FCX_K_REDUCE: return kLaunchUs + 2 * kBarrierUs + pushUs(2 * (n - 1) / n * b, c) + localUs(3 * b, c);
+    // below, b is the per-rank piece
+    case FCX_K_RS: return kLaunchUs + kBarrierUs + pushUs((n - 1) * b, c) + localUs((n + 1) * b, c);
+    case FCX_K_RS_NVLS: return kLaunchUs + kBarrierUs + mmUs(n * b, c) + localUs(2 * n * b, c);
+    case FCX_K_AG: return kLaunchUs + kBarrierUs + pushUs((n - 1) * b, c) + localUs(2 * n * b, c);
+    case FCX_K_AG_NVLS: return kLaunchUs + kBarrierUs + mmUs((n - 1) * b, c) + localUs(2 * n * b, c);
+    case FCX_K_BCAST: return kLaunchUs + kBarrierUs + (caps.multicast ? mmUs(b, c) : pushUs((n - 1) * b, c)) + localUs(2 * b, c);
+    case FCX_K_GATHER:
+    case FCX_K_SCATTER: return kLaunchUs + kBarrierUs + pushUs((n - 1) * b, c) + localUs(2 * b, c);
+    case FCX_K_A2A:
+    case FCX_K_A2AV: return kLaunchUs + 2 * kBarrierUs + pushUs((n - 1) * b, c) + localUs(2 * n * b, c);
+    default: return 1e9;
+  }
+}
+
+// ------------------------------------------------------------------ tuner
+
+Tuner::Tuner(Bootstrap *bs, const TunerCaps &caps) : bs_(bs), caps_(caps) {
+  search_ = envInt("USE_TUNER", 0) != 0;
+  nLoops_ = (int)envInt("TUNER_SEARCH_NLOOPS", 5);
+  std::string tag = envStr("USE_COMM_TAG", "");
+  if (!tag.empty()) {
+    size_t c = tag.find(':');
+    int k = kindFromName(tag.substr(0, c));
+    if (k >= 0) {
+      pinned_ = true;
+      pin_.kind = k;
+      pin_.nctas = c == std::string::npos ? 16 : std::max(1, atoi(tag.c_str() + c + 1));
+    } else {
+      FCX_WARN("FLAGCX_USE_COMM_TAG='%s' names no kernel variant", tag.c_str());
+    }
+  }
+  std::string cache = envStr("TUNER_CACHE", "");
+  if (!cache.empty()) load(cache);
+}
+
+Tuner::~Tuner() {
+  if (ev0_) cudaEventDestroy(ev0_);
+  if (ev1_) cudaEventDestroy(ev1_);
+}
+
+int Tuner::bucket(size_t bytes) {
+  int l = 0;
+  while (((size_t)1 << l) < bytes && l < 62) l++;
+  return l;
+}
+
+static void addCtas(std::vector<Plan> &out, int kind, std::initializer_list<int> cs, size_t units, int maxCtas) {
+  int cap = (int)std::min<size_t>((units + 511) / 512, (size_t)maxCtas);
+  cap = std::max(cap, 1);
+  int last = -1;
+  for (int c : cs) {
+    int cc = std::min(c, cap);
+    if (cc != last) out.push_back({kind, cc});
+    last = cc;
+  }
+}
+
+std::vector<Plan> Tuner::candidates(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red, bool cast) const {
+  std::vector<Plan> out;
+  const int n = caps_.nranks;
+  const size_t units = (bytes + 15) / 16;
+  const int mx = caps_.maxCtas;
+  const bool mmType = dt == flagcxFloat32 || dt == flagcxBfloat16 || dt == flagcxFloat16;
+  const bool mmOp = dt == flagcxFloat32 ? (red == flagcxSum || red == flagcxAvg) : (red != flagcxProd);
+  const bool nvls = caps_.multicast && mmType && mmOp && !cast && n > 1;
+  switch (op) {
+    case flagcxCommOpAllReduce:
+      if (!cast && bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_AR_LL, {1, 2, 4}, units, mx);
+      if ((bytes + 64) * n <= caps_.stageBytes && bytes <= (8u << 20)) addCtas(out, FCX_K_AR_ONESHOT, {2, 8, 16, 32}, units, mx);
+      if (bytes > 2048 || out.empty()) addCtas(out, FCX_K_AR_TWOSHOT, {8, 16, 32, 64}, units / n + 1, mx);
+      if (nvls && bytes >= 4096) addCtas(out, FCX_K_AR_NVLS, {4, 8, 16, 32}, units / n + 1, mx);
+      break;
+    case flagcxCommOpReduceScatter:
+      addCtas(out, FCX_K_RS, {2, 8, 16, 32, 64}, units, mx);
+      if (nvls && bytes >= 4096) addCtas(out, FCX_K_RS_NVLS, {4, 8, 16, 32}, units, mx);
+      break;
+    case flagcxCommOpAllGather:
+      addCtas(out, FCX_K_AG, {2, 8, 16, 32, 64}, units, mx);
+      if (caps_.multicast && n > 1 && bytes >= 4096) addCtas(out, FCX_K_AG_NVLS, {4, 8, 16, 32}, units, mx);
+      break;
+    case flagcxCommOpReduce: addCtas(out, FCX_K_REDUCE, {2, 8, 16, 32, 64}, units / n + 1, mx); break;
+    case flagcxCommOpBroadcast: addCtas(out, FCX_K_BCAST, {1, 4, 8, 16, 32}, units, mx); break;
+    case flagcxCommOpGather: addCtas(out, FCX_K_GATHER, {1, 4, 16, 32}, units, mx); break;
+    case flagcxCommOpScatter: addCtas(out, FCX_K_SCATTER, {1, 4, 16, 32}, units, mx); break;
+    case flagcxCommOpAlltoAll: addCtas(out, FCX_K_A2A, {2, 8, 16, 32, 64}, units, mx); break;
+    case flagcxCommOpAlltoAllv: addCtas(out, FCX_K_A2AV, {2, 8, 16, 32, 64}, units, mx); break;
+    default: out.push_back({FCX_K_BARRIER, 1}); break;
+  }
+  return out;
+}
+
+void Tuner::decide(const Key &k, Search &s) {
+  // Average every candidate's mean time over the ranks, then take the minimum.
+  const int nc = (int)s.cands.size(), n = bs_ ? bs_->nranks() : 1;
+  std::vector<double> all((size_t)n * nc, 0.0);
+  int me = bs_ ? bs_->rank() : 0;
+  for (int i = 0; i < nc; i++) all[(size_t)me * nc + i] = s.nSamples[i] ? s.sumUs[i] / s.nSamples[i] : 1e12;
+  if (bs_ && n > 1) bs_->allGather(all.data(), nc * sizeof(double));
+  std::vector<double> mean(nc, 0.0);
+  for (int r = 0; r < n; r++)
+    for (int i = 0; i < nc; i++) mean[i] += all[(size_t)r * nc + i] / n;
+  int bestI = 0;  // candidate 0 is the prior's pick (candidates are sorted by the cost model)
+  for (int i = 1; i < nc; i++)
+    if (mean[i] < mean[bestI] * 0.95) bestI = i;
+  best_[k] = s.cands[bestI];
+  bestUs_[k] = mean[bestI];
+  s.decided = true;
+  FCX_INFO(SUB_TUNING, "tuner: op %d, <=2^%d bytes -> %s with %d CTAs (%.2f us)", k.op, k.log2b, kindName(s.cands[bestI].kind),
+           s.cands[bestI].nctas, mean[bestI]);
+}
+
+Plan Tuner::choose(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red, bool cast, bool *timed) {
+  if (timed) *timed = false;
+  // Close the timing of the previous searched call.
+  if (cur_) {
+    cudaEventSynchronize(ev1_);
+    float ms = 0;
+    if (cudaEventElapsedTime(&ms, ev0_, ev1_) == cudaSuccess) {
+      cur_->sumUs[curIdx_] += ms * 1e3;
+      cur_->nSamples[curIdx_]++;
+    }
+    cudaGetLastError();
+    Search *s = cur_;
+    cur_ = nullptr;
+    if (!s->decided && s->calls >= (long)nLoops_ * (long)s->cands.size()) decide(curKey_, *s);
+  }
+  std::vector<Plan> cands = candidates(op, bytes, dt, red, cast);
+  auto legal = [&](const Plan &p) {
+    for (auto &c : cands)
+      if (c.kind == p.kind) return true;
+    return false;
+  };
+  if (pinned_ && legal(pin_)) return pin_;
+  Key k{(int)op, bucket(bytes)};
+  auto it = best_.find(k);
+  if (it != best_.end() && legal(it->second)) return it->second;
+  // order by the prior
+  std::sort(cands.begin(), cands.end(), [&](const Plan &a, const Plan &b) {
+    return estimateUs(a, op, bytes, (int)dtypeSize(dt), caps_) < estimateUs(b, op, bytes, (int)dtypeSize(dt), caps_);
+  });
+  if (!search_ || cands.size() < 2) return cands[0];
+  Search &s = searches_[k];
+  if (s.cands.empty()) {
+    s.cands = cands;
+    s.sumUs.assign(cands.size(), 0.0);
+    s.nSamples.assign(cands.size(), 0);
+  }
+  if (s.decided) return best_[k];
+  int idx = (int)(s.calls % (long)s.cands.size());
+  s.calls++;
+  cur_ = &s;
+  curIdx_ = idx;
+  curKey_ = k;
+  if (timed) *timed = true;
+  return s.cands[idx];
+}
+
+Plan Tuner::peek(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red, bool cast) const {
+  std::vector<Plan> cands = candidates(op, bytes, dt, red, cast);
+  auto legal = [&](const Plan &p) {
+    for (auto &c : cands)
+      if (c.kind == p.kind) return true;
+    return false;
+  };
+  if (pinned_ && legal(pin_)) return pin_;
+  auto it = best_.find(Key{(int)op, bucket(bytes)});
+  if (it != best_.end() && legal(it->second)) return it->second;
+  Plan best = cands[0];
+  double bestUs = 1e30;
+  for (auto &c : cands) {
+    double us = estimateUs(c, op, bytes, (int)dtypeSize(dt), caps_);
+    if (us < bestUs) { bestUs = us; best = c; }
+  }
+  return best;
+}
+
+double Tuner::estimate(const Plan &p, flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt) const {
+  return estimateUs(p, op, bytes, (int)dtypeSize(dt), caps_);
+}
+
+void Tuner::pin(const Plan *p) {
+  pinned_ = p != nullptr;
+  if (p) pin_ = *p;
+}
+
+void Tuner::beginTiming(cudaStream_t st) {
+  if (!ev0_) { cudaEventCreate(&ev0_); cudaEventCreate(&ev1_); }
+  cudaEventRecord(ev0_, st);
+}
+
+void Tuner::endTiming(cudaStream_t st) { cudaEventRecord(ev1_, st); }
+
+void Tuner::record(flagcxCommOp_t op, size_t bytes, const Plan &p, double us) {
+  Key k{(int)op, bucket(bytes)};
+  auto it = bestUs_.find(k);
+  if (it == bestUs_.end() || us < it->second) {
+    best_[k] = p;
+    bestUs_[k] = us;
+  }
+}
+
+flagcxResult_t Tuner::load(const std::string &path) {
+  FILE *f = fopen(path.c_str(), "r");
+  if (!f) return flagcxSystemError;
+  char line[512];
+  int loaded = 0;
+  while (fgets(line, sizeof line, f)) {
+    int op, l2, nr, nctas;
+    char kind[64];
+    double us;
+    if (sscanf(line, " {\"op\": %d, \"log2_bytes\": %d, \"nranks\": %d, \"kind\": \"%63[^\"]\", \"nctas\": %d, \"us\": %lf", &op, &l2,
+               &nr, kind, &nctas, &us) == 6) {
+      int k = kindFromName(kind);
+      if (nr != caps_.nranks || k < 0) continue;
+      if ((k == FCX_K_AR_NVLS || k == FCX_K_RS_NVLS || k == FCX_K_AG_NVLS) && !caps_.multicast) continue;
+      best_[{op, l2}] = {k, nctas};
+      bestUs_[{op, l2}] = us;
+      loaded++;
+    }
+  }
+  fclose(f);
+  FCX_INFO(SUB_TUNING, "tuner: loaded %d decisions from %s", loaded, path.c_str());
+  return flagcxSuccess;
+}
+
+flagcxResult_t Tuner::save(const std::string &path) const {
+  FILE *f = fopen(path.c_str(), "w");
+  if (!f) return flagcxSystemError;
+  fprintf(f, "[\n");
+  size_t i = 0;
+  for (auto &kv : best_) {
+    auto us = bestUs_.find(kv.first);
+    fprintf(f, " {\"op\": %d, \"log2_bytes\": %d, \"nranks\": %d, \"kind\": \"%s\", \"nctas\": %d, \"us\": %.3f}%s\n", kv.first.op,
+            kv.first.log2b, caps_.nranks, kindName(kv.second.kind), kv.second.nctas, us == bestUs_.end() ? 0.0 : us->second,
+            ++i == best_.size() ? "" : ",");
+  }
+  fprintf(f, "]\n");
+  fclose(f);
+  return flagcxSuccess;
+}
+
+std::string Tuner::describe() const {
+  std::ostringstream os;
+  for (auto &kv : best_)
+    os << "op " << kv.first.op << " <=2^" << kv.first.log2b << " B: " << kindName(kv.second.kind) << " x" << kv.second.nctas << "\n";
+  return os.str();
+}
+
+}  // namespace fcx

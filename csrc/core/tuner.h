@@ -1,0 +1,108 @@
+// Variant selection for the collective kernels.
+//
+// The reference's tuner searches NCCL environment knobs by tearing the NCCL
+// communicator down and re-creating it per candidate, and times candidates
+// with CUDA events on the caller's stream (flagcx/core/flagcx_tuner.cc:160-449,
+// candidates in flagcx/adaptor/tuner/nccl_tuner.cc:5-16).  This one searches
+// over the library's own kernel variants (kind x CTA count) with no
+// communicator re-creation: a candidate is just different launch arguments.
+//
+//   * prior: an alpha-beta cost model (launch + barriers + NVLink bytes +
+//     local HBM bytes), the counterpart of the reference's unused
+//     flagcx/core/cost_model.cc, seeded with measured link/HBM rates;
+//   * online search (FLAGCX_USE_TUNER=1): for each (op, size bucket) the first
+//     nLoops x nCandidates calls cycle through the candidates, timed with
+//     events; ranks then average their times over the bootstrap network and
+//     adopt the fastest (with 5% hysteresis in favour of the prior's pick);
+//   * persistence (FLAGCX_TUNER_CACHE=<file>): decisions are saved at
+//     communicator destruction and loaded at creation;
+//   * pinning (FLAGCX_USE_COMM_TAG="<kind>:<nctas>") forces one variant.
+#pragma once
+#include "bootstrap.h"
+#include "flagcx.h"
+#include "../kernels/devcomm.h"
+#include <cuda_runtime_api.h>
+#include <map>
+#include <string>
+#include <vector>
+
+namespace fcx {
+
+struct Plan {
+  int kind = 0;   // FcxKind
+  int nctas = 1;
+};
+
+struct TunerCaps {
+  int nranks = 1;
+  bool multicast = false;
+  size_t stageBytes = 0;
+  int maxCtas = 64;
+};
+
+// Estimated duration in microseconds of one launch (cost-model prior).
+double estimateUs(const Plan &p, flagcxCommOp_t op, size_t bytes, int esize, const TunerCaps &caps);
+
+const char *kindName(int kind);
+int kindFromName(const std::string &s);
+
+class Tuner {
+ public:
+  Tuner(Bootstrap *bs, const TunerCaps &caps);
+  ~Tuner();
+
+  // All variants that can legally run this call.
+  std::vector<Plan> candidates(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red, bool cast) const;
+
+  // Pick the plan for this call.  When the online search is active and the
+  // returned `timed` is true the caller brackets the launch with
+  // beginTiming/endTiming.
+  Plan choose(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red, bool cast, bool *timed);
+  void beginTiming(cudaStream_t s);
+  void endTiming(cudaStream_t s);
+
+  // Offline interface: record a measured time for a plan, adopt the best.
+  void record(flagcxCommOp_t op, size_t bytes, const Plan &p, double us);
+  flagcxResult_t load(const std::string &path);
+  flagcxResult_t save(const std::string &path) const;
+  std::string describe() const;  // one line per decided key
+
+  bool searching() const { return search_; }
+  // The plan that would run, without advancing the online search.
+  Plan peek(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red, bool cast) const;
+  double estimate(const Plan &p, flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt) const;
+  // Force one variant for every call it can legally serve; nullptr clears.
+  void pin(const Plan *p);
+
+ private:
+  struct Key {
+    int op, log2b;
+    bool operator<(const Key &o) const { return op != o.op ? op < o.op : log2b < o.log2b; }
+  };
+  struct Search {
+    std::vector<Plan> cands;
+    std::vector<double> sumUs;
+    std::vector<int> nSamples;
+    long calls = 0;
+    bool decided = false;
+  };
+  static int bucket(size_t bytes);
+  void decide(const Key &k, Search &s);
+
+  Bootstrap *bs_;
+  TunerCaps caps_;
+  bool search_ = false;
+  int nLoops_ = 5;
+  bool pinned_ = false;
+  Plan pin_;
+  std::map<Key, Plan> best_;
+  std::map<Key, double> bestUs_;
+  std::map<Key, Search> searches_;
+  // timing state of the call in flight
+  cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
+  Search *cur_ = nullptr;
+  int curIdx_ = -1;
+  Key curKey_{};
+};
+
+}  // namespace fcx

@@ -1,0 +1,95 @@
+/*
+ * flagcx_ext.h - additions of the B200-native library that have no
+ * counterpart in the reference's flagcx.h.  Everything here is optional: a
+ * program written against flagcx.h alone never needs it.
+ */
+#ifndef FLAGCX_EXT_H_
+#define FLAGCX_EXT_H_
+
+#include "flagcx.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* All-reduce with the output cast and a scale fused into the reduction pass:
+ * recv[i] = cast_out( scale * reduce_r(send_r[i]) ).  Accumulation is fp32.
+ * Supported (in -> out): fp32 -> bf16/fp16/fp8e4m3, bf16 -> fp8e4m3/fp8e5m2/fp32,
+ * fp8e4m3 -> bf16, and in == out for every type. */
+flagcxResult_t flagcxAllReduceCast(const void *sendbuff, void *recvbuff, size_t count, flagcxDataType_t inType,
+                                   flagcxDataType_t outType, float scale, flagcxRedOp_t op, flagcxComm_t comm,
+                                   flagcxStream_t stream);
+
+/* Split a communicator MPI-style: ranks passing the same color form a new
+ * communicator, ordered by key (ties by old rank).  color < 0 yields NULL.
+ * Collective over the parent. */
+flagcxResult_t flagcxCommSplit(flagcxComm_t comm, int color, int key, flagcxComm_t *newcomm);
+
+/* Per-communicator statistics. */
+typedef struct {
+  uint64_t calls[flagcxNumCommOps];
+  uint64_t bytes[flagcxNumCommOps];
+  uint64_t launches;      /* kernels launched by the library on behalf of this communicator */
+  uint64_t timeouts;      /* device waits that ended by deadline */
+  uint64_t kindLaunches[16];
+} flagcxCommCounters;
+flagcxResult_t flagcxCommGetCounters(flagcxComm_t comm, flagcxCommCounters *out);
+
+/* Cluster view of a communicator (FLAGCX_CLUSTER_SPLIT_LIST emulates several
+ * clusters on one box). */
+flagcxResult_t flagcxCommGetClusterInfo(flagcxComm_t comm, int *nclusters, int *myCluster, int *clusterOfRank /* nranks ints, may be NULL */);
+
+/* Symmetric heap access for fused kernels written by the user: device
+ * pointers through which this rank reaches every rank's heap, the multicast
+ * alias (NULL when the box has none), and translation of a pointer returned by
+ * flagcxMemAlloc(comm) into its heap offset. */
+flagcxResult_t flagcxCommHeapInfo(flagcxComm_t comm, void **peerBases /* nranks */, void **mcBase, size_t *heapBytes);
+flagcxResult_t flagcxHeapOffset(flagcxComm_t comm, const void *ptr, size_t *offset);
+/* A copy of the device-side communicator descriptor (struct FcxDevComm, see
+ * flagcx_device.cuh) to pass to user kernels by value. */
+flagcxResult_t flagcxCommDeviceDescriptor(flagcxComm_t comm, void *out, size_t outBytes);
+/* Reserve `n` consecutive user signal slots (at most 48 per communicator). */
+flagcxResult_t flagcxCommAllocSignals(flagcxComm_t comm, int n, int *first);
+
+/* Tuner control. */
+flagcxResult_t flagcxTunerRecord(flagcxComm_t comm, flagcxCommOp_t op, size_t bytes, const char *kind, int nctas, double us);
+flagcxResult_t flagcxTunerSave(flagcxComm_t comm, const char *path);
+flagcxResult_t flagcxTunerLoad(flagcxComm_t comm, const char *path);
+/* Force the variant of subsequent calls ("ar_twoshot", 32); kind NULL clears. */
+flagcxResult_t flagcxTunerPin(flagcxComm_t comm, const char *kind, int nctas);
+/* Writes a NUL-terminated description of the plan that would run. */
+flagcxResult_t flagcxTunerQuery(flagcxComm_t comm, flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red,
+                                char *kindOut, size_t kindOutBytes, int *nctas, double *estimateUs);
+
+/* Failure handling.  Device waits are bounded by this many milliseconds
+ * (default FLAGCX_KERNEL_TIMEOUT_MS or 30000). */
+flagcxResult_t flagcxCommSetTimeoutMs(flagcxComm_t comm, int ms);
+/* Launch a kernel that waits for a signal nobody raises; after the time-out
+ * it returns and flagcxCommGetAsyncError reports flagcxRemoteError.  Used to
+ * test the bounded-wait path without disturbing the GPU. */
+flagcxResult_t flagcxCommWaitTest(flagcxComm_t comm, flagcxStream_t stream);
+/* Details of the last device-side give-up: code 0 none / 1 time-out / 2 abort. */
+flagcxResult_t flagcxCommGetDeviceError(flagcxComm_t comm, int *code, int *peer, int *where, unsigned long long *expected,
+                                        unsigned long long *seen);
+/* Clear a recorded device error so that the communicator can be used again
+ * (only meaningful when all ranks do so at the same point). */
+flagcxResult_t flagcxCommClearError(flagcxComm_t comm);
+
+/* Single-GPU emulation of an n-rank collective (protocol tests without
+ * NVLink): runs `nranks` emulated ranks inside one cooperative launch.
+ * send[r]/recv[r] are device pointers on the current device. */
+typedef struct flagcxEmu *flagcxEmu_t;
+flagcxResult_t flagcxEmuCreate(flagcxEmu_t *emu, int nranks, size_t stageBytes);
+flagcxResult_t flagcxEmuDestroy(flagcxEmu_t emu);
+flagcxResult_t flagcxEmuCollective(flagcxEmu_t emu, flagcxCommOp_t op, const char *kind, int nctas, void *const *send,
+                                   void *const *recv, size_t count, flagcxDataType_t dt, flagcxDataType_t outDt, float scale,
+                                   flagcxRedOp_t red, int root, const size_t *a2avTables /* [nranks][4][nranks] or NULL */,
+                                   void *cudaStream);
+flagcxResult_t flagcxEmuSendRecv(flagcxEmu_t emu, int nops, const int *srcRank, const int *dstRank, void *const *sendbuf,
+                                 void *const *recvbuf, const size_t *bytes, int ctasPerOp, void *cudaStream);
+flagcxResult_t flagcxEmuGetError(flagcxEmu_t emu, int *code);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,892 @@
+// The collective kernels.
+//
+// One templated body, fcxCollBody<TIn,TOut>, implements every collective as a
+// sequence of at most three phases separated by cross-GPU CTA barriers.  The
+// data path is "push": a rank stores its contribution straight into the
+// staging area of the peer that needs it (NVLink stores from the SMs), the
+// barrier publishes it, and the receiver combines or copies it out of its own
+// HBM.  The NVLS kinds replace the push by multimem.ld_reduce / multimem.st on
+// the NVSwitch multicast alias of the heaps.  In the reference these
+// operations are calls into the vendor library
+// (flagcx/adaptor/ccl/nccl_adaptor.cc:92-256); nothing here calls it.
+//
+// Work is cut into "units" of G elements (16 bytes of the narrower of the two
+// element types).  Unit u of any buffer is always handled by the same thread
+// of the same CTA index on every rank and in every phase, which is what lets a
+// per-CTA barrier (instead of a grid-wide one) order the phases.
+//
+// The body takes the CTA index and CTA count as arguments so that the very
+// same code can run as one real rank per GPU (fcxCollKernel) or as several
+// emulated ranks inside one cooperative launch on a single GPU
+// (fcxCollEmuKernel), which is how the protocol is tested without NVLink.
+#include "prims.cuh"
+#include "launch.h"
+
+#include <cuda_runtime.h>
+
+namespace fcxdev {
+
+__device__ __forceinline__ char *stagePtr(const FcxDevComm &dc, int r, uint64_t seq) {
+  return dc.heap[r] + FCX_OFF_STAGE + (size_t)(seq & 1) * dc.stageBytes;
+}
+
+// ---------------------------------------------------------------- plain copies
+
+// Copy `bytes` between two buffers in units of `unitBytes` (a multiple of 16).
+// Unit u always belongs to thread (u mod gstride), whatever the alignment, so
+// the same thread that wrote a unit into a slot is the one that reads it back
+// on the other side of a barrier.  When both pointers are 16-byte aligned the
+// loop keeps four independent 16-byte loads in flight per thread.
+__device__ __forceinline__ void copyUnits(char *dst, const char *src, size_t bytes, int unitBytes, size_t gtid,
+                                          size_t gstride) {
+  const size_t nfull = bytes / unitBytes;
+  const int tail = (int)(bytes - nfull * unitBytes);
+  uintptr_t both = (uintptr_t)dst | (uintptr_t)src;
+  if ((both & 15u) == 0) {
+    size_t u = gtid;
+    if (unitBytes == 16) {
+      for (; u + 3 * gstride < nfull; u += 4 * gstride) {
+        uint4 v0 = ld16(src + u * 16), v1 = ld16(src + (u + gstride) * 16), v2 = ld16(src + (u + 2 * gstride) * 16),
+              v3 = ld16(src + (u + 3 * gstride) * 16);
+        st16(dst + u * 16, v0);
+        st16(dst + (u + gstride) * 16, v1);
+        st16(dst + (u + 2 * gstride) * 16, v2);
+        st16(dst + (u + 3 * gstride) * 16, v3);
+      }
+      for (; u < nfull; u += gstride) st16(dst + u * 16, ld16(src + u * 16));
+    } else {
+      const int lines = unitBytes / 16;
+      for (; u < nfull; u += gstride) {
+        uint4 v[4];
+        const char *s = src + u * unitBytes;
+        char *d = dst + u * unitBytes;
+        for (int l0 = 0; l0 < lines; l0 += 4) {
+#pragma unroll
+          for (int l = 0; l < 4; l++)
+            if (l0 + l < lines) v[l] = ld16(s + (l0 + l) * 16);
+#pragma unroll
+          for (int l = 0; l < 4; l++)
+            if (l0 + l < lines) st16(d + (l0 + l) * 16, v[l]);
+        }
+      }
+    }
+  } else if ((both & 3u) == 0 && (bytes & 3u) == 0) {
+    for (size_t u = gtid; u < nfull; u += gstride) {
+      const uint32_t *s = (const uint32_t *)(src + u * unitBytes);
+      uint32_t *d = (uint32_t *)(dst + u * unitBytes);
+      for (int i = 0; i < unitBytes / 4; i++) d[i] = s[i];
+    }
+  } else {
+    for (size_t u = gtid; u < nfull; u += gstride) {
+      const char *s = src + u * unitBytes;
+      char *d = dst + u * unitBytes;
+      for (int i = 0; i < unitBytes; i++) d[i] = s[i];
+    }
+  }
+  if (tail && (nfull % gstride) == gtid) {
+    const char *s = src + nfull * unitBytes;
+    char *d = dst + nfull * unitBytes;
+    for (int i = 0; i < tail; i++) d[i] = s[i];
+  }
+}
+__device__ __forceinline__ void copyToSlot(char *slot, const char *user, size_t bytes, int unitBytes, size_t gtid,
+                                           size_t gstride) {
+  copyUnits(slot, user, bytes, unitBytes, gtid, gstride);
+}
+__device__ __forceinline__ void copyFromSlot(char *user, const char *slot, size_t bytes, int unitBytes, size_t gtid,
+                                             size_t gstride) {
+  copyUnits(user, slot, bytes, unitBytes, gtid, gstride);
+}
+
+// ---------------------------------------------------------------- LL one-shot all-reduce
+
+// A 16-byte LL line carries 8 payload bytes and two copies of the 32-bit
+// sequence tag: {d0, tag, d1, tag}.  Each 8-byte half is written atomically,
+// so a reader that sees the tag in a half also sees that half's payload.
+__device__ __forceinline__ void llStore(char *line, uint32_t d0, uint32_t d1, uint32_t tag) {
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(line), "r"(d0), "r"(tag), "r"(d1), "r"(tag)
+               : "memory");
+}
+__device__ __forceinline__ uint4 llLoad(const char *line) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(line) : "memory");
+  return v;
+}
+
+template <typename T>
+__device__ void arLL(const FcxDevComm &dc, const FcxCollArgs &a, int cta, int nctas) {
+  using Acc = typename Elem<T>::Acc;
+  constexpr int G = 16 / (int)sizeof(T);
+  const int n = dc.nranks, me = dc.rank;
+  const uint32_t tag = (uint32_t)a.seq;
+  const size_t gtid = (size_t)cta * blockDim.x + threadIdx.x, gstride = (size_t)nctas * blockDim.x;
+  const size_t nunits = (a.count + G - 1) / G;
+  const char *send = (const char *)a.send;
+  const bool alS = aligned16(send), alR = aligned16(a.recv);
+  const size_t llOff = FCX_OFF_LL + (size_t)(a.seq & 1) * FCX_MAX_RANKS * FCX_LL_SLOT_BYTES;
+  bool ok = true;
+  for (size_t u = gtid; u < nunits; u += gstride) {
+    int nv = (int)min((size_t)G, a.count - u * G);
+    Acc mine[G];
+    loadUnit<T, G>(send + u * 16, alS, nv, mine);
+    uint4 raw;
+    packUnit<T, G>(mine, &raw);
+    for (int k = 1; k < n; k++) {
+      int p = (me + k) % n;
+      char *line = dc.heap[p] + llOff + (size_t)me * FCX_LL_SLOT_BYTES + u * 32;
+      llStore(line, raw.x, raw.y, tag);
+      llStore(line + 16, raw.z, raw.w, tag);
+    }
+    Acc acc[G];
+    bool first = true;
+    for (int p = 0; p < n; p++) {
+      Acc in[G];
+      if (p == me) {
+#pragma unroll
+        for (int i = 0; i < G; i++) in[i] = mine[i];
+      } else {
+        const char *line = dc.heap[me] + llOff + (size_t)p * FCX_LL_SLOT_BYTES + u * 32;
+        uint4 lo = llLoad(line), hi = llLoad(line + 16);
+        if (!(lo.y == tag && lo.w == tag && hi.y == tag && hi.w == tag)) {
+          uint64_t t0 = globalTimerNs();
+          unsigned spins = 0;
+          for (;;) {
+            lo = llLoad(line);
+            hi = llLoad(line + 16);
+            if (lo.y == tag && lo.w == tag && hi.y == tag && hi.w == tag) break;
+            if ((++spins & 63u) == 0u) {
+              if (*(volatile unsigned int *)&localOf(dc)->abortSeen) { ok = false; break; }
+              if (globalTimerNs() - t0 > dc.timeoutNs) {
+                giveUp(dc, FCX_ERR_TIMEOUT, p, FCX_WAIT_LL, cta, tag, lo.y, a.seq);
+                ok = false;
+                break;
+              }
+              if ((spins & 1023u) == 0u && *dc.abortWord) {
+                giveUp(dc, FCX_ERR_ABORT, p, FCX_WAIT_LL, cta, tag, lo.y, a.seq);
+                ok = false;
+                break;
+              }
+            }
+          }
+          if (!ok) break;
+        }
+        union { uint4 v; T t[G]; } w;
+        w.v = make_uint4(lo.x, lo.z, hi.x, hi.z);
+#pragma unroll
+        for (int i = 0; i < G; i++) in[i] = Elem<T>::up(w.t[i]);
+      }
+      if (first) {
+#pragma unroll
+        for (int i = 0; i < G; i++) acc[i] = in[i];
+        first = false;
+      } else {
+#pragma unroll
+        for (int i = 0; i < G; i++) acc[i] = applyOp<Acc>(acc[i], in[i], a.redop);
+      }
+    }
+    if (!ok) break;
+#pragma unroll
+    for (int i = 0; i < G; i++) acc[i] = finish<Acc>(acc[i], a.redop, n, a.scale);
+    uint4 outv;
+    packUnit<T, G>(acc, &outv);
+    storeUnit<T, G>((char *)a.recv + u * 16, alR, nv, &outv);
+  }
+}
+
+// ---------------------------------------------------------------- reductions out of staging
+
+// out[u] = finish( x_0[u] (op) x_1[u] ... x_{n-1}[u] ) over the ranks in rank
+// order, where x_own comes from `own` (user memory) and the others from the
+// local staging slots.  The result unit goes to `dstUser` (user memory, may
+// be null) and, as a full 16-byte-multiple unit, to every pointer in dstSlots.
+template <typename TIn, typename TOut, int G>
+__device__ __forceinline__ void reduceUnits(const FcxDevComm &dc, const FcxCollArgs &a, const char *own, bool ownAligned,
+                                            const char *slotBase, size_t slotStride, size_t nElems, char *dstUser,
+                                            bool dstAligned, char *const *dstSlots, int nDstSlots, size_t gtid,
+                                            size_t gstride) {
+  using AI = typename Elem<TIn>::Acc;
+  using AO = typename Elem<TOut>::Acc;
+  constexpr int INB = G * (int)sizeof(TIn), OUTB = G * (int)sizeof(TOut);
+  const int n = dc.nranks, me = dc.rank;
+  const size_t nunits = (nElems + G - 1) / G;
+  for (size_t u = gtid; u < nunits; u += gstride) {
+    int nv = (int)min((size_t)G, nElems - u * G);
+    AI acc[G];
+    for (int p = 0; p < n; p++) {
+      AI in[G];
+      if (p == me) loadUnit<TIn, G>(own + u * INB, ownAligned, nv, in);
+      else loadUnit<TIn, G>(slotBase + (size_t)p * slotStride + u * INB, true, G, in);
+      if (p == 0) {
+#pragma unroll
+        for (int i = 0; i < G; i++) acc[i] = in[i];
+      } else {
+#pragma unroll
+        for (int i = 0; i < G; i++) acc[i] = applyOp<AI>(acc[i], in[i], a.redop);
+      }
+    }
+    AO res[G];
+#pragma unroll
+    for (int i = 0; i < G; i++) res[i] = accCast<AO, AI>(finish<AI>(acc[i], a.redop, n, a.scale));
+    uint4 packed[OUTB / 16];
+    packUnit<TOut, G>(res, packed);
+    if (dstUser) storeUnit<TOut, G>(dstUser + u * OUTB, dstAligned, nv, packed);
+    for (int k = 0; k < nDstSlots; k++) storeUnit<TOut, G>(dstSlots[k] + u * OUTB, true, G, packed);
+  }
+}
+
+// ---------------------------------------------------------------- NVLS helpers
+
+template <typename T>
+__device__ __forceinline__ uint4 mmFinish(uint4 r, int op, int nranks, float scale) {
+  // avg and scale need arithmetic on the switch's result
+  if (op != 4 && scale == 1.0f) return r;
+  using Acc = typename Elem<T>::Acc;
+  constexpr int G = 16 / (int)sizeof(T);
+  union { uint4 v; T t[G]; } w;
+  w.v = r;
+  Acc x[G];
+#pragma unroll
+  for (int i = 0; i < G; i++) x[i] = finish<Acc>(Elem<T>::up(w.t[i]), op, nranks, scale);
+  uint4 o;
+  packUnit<T, G>(x, &o);
+  return o;
+}
+
+// ---------------------------------------------------------------- the body
+
+template <typename TIn, typename TOut>
+__device__ void fcxCollBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta, int nctas) {
+  constexpr int ESI = (int)sizeof(TIn), ESO = (int)sizeof(TOut);
+  constexpr int G = 16 / (ESI < ESO ? ESI : ESO);
+  constexpr int INB = G * ESI, OUTB = G * ESO;
+  const int n = dc.nranks, me = dc.rank;
+  const uint64_t seq = a.seq;
+  const size_t gtid = (size_t)cta * blockDim.x + threadIdx.x, gstride = (size_t)nctas * blockDim.x;
+
+  if (!prologue(dc, seq, cta)) return;
+
+  const char *send = (const char *)a.send;
+  char *recv = (char *)a.recv;
+
+  switch (a.kind) {
+    case FCX_K_BARRIER: {
+      if (cta == 0) ctaBarrier(dc, 0, barrierValue(seq, 1), seq);
+      break;
+    }
+
+    case FCX_K_AR_LL: {
+      if constexpr (ESI == ESO) arLL<TIn>(dc, a, cta, nctas);
+      break;
+    }
+
+    case FCX_K_AR_ONESHOT: {
+      // every rank receives every other rank's whole vector
+      const size_t bytes = a.count * ESI;
+      const size_t slot = (bytes + INB - 1) / INB * INB;
+      for (int k = 1; k < n; k++) {
+        int p = (me + k) % n;
+        copyToSlot(stagePtr(dc, p, seq) + (size_t)me * slot, send, bytes, INB, gtid, gstride);
+      }
+      if (!ctaBarrier(dc, cta, barrierValue(seq, 1), seq)) break;
+      reduceUnits<TIn, TOut, G>(dc, a, send, aligned16(send), stagePtr(dc, me, seq), slot, a.count, recv,
+                                aligned16(recv), nullptr, 0, gtid, gstride);
+      break;
+    }
+
+    case FCX_K_AR_TWOSHOT:
+    case FCX_K_REDUCE: {
+      const bool toRootOnly = a.kind == FCX_K_REDUCE;
+      const size_t totalUnits = (a.count + G - 1) / G;
+      const size_t sliceUnits = (totalUnits + n - 1) / n;
+      const size_t sliceElems = sliceUnits * G;
+      const size_t slotA = sliceUnits * INB, slotB = sliceUnits * OUTB;
+      auto elemsOf = [&](int p) -> size_t {
+        size_t lo = (size_t)p * sliceElems;
+        return lo >= a.count ? 0 : min(sliceElems, a.count - lo);
+      };
+      // phase 1: slice p of my vector goes to rank p
+      for (int k = 1; k < n; k++) {
+        int p = (me + k) % n;
+        size_t ne = elemsOf(p);
+        if (ne)
+          copyToSlot(stagePtr(dc, p, seq) + (size_t)me * slotA, send + (size_t)p * sliceElems * ESI, ne * ESI, INB,
+                     gtid, gstride);
+      }
+      if (!ctaBarrier(dc, cta, barrierValue(seq, 1), seq)) break;
+      // phase 2: combine my slice, hand the result to whoever needs it
+      {
+        size_t ne = elemsOf(me);
+        char *dstSlots[FCX_MAX_RANKS];
+        int nd = 0;
+        char *dstUser = nullptr;
+        if (toRootOnly) {
+          if (me == a.root) dstUser = recv + (size_t)me * sliceElems * ESO;
+          else dstSlots[nd++] = stagePtr(dc, a.root, seq) + (size_t)n * slotA + (size_t)me * slotB;
+        } else {
+          dstUser = recv + (size_t)me * sliceElems * ESO;
+          for (int k = 1; k < n; k++) {
+            int p = (me + k) % n;
+            dstSlots[nd++] = stagePtr(dc, p, seq) + (size_t)n * slotA + (size_t)me * slotB;
+          }
+        }
+        if (ne) {
+          const char *own = send + (size_t)me * sliceElems * ESI;
+          reduceUnits<TIn, TOut, G>(dc, a, own, aligned16(own), stagePtr(dc, me, seq), slotA, ne, dstUser,
+                                    dstUser && aligned16(dstUser), dstSlots, nd, gtid, gstride);
+        }
+      }
+      if (!ctaBarrier(dc, cta, barrierValue(seq, 2), seq)) break;
+      // phase 3: collect the other ranks' finished slices
+      if (!toRootOnly || me == a.root) {
+        for (int k = 1; k < n; k++) {
+          int p = (me + k) % n;
+          size_t ne = elemsOf(p);
+          if (ne)
+            copyFromSlot(recv + (size_t)p * sliceElems * ESO,
+                         stagePtr(dc, me, seq) + (size_t)n * slotA + (size_t)p * slotB, ne * ESO, OUTB, gtid, gstride);
+        }
+      }
+      break;
+    }
+
+    case FCX_K_AR_NVLS:
+    case FCX_K_RS_NVLS: {
+      if constexpr (ESI == ESO && Mm<TIn>::ok) {
+        // copy in (local), switch-reduce my slice, multicast it back (all-reduce)
+        // or keep it (reduce-scatter), copy out (local).  Copies are indexed
+        // relative to the slice so that the unit-ownership rule holds between
+        // the rank that wrote a line and the rank that reads it through the switch.
+        const bool isRS = a.kind == FCX_K_RS_NVLS;
+        size_t sliceElems, sliceBytes;
+        if (isRS) {
+          sliceElems = a.count;
+          sliceBytes = (a.count * ESI + 15) / 16 * 16;
+        } else {
+          size_t totalUnits = (a.count + G - 1) / G;
+          size_t sliceUnits = (totalUnits + n - 1) / n;
+          sliceElems = sliceUnits * G;
+          sliceBytes = sliceUnits * 16;
+        }
+        auto elemsOf = [&](int p) -> size_t {
+          if (isRS) return a.count;
+          size_t lo = (size_t)p * sliceElems;
+          return lo >= a.count ? 0 : min(sliceElems, a.count - lo);
+        };
+        const size_t srcStride = isRS ? a.sendStride : sliceElems;
+        for (int p = 0; p < n; p++) {
+          size_t ne = elemsOf(p);
+          if (ne)
+            copyToSlot(stagePtr(dc, me, seq) + (size_t)p * sliceBytes, send + (size_t)p * srcStride * ESI, ne * ESI, 16,
+                       gtid, gstride);
+        }
+        if (!ctaBarrier(dc, cta, barrierValue(seq, 1), seq)) break;
+        const size_t stageOff = FCX_OFF_STAGE + (size_t)(seq & 1) * dc.stageBytes;
+        char *mcSlice = dc.mcHeap + stageOff + (size_t)me * sliceBytes;
+        const size_t myElems = elemsOf(me);
+        const size_t myUnits = (myElems + G - 1) / G;
+        if (isRS) {
+          bool alR = aligned16(recv);
+          size_t u = gtid;
+          for (; u + 3 * gstride < myUnits; u += 4 * gstride) {
+            uint4 r[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) r[i] = Mm<TIn>::ldReduce(mcSlice + (u + i * gstride) * 16, a.redop);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+              size_t uu = u + i * gstride;
+              uint4 f = mmFinish<TIn>(r[i], a.redop, n, a.scale);
+              storeUnit<TIn, G>(recv + uu * 16, alR, (int)min((size_t)G, myElems - uu * G), &f);
+            }
+          }
+          for (; u < myUnits; u += gstride) {
+            uint4 f = mmFinish<TIn>(Mm<TIn>::ldReduce(mcSlice + u * 16, a.redop), a.redop, n, a.scale);
+            storeUnit<TIn, G>(recv + u * 16, alR, (int)min((size_t)G, myElems - u * G), &f);
+          }
+          break;
+        }
+        {
+          size_t u = gtid;
+          for (; u + 3 * gstride < myUnits; u += 4 * gstride) {
+            uint4 r[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) r[i] = Mm<TIn>::ldReduce(mcSlice + (u + i * gstride) * 16, a.redop);
+#pragma unroll
+            for (int i = 0; i < 4; i++) mmStore(mcSlice + (u + i * gstride) * 16, mmFinish<TIn>(r[i], a.redop, n, a.scale));
+          }
+          for (; u < myUnits; u += gstride)
+            mmStore(mcSlice + u * 16, mmFinish<TIn>(Mm<TIn>::ldReduce(mcSlice + u * 16, a.redop), a.redop, n, a.scale));
+        }
+        if (!ctaBarrier(dc, cta, barrierValue(seq, 2), seq)) break;
+        for (int p = 0; p < n; p++) {
+          size_t ne = elemsOf(p);
+          if (ne)
+            copyFromSlot(recv + (size_t)p * sliceElems * ESI, stagePtr(dc, me, seq) + (size_t)p * sliceBytes, ne * ESI, 16,
+                         gtid, gstride);
+        }
+      }
+      break;
+    }
+
+    case FCX_K_RS: {
+      const size_t bytes = a.count * ESI;
+      const size_t slot = (bytes + INB - 1) / INB * INB;
+      for (int k = 1; k < n; k++) {
+        int p = (me + k) % n;
+        copyToSlot(stagePtr(dc, p, seq) + (size_t)me * slot, send + (size_t)p * a.sendStride * ESI, bytes, INB, gtid,
+                   gstride);
+      }
+      if (!ctaBarrier(dc, cta, barrierValue(seq, 1), seq)) break;
+      const char *own = send + (size_t)me * a.sendStride * ESI;
+      reduceUnits<TIn, TOut, G>(dc, a, own, aligned16(own), stagePtr(dc, me, seq), slot, a.count, recv, aligned16(recv),
+                                nullptr, 0, gtid, gstride);
+      break;
+    }
+
+    default:
+      break;
+  }
+
+  epilogue(dc, seq, nctas);
+}
+
+// Byte-moving collectives need no element type.
+__device__ void fcxMoveBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta, int nctas) {
+  const int n = dc.nranks, me = dc.rank;
+  const uint64_t seq = a.seq;
+  const size_t gtid = (size_t)cta * blockDim.x + threadIdx.x, gstride = (size_t)nctas * blockDim.x;
+  const size_t es = a.elemSize;
+  if (!prologue(dc, seq, cta)) return;
+  const char *send = (const char *)a.send;
+  char *recv = (char *)a.recv;
+  const size_t bytes = a.count * es;
+  const size_t slot = (bytes + 15) / 16 * 16;
+
+  switch (a.kind) {
+    case FCX_K_AG: {
+      for (int k = 1; k < n; k++) {
+        int p = (me + k) % n;
+        copyToSlot(stagePtr(dc, p, seq) + (size_t)me * slot, send, bytes, 16, gtid, gstride);
+      }
+      char *mine = recv + (size_t)me * a.recvStride * es;
+      if (mine != send) copyUnits(mine, send, bytes, 16, gtid, gstride);
+      if (!ctaBarrier(dc, cta, barrierValue(seq, 1), seq)) break;
+      for (int k = 1; k < n; k++) {
+        int p = (me + k) % n;
+        copyFromSlot(recv + (size_t)p * a.recvStride * es, stagePtr(dc, me, seq) + (size_t)p * slot, bytes, 16, gtid,
+                     gstride);
+      }
+      break;
+    }
+
+    case FCX_K_AG_NVLS: {
+      // one multicast store per line instead of n-1 unicast stores
+      const size_t stageOff = FCX_OFF_STAGE + (size_t)(seq & 1) * dc.stageBytes;
+      char *mc = dc.mcHeap + stageOff + (size_t)me * slot;
+      bool al = aligned16(send);
+      size_t nunits = (bytes + 15) / 16;
+      for (size_t u = gtid; u < nunits; u += gstride) {
+        uint4 v;
+        int nv = (int)min((size_t)16, bytes - u * 16);
+        if (al && nv == 16) v = ld16(send + u * 16);
+        else {
+          union { uint4 q; char c[16]; } w;
+          w.q = make_uint4(0, 0, 0, 0);
+          for (int i = 0; i < nv; i++) w.c[i] = send[u * 16 + i];
+          v = w.q;
+        }
+        mmStore(mc + u * 16, v);
+      }
+      if (!ctaBarrier(dc, cta, barrierValue(seq, 1), seq)) break;
+      for (int p = 0; p < n; p++) {
+        char *dst = recv + (size_t)p * a.recvStride * es;
+        if (p == me && dst == send) continue;
+        copyFromSlot(dst, stagePtr(dc, me, seq) + (size_t)p * slot, bytes, 16, gtid, gstride);
+      }
+      break;
+    }
+
+    case FCX_K_BCAST: {
+      const bool useMc = dc.mcHeap != nullptr && a.useMc;
+      if (me == a.root) {
+        if (useMc) {
+          const size_t stageOff = FCX_OFF_STAGE + (size_t)(seq & 1) * dc.stageBytes;
+          char *mc = dc.mcHeap + stageOff;
+          bool al = aligned16(send);
+          size_t nunits = (bytes + 15) / 16;
+          for (size_t u = gtid; u < nunits; u += gstride) {
+            int nv = (int)min((size_t)16, bytes - u * 16);
+            uint4 v;
+            if (al && nv == 16) v = ld16(send + u * 16);
+            else {
+              union { uint4 q; char c[16]; } w;
+              w.q = make_uint4(0, 0, 0, 0);
+              for (int i = 0; i < nv; i++) w.c[i] = send[u * 16 + i];
+              v = w.q;
+            }
+            mmStore(mc + u * 16, v);
+          }
+        } else {
+          for (int k = 1; k < n; k++) {
+            int p = (me + k) % n;
+            copyToSlot(stagePtr(dc, p, seq), send, bytes, 16, gtid, gstride);
+          }
+        }
+        if (recv != send) copyUnits(recv, send, bytes, 16, gtid, gstride);
+      }
+      if (!ctaBarrier(dc, cta, barrierValue(seq, 1), seq)) break;
+      if (me != a.root) copyFromSlot(recv, stagePtr(dc, me, seq), bytes, 16, gtid, gstride);
+      break;
+    }
+
+    case FCX_K_GATHER: {
+      if (me != a.root) {
+        copyToSlot(stagePtr(dc, a.root, seq) + (size_t)me * slot, send, bytes, 16, gtid, gstride);
+      } else {
+        char *mine = recv + (size_t)me * a.recvStride * es;
+        if (mine != send) copyUnits(mine, send, bytes, 16, gtid, gstride);
+      }
+      if (!ctaBarrier(dc, cta, barrierValue(seq, 1), seq)) break;
+      if (me == a.root)
+        for (int k = 1; k < n; k++) {
+          int p = (me + k) % n;
+          copyFromSlot(recv + (size_t)p * a.recvStride * es, stagePtr(dc, me, seq) + (size_t)p * slot, bytes, 16, gtid,
+                       gstride);
+        }
+      break;
+    }
+
+    case FCX_K_SCATTER: {
+      if (me == a.root) {
+        for (int k = 1; k < n; k++) {
+          int p = (me + k) % n;
+          copyToSlot(stagePtr(dc, p, seq), send + (size_t)p * a.sendStride * es, bytes, 16, gtid, gstride);
+        }
+        const char *mine = send + (size_t)me * a.sendStride * es;
+        if (mine != recv) copyUnits(recv, mine, bytes, 16, gtid, gstride);
+      }
+      if (!ctaBarrier(dc, cta, barrierValue(seq, 1), seq)) break;
+      if (me != a.root) copyFromSlot(recv, stagePtr(dc, me, seq), bytes, 16, gtid, gstride);
+      break;
+    }
+
+    case FCX_K_A2A: {
+      for (int k = 1; k < n; k++) {
+        int p = (me + k) % n;
+        copyToSlot(stagePtr(dc, p, seq) + (size_t)me * slot, send + (size_t)p * a.sendStride * es, bytes, 16, gtid,
+                   gstride);
+      }
+      {
+        const char *s = send + (size_t)me * a.sendStride * es;
+        char *d = recv + (size_t)me * a.recvStride * es;
+        if (s != d) copyUnits(d, s, bytes, 16, gtid, gstride);
+      }
+      if (!ctaBarrier(dc, cta, barrierValue(seq, 1), seq)) break;
+      for (int k = 1; k < n; k++) {
+        int p = (me + k) % n;
+        copyFromSlot(recv + (size_t)p * a.recvStride * es, stagePtr(dc, me, seq) + (size_t)p * slot, bytes, 16, gtid,
+                     gstride);
+      }
+      break;
+    }
+
+    case FCX_K_A2AV: {
+      // Variable blocks move in rounds through per-source slots that are cut
+      // in two halves, so that round k+1 can be pushed while the receiver
+      // still copies round k-1 out... the barrier of round k orders them.
+      // Ranks first agree on the number of rounds through the mailboxes.
+      const size_t slotBytes = (dc.stageBytes / n / 2) & ~(size_t)15;
+      uint64_t myRounds = 1;
+      for (int p = 0; p < n; p++) {
+        uint64_t r1 = (a.scounts[p] * es + slotBytes - 1) / slotBytes, r2 = (a.rcounts[p] * es + slotBytes - 1) / slotBytes;
+        myRounds = max(myRounds, max(r1, r2));
+      }
+      if (threadIdx.x < n && threadIdx.x != me) {
+        FcxMail *mb = (FcxMail *)(dc.heap[threadIdx.x] + FCX_OFF_MAIL) + (seq & 1) * FCX_MAX_RANKS + me;
+        stRelaxed(&mb->a, myRounds);
+      }
+      if (!ctaBarrier(dc, cta, barrierValue(seq, 1), seq)) break;
+      uint64_t rounds = myRounds;
+      for (int p = 0; p < n; p++)
+        if (p != me) {
+          const FcxMail *mb = (const FcxMail *)(dc.heap[me] + FCX_OFF_MAIL) + (seq & 1) * FCX_MAX_RANKS + p;
+          rounds = max(rounds, ldRelaxed(&mb->a));
+        }
+      {
+        const char *s = send + a.sdispls[me] * es;
+        char *d = recv + a.rdispls[me] * es;
+        size_t b = a.scounts[me] * es;
+        if (s != d && b) copyUnits(d, s, b, 16, gtid, gstride);
+      }
+      bool ok = true;
+      for (uint64_t r = 0; r < rounds && ok; r++) {
+        const size_t half = (r & 1) * slotBytes;
+        for (int k = 1; k < n; k++) {
+          int p = (me + k) % n;
+          size_t tot = a.scounts[p] * es, lo = r * slotBytes;
+          if (lo < tot)
+            copyToSlot(stagePtr(dc, p, seq) + (size_t)me * 2 * slotBytes + half, send + a.sdispls[p] * es + lo,
+                       min(slotBytes, tot - lo), 16, gtid, gstride);
+        }
+        ok = ctaBarrier(dc, cta, barrierValue(seq, 2 + (unsigned)r), seq);
+        if (!ok) break;
+        for (int k = 1; k < n; k++) {
+          int p = (me + k) % n;
+          size_t tot = a.rcounts[p] * es, lo = r * slotBytes;
+          if (lo < tot)
+            copyFromSlot(recv + a.rdispls[p] * es + lo, stagePtr(dc, me, seq) + (size_t)p * 2 * slotBytes + half,
+                         min(slotBytes, tot - lo), 16, gtid, gstride);
+        }
+      }
+      break;
+    }
+
+    default:
+      break;
+  }
+  epilogue(dc, seq, nctas);
+}
+
+// ---------------------------------------------------------------- grouped send/recv
+
+// Each op owns `ctasPerOp` consecutive CTAs.  Staged sends copy a chunk into
+// this rank's per-peer staging slot and raise `ready` on the receiver; the
+// receiver pulls the chunk over NVLink and raises `consumed` on the sender.
+// A send whose buffer lives in the heap publishes the offset instead and the
+// receiver pulls straight from it.
+__device__ __forceinline__ FcxP2pCtl *p2pCtl(const FcxDevComm &dc, int onRank, int dir, int peer) {
+  return (FcxP2pCtl *)(dc.heap[onRank] + FCX_OFF_P2P) + dir * FCX_MAX_RANKS + peer;
+}
+
+// Arrive at the op's counter; returns true in every thread of the last CTA.
+__device__ __forceinline__ bool opArrive(const FcxDevComm &dc, int op, int slot, int ctasPerOp) {
+  __shared__ unsigned int isLast;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    unsigned int *c = &localOf(dc)->opCount[op][slot];
+    unsigned int old = atomicAdd(c, 1u);
+    isLast = (old == (unsigned)ctasPerOp - 1u);
+    if (isLast) { *c = 0; __threadfence(); }
+  }
+  __syncthreads();
+  return isLast != 0;
+}
+
+__device__ void fcxP2pBody(const FcxDevComm &dc, const FcxP2pArgs &g, int cta) {
+  const int opIdx = cta / g.ctasPerOp, sub = cta % g.ctasPerOp;
+  if (opIdx >= g.nops) return;
+  if (*(volatile unsigned int *)&localOf(dc)->abortSeen) return;
+  const FcxP2pOp &op = g.ops[opIdx];
+  const int me = dc.rank, peer = op.peer;
+  const size_t gtid = (size_t)sub * blockDim.x + threadIdx.x, gstride = (size_t)g.ctasPerOp * blockDim.x;
+  const size_t chunk = dc.p2pChunkBytes;
+  const uint64_t nchunks = op.bytes ? (op.bytes + chunk - 1) / chunk : 1;
+
+  if (op.isRecv == 2) {  // local copy (send to self matched with recv from self); peer field unused
+    const char *s = (const char *)(uintptr_t)op.heapOff;
+    char *d = (char *)op.buf;
+    copyUnits(d, s, op.bytes, 16, gtid, gstride);
+    return;
+  }
+
+  if (!op.isRecv) {
+    // ---- sender
+    FcxP2pCtl *theirs = p2pCtl(dc, peer, 0, me);  // on the receiver: what I (sender) publish
+    FcxP2pCtl *mine = p2pCtl(dc, me, 1, peer);    // on me: what the receiver publishes
+    const bool zeroCopy = op.heapOff != ~0ull;
+    if (zeroCopy) {
+      if (sub == 0 && threadIdx.x == 0) {
+        stRelaxed(&theirs->srcOff, op.heapOff);
+        stRelease(&theirs->ready, op.firstChunk + nchunks);
+      }
+      // the buffer stays in use until the receiver has read all of it
+      bool ok = true;
+      if (threadIdx.x == 0)
+        ok = waitGe(dc, &mine->consumed, op.firstChunk + nchunks, peer, FCX_WAIT_P2P_CONSUMED, cta, op.firstChunk);
+      __syncthreads_and(ok);
+      return;
+    }
+    for (uint64_t c = 0; c < nchunks; c++) {
+      uint64_t gidx = op.firstChunk + c;
+      int slot = (int)(gidx & 1);
+      bool ok = true;
+      if (gidx >= 2 && threadIdx.x == 0)
+        ok = waitGe(dc, &mine->consumed, gidx - 1, peer, FCX_WAIT_P2P_CONSUMED, cta, gidx);
+      if (!__syncthreads_and(ok)) return;
+      size_t lo = c * chunk, nb = op.bytes > lo ? min(chunk, op.bytes - lo) : 0;
+      char *st = dc.heap[me] + dc.p2pOff + ((size_t)peer * 2 + slot) * chunk;
+      if (nb) copyToSlot(st, (const char *)op.buf + lo, nb, 16, gtid, gstride);
+      if (opArrive(dc, opIdx, slot, g.ctasPerOp) && threadIdx.x == 0) {
+        if (c == 0) stRelaxed(&theirs->srcOff, ~0ull);
+        stRelease(&theirs->ready, gidx + 1);
+      }
+    }
+    return;
+  }
+
+  // ---- receiver
+  FcxP2pCtl *mine = p2pCtl(dc, me, 0, peer);    // on me: what the sender publishes
+  FcxP2pCtl *theirs = p2pCtl(dc, peer, 1, me);  // on the sender: what I (receiver) publish
+  {
+    bool ok = true;
+    if (threadIdx.x == 0) ok = waitGe(dc, &mine->ready, op.firstChunk + 1, peer, FCX_WAIT_P2P_READY, cta, op.firstChunk);
+    if (!__syncthreads_and(ok)) return;
+  }
+  const uint64_t srcOff = ldRelaxed(&mine->srcOff);
+  if (srcOff != ~0ull) {
+    if (op.bytes) copyFromSlot((char *)op.buf, dc.heap[peer] + srcOff, op.bytes, 16, gtid, gstride);
+    if (opArrive(dc, opIdx, 0, g.ctasPerOp) && threadIdx.x == 0) stRelease(&theirs->consumed, op.firstChunk + nchunks);
+    return;
+  }
+  for (uint64_t c = 0; c < nchunks; c++) {
+    uint64_t gidx = op.firstChunk + c;
+    int slot = (int)(gidx & 1);
+    if (c > 0) {
+      bool ok = true;
+      if (threadIdx.x == 0) ok = waitGe(dc, &mine->ready, gidx + 1, peer, FCX_WAIT_P2P_READY, cta, gidx);
+      if (!__syncthreads_and(ok)) return;
+    }
+    size_t lo = c * chunk, nb = op.bytes > lo ? min(chunk, op.bytes - lo) : 0;
+    const char *st = dc.heap[peer] + dc.p2pOff + ((size_t)me * 2 + slot) * chunk;
+    if (nb) copyFromSlot((char *)op.buf + lo, st, nb, 16, gtid, gstride);
+    if (opArrive(dc, opIdx, slot, g.ctasPerOp) && threadIdx.x == 0) stRelease(&theirs->consumed, gidx + 1);
+  }
+}
+
+// ---------------------------------------------------------------- global entry points
+
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(FCX_THREADS, 1) fcxCollKernel(FcxDevComm dc, FcxCollArgs a) {
+  fcxCollBody<TIn, TOut>(dc, a, blockIdx.x, gridDim.x);
+}
+__global__ void __launch_bounds__(FCX_THREADS, 1) fcxMoveKernel(FcxDevComm dc, FcxCollArgs a) {
+  fcxMoveBody(dc, a, blockIdx.x, gridDim.x);
+}
+__global__ void __launch_bounds__(FCX_THREADS, 1) fcxP2pKernel(FcxDevComm dc, FcxP2pArgs g) {
+  fcxP2pBody(dc, g, blockIdx.x);
+}
+
+// Emulation: rank = blockIdx.x / ctasPerRank.  Launched cooperatively so that
+// all emulated ranks are resident at once and may wait on one another.
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(FCX_THREADS, 1) fcxCollEmuKernel(const FcxDevComm *dcs, const FcxCollArgs *as, int ctasPerRank) {
+  int r = blockIdx.x / ctasPerRank;
+  fcxCollBody<TIn, TOut>(dcs[r], as[r], blockIdx.x % ctasPerRank, ctasPerRank);
+}
+__global__ void __launch_bounds__(FCX_THREADS, 1) fcxMoveEmuKernel(const FcxDevComm *dcs, const FcxCollArgs *as, int ctasPerRank) {
+  int r = blockIdx.x / ctasPerRank;
+  fcxMoveBody(dcs[r], as[r], blockIdx.x % ctasPerRank, ctasPerRank);
+}
+__global__ void __launch_bounds__(FCX_THREADS, 1) fcxP2pEmuKernel(const FcxDevComm *dcs, const FcxP2pArgs *gs, int ctasPerRank) {
+  int r = blockIdx.x / ctasPerRank;
+  fcxP2pBody(dcs[r], gs[r], blockIdx.x % ctasPerRank);
+}
+
+// A wait that nothing satisfies, used to test the time-out path: returns
+// after dc.timeoutNs with the error record filled in.
+__global__ void fcxWaitTestKernel(FcxDevComm dc, uint64_t want) {
+  if (threadIdx.x == 0) {
+    const uint64_t *f = (const uint64_t *)(dc.heap[dc.rank] + FCX_OFF_DEVAPI) + (FCX_DEVAPI_SIGNALS - 1) * FCX_MAX_RANKS;
+    waitGe(dc, f, want, dc.rank, FCX_WAIT_TEST, 0, 0);
+  }
+}
+
+}  // namespace fcxdev
+
+// ---------------------------------------------------------------- host launchers
+
+using namespace fcxdev;
+
+namespace {
+
+template <typename TIn, typename TOut>
+cudaError_t launchTyped(const FcxDevComm &dc, const FcxCollArgs &a, int nctas, cudaStream_t s) {
+  fcxCollKernel<TIn, TOut><<<nctas, FCX_THREADS, 0, s>>>(dc, a);
+  return cudaGetLastError();
+}
+
+template <typename TIn, typename TOut>
+cudaError_t launchTypedEmu(const FcxDevComm *dcs, const FcxCollArgs *as, int nranks, int nctas, cudaStream_t s) {
+  void *params[] = {(void *)&dcs, (void *)&as, (void *)&nctas};
+  return cudaLaunchCooperativeKernel((const void *)fcxCollEmuKernel<TIn, TOut>, dim3(nranks * nctas), dim3(FCX_THREADS),
+                                     params, 0, s);
+}
+
+// dtype codes follow flagcxDataType_t
+#define FCX_DISPATCH_SAME(DT, CALL)                                         \
+  switch (DT) {                                                             \
+    case 0: return CALL(int8_t, int8_t);                                    \
+    case 1: return CALL(uint8_t, uint8_t);                                  \
+    case 2: return CALL(int32_t, int32_t);                                  \
+    case 3: return CALL(uint32_t, uint32_t);                                \
+    case 4: return CALL(long long, long long);                              \
+    case 5: return CALL(unsigned long long, unsigned long long);            \
+    case 6: return CALL(__half, __half);                                    \
+    case 7: return CALL(float, float);                                      \
+    case 8: return CALL(double, double);                                    \
+    case 9: return CALL(__nv_bfloat16, __nv_bfloat16);                      \
+    case 10: return CALL(F8E4, F8E4);                                       \
+    case 11: return CALL(F8E5, F8E5);                                       \
+    default: return cudaErrorInvalidValue;                                  \
+  }
+
+}  // namespace
+
+extern "C" cudaError_t fcxLaunchColl(const FcxDevComm *dc, const FcxCollArgs *a, int nctas, cudaStream_t s) {
+  if (a->kind >= FCX_K_AG && a->kind != FCX_K_REDUCE) {
+    fcxMoveKernel<<<nctas, FCX_THREADS, 0, s>>>(*dc, *a);
+    return cudaGetLastError();
+  }
+  if (a->kind == FCX_K_BARRIER) return launchTyped<uint8_t, uint8_t>(*dc, *a, 1, s);
+#define CALL(TI, TO) launchTyped<TI, TO>(*dc, *a, nctas, s)
+  if (a->outDtype == a->dtype) { FCX_DISPATCH_SAME(a->dtype, CALL) }
+  // fused cast: wide input, narrow output
+  if (a->dtype == 7 && a->outDtype == 9) return CALL(float, __nv_bfloat16);
+  if (a->dtype == 7 && a->outDtype == 6) return CALL(float, __half);
+  if (a->dtype == 7 && a->outDtype == 10) return CALL(float, F8E4);
+  if (a->dtype == 9 && a->outDtype == 10) return CALL(__nv_bfloat16, F8E4);
+  if (a->dtype == 9 && a->outDtype == 11) return CALL(__nv_bfloat16, F8E5);
+  if (a->dtype == 9 && a->outDtype == 7) return CALL(__nv_bfloat16, float);
+  if (a->dtype == 10 && a->outDtype == 9) return CALL(F8E4, __nv_bfloat16);
+#undef CALL
+  return cudaErrorInvalidValue;
+}
+
+extern "C" cudaError_t fcxLaunchP2p(const FcxDevComm *dc, const FcxP2pArgs *g, cudaStream_t s) {
+  fcxP2pKernel<<<g->nops * g->ctasPerOp, FCX_THREADS, 0, s>>>(*dc, *g);
+  return cudaGetLastError();
+}
+
+extern "C" cudaError_t fcxLaunchWaitTest(const FcxDevComm *dc, uint64_t want, cudaStream_t s) {
+  fcxWaitTestKernel<<<1, 32, 0, s>>>(*dc, want);
+  return cudaGetLastError();
+}
+
+// dcs/as/gs are device arrays with one entry per emulated rank.
+extern "C" cudaError_t fcxLaunchCollEmu(const FcxDevComm *dcs, const FcxCollArgs *as, const FcxCollArgs *hostArgs0,
+                                        int nranks, int nctas, cudaStream_t s) {
+  const FcxCollArgs *a = hostArgs0;
+  if (a->kind >= FCX_K_AG && a->kind != FCX_K_REDUCE) {
+    void *params[] = {(void *)&dcs, (void *)&as, (void *)&nctas};
+    return cudaLaunchCooperativeKernel((const void *)fcxMoveEmuKernel, dim3(nranks * nctas), dim3(FCX_THREADS), params, 0, s);
+  }
+#define CALL(TI, TO) launchTypedEmu<TI, TO>(dcs, as, nranks, nctas, s)
+  if (a->kind == FCX_K_BARRIER) return CALL(uint8_t, uint8_t);
+  if (a->outDtype == a->dtype) { FCX_DISPATCH_SAME(a->dtype, CALL) }
+  if (a->dtype == 7 && a->outDtype == 9) return CALL(float, __nv_bfloat16);
+  if (a->dtype == 7 && a->outDtype == 6) return CALL(float, __half);
+  if (a->dtype == 7 && a->outDtype == 10) return CALL(float, F8E4);
+  if (a->dtype == 9 && a->outDtype == 10) return CALL(__nv_bfloat16, F8E4);
+  if (a->dtype == 9 && a->outDtype == 11) return CALL(__nv_bfloat16, F8E5);
+  if (a->dtype == 9 && a->outDtype == 7) return CALL(__nv_bfloat16, float);
+  if (a->dtype == 10 && a->outDtype == 9) return CALL(F8E4, __nv_bfloat16);
+#undef CALL
+  return cudaErrorInvalidValue;
+}
+
+extern "C" cudaError_t fcxLaunchP2pEmu(const FcxDevComm *dcs, const FcxP2pArgs *gs, int nranks, int ctasPerRank,
+                                       cudaStream_t s) {
+  void *params[] = {(void *)&dcs, (void *)&gs, (void *)&ctasPerRank};
+  return cudaLaunchCooperativeKernel((const void *)fcxP2pEmuKernel, dim3(nranks * ctasPerRank), dim3(FCX_THREADS), params, 0, s);
+}
