@@ -70,10 +70,10 @@ flagcxResult_t hostCollective(flagcxComm *c, const PendingOp &o) {
     FCX_CHECK(cudaToResult(cudaStreamSynchronize(o.stream), "host path"));
     hs.resize(sendBytes);
     hr.resize(std::max(recvBytes, (size_t)1));
-    if (sendBytes) FCX_CHECK(cudaToResult(cudaMemcpy(hs.data(), o.send, sendBytes, cudaMemcpyDeviceToHost), "host path D2H"));
+    if (sendBytes) FCX_CHECK(cudaToResult(cudaMemcpy(hs.data(), o.send, sendBytes, cudaMemcpyDefault), "host path D2H"));
     if (o.op == flagcxCommOpAllGather || o.op == flagcxCommOpGather || o.op == flagcxCommOpAlltoAllv) {
       // these may leave parts of recv untouched or are written in place: start from the device contents
-      if (recvBytes) FCX_CHECK(cudaToResult(cudaMemcpy(hr.data(), o.recv, recvBytes, cudaMemcpyDeviceToHost), "host path D2H"));
+      if (recvBytes) FCX_CHECK(cudaToResult(cudaMemcpy(hr.data(), o.recv, recvBytes, cudaMemcpyDefault), "host path D2H"));
     }
     send = hs.data();
     recv = hr.data();
@@ -94,7 +94,7 @@ flagcxResult_t hostCollective(flagcxComm *c, const PendingOp &o) {
     default: r = flagcxInvalidArgument;
   }
   FCX_CHECK(r);
-  if (viaCopies && recvBytes) FCX_CHECK(cudaToResult(cudaMemcpy(o.recv, hr.data(), recvBytes, cudaMemcpyHostToDevice), "host path H2D"));
+  if (viaCopies && recvBytes) FCX_CHECK(cudaToResult(cudaMemcpy(o.recv, hr.data(), recvBytes, cudaMemcpyDefault), "host path H2D"));
   return flagcxSuccess;
 }
 

@@ -66,7 +66,7 @@ static void detectClusters(flagcxComm *c) {
   c->myCluster = c->clusterOf[c->rank];
 }
 
-flagcxResult_t commCreate(flagcxComm **out, int nranks, const BootstrapHandle &h, int rank, double heapScale) {
+flagcxResult_t commCreate(flagcxComm **out, int nranks, const BootstrapHandle &h, int rank, double heapScale, unsigned flags) {
   if (nranks < 1 || rank < 0 || rank >= nranks) return flagcxInvalidArgument;
   std::unique_ptr<flagcxComm> c(new flagcxComm);
   c->rank = rank;
@@ -78,6 +78,7 @@ flagcxResult_t commCreate(flagcxComm **out, int nranks, const BootstrapHandle &h
   bool haveGpu = cudaGetDeviceCount(&ndev) == cudaSuccess && ndev > 0;
   cudaGetLastError();
   bool forceHost = envInt("USE_HOST_COMM", 0) != 0;
+  if (flags & FLAGCX_INIT_HOST_ONLY) haveGpu = false;  // buffers of this communicator are host memory
   c->hostOnly = !haveGpu;
   c->hostFallback = haveGpu && forceHost;
   if (haveGpu) cudaGetDevice(&c->cudaDev);
@@ -350,7 +351,17 @@ flagcxResult_t flagcxCommInitRank(flagcxComm_t *comm, int nranks, flagcxUniqueId
   BootstrapHandle h;
   memcpy(&h, commId->internal, sizeof h);
   flagcxComm *c = nullptr;
-  FCX_CHECK(commCreate(&c, nranks, h, rank, 1.0));
+  FCX_CHECK(commCreate(&c, nranks, h, rank, 1.0, 0));
+  *comm = c;
+  return flagcxSuccess;
+}
+
+flagcxResult_t flagcxCommInitRankEx(flagcxComm_t *comm, int nranks, flagcxUniqueId_t commId, int rank, unsigned flags) {
+  if (!comm || !commId) return flagcxInvalidArgument;
+  BootstrapHandle h;
+  memcpy(&h, commId->internal, sizeof h);
+  flagcxComm *c = nullptr;
+  FCX_CHECK(commCreate(&c, nranks, h, rank, 1.0, flags));
   *comm = c;
   return flagcxSuccess;
 }

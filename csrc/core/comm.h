@@ -108,7 +108,7 @@ flagcxResult_t hostCollective(flagcxComm *c, const PendingOp &op);
 int groupDepth();
 
 // comm.cc
-flagcxResult_t commCreate(flagcxComm **out, int nranks, const BootstrapHandle &h, int rank, double heapScale);
+flagcxResult_t commCreate(flagcxComm **out, int nranks, const BootstrapHandle &h, int rank, double heapScale, unsigned flags);
 flagcxResult_t commFree(flagcxComm *c);
 
 }  // namespace fcx

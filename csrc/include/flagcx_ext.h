@@ -20,6 +20,11 @@ flagcxResult_t flagcxAllReduceCast(const void *sendbuff, void *recvbuff, size_t 
                                    flagcxDataType_t outType, float scale, flagcxRedOp_t op, flagcxComm_t comm,
                                    flagcxStream_t stream);
 
+/* flagcxCommInitRank with options.  FLAGCX_INIT_HOST_ONLY makes a communicator
+ * whose buffers are host memory (TCP host path) even on a machine with GPUs. */
+#define FLAGCX_INIT_HOST_ONLY 1u
+flagcxResult_t flagcxCommInitRankEx(flagcxComm_t *comm, int nranks, flagcxUniqueId_t commId, int rank, unsigned flags);
+
 /* Split a communicator MPI-style: ranks passing the same color form a new
  * communicator, ordered by key (ties by old rank).  color < 0 yields NULL.
  * Collective over the parent. */

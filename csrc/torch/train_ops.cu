@@ -1,0 +1,472 @@
+// Fused element-wise / normalisation / loss / optimiser kernels of the
+// training step (GPT-2-style decoder, bf16 activations, fp32 arithmetic).
+// The reference library has no model code at all; these kernels exist so
+// that the data-parallel benchmark spends its non-GEMM time in a handful of
+// bandwidth-bound passes instead of dozens of eager element-wise launches.
+//
+// All kernels are plain sm_100a CUDA C++: 16-byte vector accesses, one warp
+// per row for the row-wise ops, grid sized as a multiple of the SM count.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <algorithm>
+
+#include "train_ops.h"
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+
+__device__ __forceinline__ float warpSum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warpMax(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+struct alignas(16) Bf8 { bf16 v[8]; };
+
+__device__ __forceinline__ void unpack8(const Bf8 &p, float *f) {
+#pragma unroll
+  for (int i = 0; i < 8; i++) f[i] = __bfloat162float(p.v[i]);
+}
+__device__ __forceinline__ Bf8 pack8(const float *f) {
+  Bf8 p;
+#pragma unroll
+  for (int i = 0; i < 8; i++) p.v[i] = __float2bfloat16_rn(f[i]);
+  return p;
+}
+
+// ---------------------------------------------------------------- LayerNorm
+// One warp per row; C is a multiple of 256 and at most 256*MAXV, so each lane
+// keeps its C/32 values in registers between the statistics and the output.
+template <int MAXV>
+__global__ void __launch_bounds__(256) lnFwdKernel(const bf16 *__restrict__ x, const bf16 *__restrict__ delta,
+                                                   const bf16 *__restrict__ gamma, const bf16 *__restrict__ beta,
+                                                   bf16 *__restrict__ resOut, bf16 *__restrict__ y, float *__restrict__ mean,
+                                                   float *__restrict__ rstd, int M, int C, float eps) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const int nv = C / 256;  // 16-byte vectors per lane
+  for (int row = warp; row < M; row += nwarps) {
+    const Bf8 *xr = (const Bf8 *)(x + (size_t)row * C);
+    const Bf8 *dr = delta ? (const Bf8 *)(delta + (size_t)row * C) : nullptr;
+    float v[MAXV][8];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; i++)
+      if (i < nv) {
+        unpack8(xr[i * 32 + lane], v[i]);
+        if (dr) {
+          float d[8];
+          unpack8(dr[i * 32 + lane], d);
+#pragma unroll
+          for (int k = 0; k < 8; k++) v[i][k] += d[k];
+          // the residual stream is kept in bf16: round it here so that the
+          // statistics see what the next layer will read
+          Bf8 r = pack8(v[i]);
+          ((Bf8 *)(resOut + (size_t)row * C))[i * 32 + lane] = r;
+          unpack8(r, v[i]);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; k++) s += v[i][k];
+      }
+    const float mu = warpSum(s) / C;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; i++)
+      if (i < nv) {
+#pragma unroll
+        for (int k = 0; k < 8; k++) { float d = v[i][k] - mu; q += d * d; }
+      }
+    const float rs = rsqrtf(warpSum(q) / C + eps);
+    if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
+#pragma unroll
+    for (int i = 0; i < MAXV; i++)
+      if (i < nv) {
+        float g[8], b[8], o[8];
+        unpack8(((const Bf8 *)gamma)[i * 32 + lane], g);
+        unpack8(((const Bf8 *)beta)[i * 32 + lane], b);
+#pragma unroll
+        for (int k = 0; k < 8; k++) o[k] = (v[i][k] - mu) * rs * g[k] + b[k];
+        ((Bf8 *)(y + (size_t)row * C))[i * 32 + lane] = pack8(o);
+      }
+  }
+}
+
+// Backward: dx = rstd * (g*dy - mean(g*dy) - xhat * mean(g*dy*xhat)) [+ dres];
+// per-CTA partial sums of dgamma/dbeta go to `partial` ([gridDim.x][2][C],
+// fp32 scratch) and are folded by lnBwdReduceKernel.
+template <int MAXV>
+__global__ void __launch_bounds__(256) lnBwdKernel(const bf16 *__restrict__ dy, const bf16 *__restrict__ x,
+                                                   const bf16 *__restrict__ gamma, const float *__restrict__ mean,
+                                                   const float *__restrict__ rstd, const bf16 *__restrict__ dres,
+                                                   bf16 *__restrict__ dx, float *__restrict__ partial, int M, int C) {
+  extern __shared__ float sm[];  // [2][C] accumulators of this CTA
+  for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) sm[i] = 0.f;
+  __syncthreads();
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const int nv = C / 256;
+  float dg[MAXV][8], db[MAXV][8];
+#pragma unroll
+  for (int i = 0; i < MAXV; i++)
+#pragma unroll
+    for (int k = 0; k < 8; k++) dg[i][k] = db[i][k] = 0.f;
+  for (int row = warp; row < M; row += nwarps) {
+    const float mu = mean[row], rs = rstd[row];
+    float gy[MAXV][8], xh[MAXV][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; i++)
+      if (i < nv) {
+        float d[8], xv[8], g[8];
+        unpack8(((const Bf8 *)(dy + (size_t)row * C))[i * 32 + lane], d);
+        unpack8(((const Bf8 *)(x + (size_t)row * C))[i * 32 + lane], xv);
+        unpack8(((const Bf8 *)gamma)[i * 32 + lane], g);
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+          xh[i][k] = (xv[k] - mu) * rs;
+          gy[i][k] = g[k] * d[k];
+          s1 += gy[i][k];
+          s2 += gy[i][k] * xh[i][k];
+          dg[i][k] += d[k] * xh[i][k];
+          db[i][k] += d[k];
+        }
+      }
+    s1 = warpSum(s1) / C;
+    s2 = warpSum(s2) / C;
+#pragma unroll
+    for (int i = 0; i < MAXV; i++)
+      if (i < nv) {
+        float o[8];
+        if (dres) unpack8(((const Bf8 *)(dres + (size_t)row * C))[i * 32 + lane], o);
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+          float t = rs * (gy[i][k] - s1 - xh[i][k] * s2);
+          o[k] = dres ? o[k] + t : t;
+        }
+        ((Bf8 *)(dx + (size_t)row * C))[i * 32 + lane] = pack8(o);
+      }
+  }
+#pragma unroll
+  for (int i = 0; i < MAXV; i++)
+    if (i < nv) {
+#pragma unroll
+      for (int k = 0; k < 8; k++) {
+        int c = (i * 32 + lane) * 8 + k;
+        atomicAdd(&sm[c], dg[i][k]);
+        atomicAdd(&sm[C + c], db[i][k]);
+      }
+    }
+  __syncthreads();
+  float *out = partial + (size_t)blockIdx.x * 2 * C;
+  for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) out[i] = sm[i];
+}
+
+__global__ void lnBwdReduceKernel(const float *__restrict__ partial, int nparts, int C, bf16 *__restrict__ dgamma,
+                                  bf16 *__restrict__ dbeta, int accumulate) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= 2 * C) return;
+  float s = 0.f;
+  for (int p = 0; p < nparts; p++) s += partial[(size_t)p * 2 * C + c];
+  bf16 *dst = c < C ? dgamma + c : dbeta + (c - C);
+  if (accumulate) s += __bfloat162float(*dst);
+  *dst = __float2bfloat16_rn(s);
+}
+
+// ---------------------------------------------------------------- bias + GELU (tanh form)
+__device__ __forceinline__ float geluF(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  return 0.5f * x * (1.f + tanhf(k0 * (x + k1 * x * x * x)));
+}
+__device__ __forceinline__ float geluGrad(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float u = k0 * (x + k1 * x * x * x), t = tanhf(u);
+  return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * k0 * (1.f + 3.f * k1 * x * x);
+}
+
+// y = gelu(x + bias); x is [M, C]
+__global__ void __launch_bounds__(256) biasGeluFwdKernel(const bf16 *__restrict__ x, const bf16 *__restrict__ bias,
+                                                         bf16 *__restrict__ y, size_t nvec, int C) {
+  const int cv = C / 8;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+    float a[8], b[8];
+    unpack8(((const Bf8 *)x)[i], a);
+    unpack8(((const Bf8 *)bias)[i % cv], b);
+#pragma unroll
+    for (int k = 0; k < 8; k++) a[k] = geluF(a[k] + b[k]);
+    ((Bf8 *)y)[i] = pack8(a);
+  }
+}
+
+// dx = dy * gelu'(x + bias)
+__global__ void __launch_bounds__(256) biasGeluBwdKernel(const bf16 *__restrict__ dy, const bf16 *__restrict__ x,
+                                                         const bf16 *__restrict__ bias, bf16 *__restrict__ dx, size_t nvec, int C) {
+  const int cv = C / 8;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+    float a[8], b[8], d[8];
+    unpack8(((const Bf8 *)x)[i], a);
+    unpack8(((const Bf8 *)bias)[i % cv], b);
+    unpack8(((const Bf8 *)dy)[i], d);
+#pragma unroll
+    for (int k = 0; k < 8; k++) d[k] *= geluGrad(a[k] + b[k]);
+    ((Bf8 *)dx)[i] = pack8(d);
+  }
+}
+
+// Column sums of a [M, C] bf16 matrix (bias gradients).  Each CTA owns 64
+// columns and a slice of rows; partials go to fp32 scratch [gridDim.y][C].
+__global__ void __launch_bounds__(256) colSumKernel(const bf16 *__restrict__ a, float *__restrict__ partial, int M, int C) {
+  const int col0 = blockIdx.x * 64;
+  const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;  // 8 vector columns x 32 row lanes
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  const int rowsPer = (M + gridDim.y - 1) / gridDim.y;
+  const int r0 = blockIdx.y * rowsPer, r1 = min(M, r0 + rowsPer);
+  for (int r = r0 + ty; r < r1; r += 32) {
+    float v[8];
+    unpack8(*(const Bf8 *)(a + (size_t)r * C + col0 + tx * 8), v);
+#pragma unroll
+    for (int k = 0; k < 8; k++) acc[k] += v[k];
+  }
+  // reduce over the 32 row lanes: lanes with equal tx live in different warps, go through shared memory
+  __shared__ float red[32][64 + 1];
+#pragma unroll
+  for (int k = 0; k < 8; k++) red[ty][tx * 8 + k] = acc[k];
+  __syncthreads();
+  if (threadIdx.x < 64) {
+    float s = 0.f;
+#pragma unroll 8
+    for (int j = 0; j < 32; j++) s += red[j][threadIdx.x];
+    partial[(size_t)blockIdx.y * C + col0 + threadIdx.x] = s;
+  }
+}
+
+__global__ void colSumReduceKernel(const float *__restrict__ partial, int nparts, int C, bf16 *__restrict__ out, int accumulate) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float s = 0.f;
+  for (int p = 0; p < nparts; p++) s += partial[(size_t)p * C + c];
+  if (accumulate) s += __bfloat162float(out[c]);
+  out[c] = __float2bfloat16_rn(s);
+}
+
+// ---------------------------------------------------------------- softmax cross-entropy
+// One CTA per row of logits [M, Vpad] (V valid columns).  Writes the loss of
+// the row and overwrites the logits with (softmax - onehot) * gradScale.
+__global__ void __launch_bounds__(1024) ceFwdBwdKernel(bf16 *__restrict__ logits, const int64_t *__restrict__ targets,
+                                                       float *__restrict__ losses, int V, int Vpad, float gradScale) {
+  __shared__ float red[32];
+  __shared__ float bcast;
+  const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5, nw = blockDim.x >> 5;
+  bf16 *lr = logits + (size_t)row * Vpad;
+  const int nvec = V / 8;
+  const int tgt = (int)targets[row];
+  // read before anything in the row is overwritten by the gradient pass
+  const float tgtLogit = (tgt >= 0 && tgt < V) ? __bfloat162float(lr[tgt]) : 0.f;
+  float mx = -INFINITY;
+  for (int i = tid; i < nvec; i += blockDim.x) {
+    float v[8];
+    unpack8(((const Bf8 *)lr)[i], v);
+#pragma unroll
+    for (int k = 0; k < 8; k++) mx = fmaxf(mx, v[k]);
+  }
+  for (int i = nvec * 8 + tid; i < V; i += blockDim.x) mx = fmaxf(mx, __bfloat162float(lr[i]));
+  mx = warpMax(mx);
+  if (lane == 0) red[wid] = mx;
+  __syncthreads();
+  if (wid == 0) {
+    float v = lane < nw ? red[lane] : -INFINITY;
+    v = warpMax(v);
+    if (lane == 0) bcast = v;
+  }
+  __syncthreads();
+  mx = bcast;
+  float sum = 0.f;
+  for (int i = tid; i < nvec; i += blockDim.x) {
+    float v[8];
+    unpack8(((const Bf8 *)lr)[i], v);
+#pragma unroll
+    for (int k = 0; k < 8; k++) sum += __expf(v[k] - mx);
+  }
+  for (int i = nvec * 8 + tid; i < V; i += blockDim.x) sum += __expf(__bfloat162float(lr[i]) - mx);
+  sum = warpSum(sum);
+  __syncthreads();
+  if (lane == 0) red[wid] = sum;
+  __syncthreads();
+  if (wid == 0) {
+    float v = lane < nw ? red[lane] : 0.f;
+    v = warpSum(v);
+    if (lane == 0) bcast = v;
+  }
+  __syncthreads();
+  sum = bcast;
+  const float inv = 1.f / sum;
+  if (tid == 0) losses[row] = tgt >= 0 ? (logf(sum) + mx - tgtLogit) : 0.f;
+  const float gs = tgt >= 0 ? gradScale : 0.f;
+  for (int i = tid; i < nvec; i += blockDim.x) {
+    float v[8];
+    unpack8(((const Bf8 *)lr)[i], v);
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+      float p = __expf(v[k] - mx) * inv;
+      v[k] = (p - ((i * 8 + k) == tgt ? 1.f : 0.f)) * gs;
+    }
+    ((Bf8 *)lr)[i] = pack8(v);
+  }
+  for (int i = nvec * 8 + tid; i < Vpad; i += blockDim.x) {
+    float g = 0.f;
+    if (i < V) g = (__expf(__bfloat162float(lr[i]) - mx) * inv - (i == tgt ? 1.f : 0.f)) * gs;
+    lr[i] = __float2bfloat16_rn(g);
+  }
+}
+
+// ---------------------------------------------------------------- AdamW on flat buffers
+// master (fp32) is the truth; param (bf16) is refreshed from it.  The gradient
+// is read once and cleared, so no separate zero_grad pass is needed.
+__global__ void __launch_bounds__(256) adamwKernel(float *__restrict__ master, bf16 *__restrict__ param, bf16 *__restrict__ grad,
+                                                   float *__restrict__ m, float *__restrict__ v, size_t n, float lr, float b1,
+                                                   float b2, float eps, float wd, float bc1, float bc2, float gradScale,
+                                                   int zeroGrad) {
+  const size_t nvec = n / 8;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+    float g[8];
+    unpack8(((const Bf8 *)grad)[i], g);
+    float4 w0 = ((float4 *)master)[2 * i], w1 = ((float4 *)master)[2 * i + 1];
+    float4 m0 = ((float4 *)m)[2 * i], m1 = ((float4 *)m)[2 * i + 1];
+    float4 v0 = ((float4 *)v)[2 * i], v1 = ((float4 *)v)[2 * i + 1];
+    float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+    float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+      float gk = g[k] * gradScale;
+      mm[k] = b1 * mm[k] + (1.f - b1) * gk;
+      vv[k] = b2 * vv[k] + (1.f - b2) * gk * gk;
+      float upd = (mm[k] / bc1) / (sqrtf(vv[k] / bc2) + eps);
+      w[k] = w[k] - lr * (upd + wd * w[k]);
+    }
+    ((float4 *)master)[2 * i] = make_float4(w[0], w[1], w[2], w[3]);
+    ((float4 *)master)[2 * i + 1] = make_float4(w[4], w[5], w[6], w[7]);
+    ((float4 *)m)[2 * i] = make_float4(mm[0], mm[1], mm[2], mm[3]);
+    ((float4 *)m)[2 * i + 1] = make_float4(mm[4], mm[5], mm[6], mm[7]);
+    ((float4 *)v)[2 * i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    ((float4 *)v)[2 * i + 1] = make_float4(vv[4], vv[5], vv[6], vv[7]);
+    ((Bf8 *)param)[i] = pack8(w);
+    if (zeroGrad) {
+      Bf8 z;
+#pragma unroll
+      for (int k = 0; k < 8; k++) z.v[k] = __float2bfloat16_rn(0.f);
+      ((Bf8 *)grad)[i] = z;
+    }
+  }
+  // tail (n not a multiple of 8)
+  if (blockIdx.x == 0) {
+    for (size_t i = nvec * 8 + threadIdx.x; i < n; i += blockDim.x) {
+      float gk = __bfloat162float(grad[i]) * gradScale;
+      float mk = b1 * m[i] + (1.f - b1) * gk, vk = b2 * v[i] + (1.f - b2) * gk * gk;
+      float wk = master[i];
+      wk = wk - lr * ((mk / bc1) / (sqrtf(vk / bc2) + eps) + wd * wk);
+      m[i] = mk; v[i] = vk; master[i] = wk;
+      param[i] = __float2bfloat16_rn(wk);
+      if (zeroGrad) grad[i] = __float2bfloat16_rn(0.f);
+    }
+  }
+}
+
+int smCount() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------- launchers
+
+extern "C" {
+
+int fcxLnPartials(int M) { return min(smCount() * 2, (M + 7) / 8); }
+
+cudaError_t fcxLayerNormFwd(const void *x, const void *delta, const void *gamma, const void *beta, void *resOut, void *y,
+                            float *mean, float *rstd, int M, int C, float eps, cudaStream_t s) {
+  if (C % 256 != 0 || C > 256 * 8) return cudaErrorInvalidValue;
+  int grid = min(smCount() * 4, (M + 7) / 8);
+  if (C <= 1024)
+    lnFwdKernel<4><<<grid, 256, 0, s>>>((const bf16 *)x, (const bf16 *)delta, (const bf16 *)gamma, (const bf16 *)beta,
+                                        (bf16 *)resOut, (bf16 *)y, mean, rstd, M, C, eps);
+  else
+    lnFwdKernel<8><<<grid, 256, 0, s>>>((const bf16 *)x, (const bf16 *)delta, (const bf16 *)gamma, (const bf16 *)beta,
+                                        (bf16 *)resOut, (bf16 *)y, mean, rstd, M, C, eps);
+  return cudaGetLastError();
+}
+
+// `partial` must hold fcxLnPartials(M) * 2 * C floats.
+cudaError_t fcxLayerNormBwd(const void *dy, const void *x, const void *gamma, const float *mean, const float *rstd,
+                            const void *dres, void *dx, void *dgamma, void *dbeta, float *partial, int M, int C, int accumulate,
+                            cudaStream_t s) {
+  if (C % 256 != 0 || C > 256 * 8) return cudaErrorInvalidValue;
+  int grid = fcxLnPartials(M);
+  size_t smem = 2 * (size_t)C * sizeof(float);
+  if (C <= 1024)
+    lnBwdKernel<4><<<grid, 256, smem, s>>>((const bf16 *)dy, (const bf16 *)x, (const bf16 *)gamma, mean, rstd, (const bf16 *)dres,
+                                           (bf16 *)dx, partial, M, C);
+  else
+    lnBwdKernel<8><<<grid, 256, smem, s>>>((const bf16 *)dy, (const bf16 *)x, (const bf16 *)gamma, mean, rstd, (const bf16 *)dres,
+                                           (bf16 *)dx, partial, M, C);
+  lnBwdReduceKernel<<<(2 * C + 255) / 256, 256, 0, s>>>(partial, grid, C, (bf16 *)dgamma, (bf16 *)dbeta, accumulate);
+  return cudaGetLastError();
+}
+
+cudaError_t fcxBiasGeluFwd(const void *x, const void *bias, void *y, size_t M, int C, cudaStream_t s) {
+  if (C % 8 != 0) return cudaErrorInvalidValue;
+  size_t nvec = M * C / 8;
+  int grid = (int)std::min<size_t>((nvec + 255) / 256, (size_t)smCount() * 8);
+  biasGeluFwdKernel<<<grid, 256, 0, s>>>((const bf16 *)x, (const bf16 *)bias, (bf16 *)y, nvec, C);
+  return cudaGetLastError();
+}
+
+cudaError_t fcxBiasGeluBwd(const void *dy, const void *x, const void *bias, void *dx, size_t M, int C, cudaStream_t s) {
+  if (C % 8 != 0) return cudaErrorInvalidValue;
+  size_t nvec = M * C / 8;
+  int grid = (int)std::min<size_t>((nvec + 255) / 256, (size_t)smCount() * 8);
+  biasGeluBwdKernel<<<grid, 256, 0, s>>>((const bf16 *)dy, (const bf16 *)x, (const bf16 *)bias, (bf16 *)dx, nvec, C);
+  return cudaGetLastError();
+}
+
+int fcxColSumPartials(int M) { return max(1, min(32, M / 256)); }
+
+// `partial` must hold fcxColSumPartials(M) * C floats.
+cudaError_t fcxColSum(const void *a, void *out, float *partial, int M, int C, int accumulate, cudaStream_t s) {
+  if (C % 64 != 0) return cudaErrorInvalidValue;
+  int parts = fcxColSumPartials(M);
+  colSumKernel<<<dim3(C / 64, parts), 256, 0, s>>>((const bf16 *)a, partial, M, C);
+  colSumReduceKernel<<<(C + 255) / 256, 256, 0, s>>>(partial, parts, C, (bf16 *)out, accumulate);
+  return cudaGetLastError();
+}
+
+cudaError_t fcxCrossEntropyFwdBwd(void *logits, const int64_t *targets, float *losses, int M, int V, int Vpad, float gradScale,
+                                  cudaStream_t s) {
+  if (Vpad % 8 != 0 || V > Vpad) return cudaErrorInvalidValue;
+  ceFwdBwdKernel<<<M, 1024, 0, s>>>((bf16 *)logits, targets, losses, V, Vpad, gradScale);
+  return cudaGetLastError();
+}
+
+cudaError_t fcxAdamW(float *master, void *param, void *grad, float *m, float *v, size_t n, float lr, float b1, float b2, float eps,
+                     float wd, int step, float gradScale, int zeroGrad, cudaStream_t s) {
+  float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
+  int grid = (int)std::min<size_t>((n / 8 + 255) / 256 + 1, (size_t)smCount() * 8);
+  adamwKernel<<<grid, 256, 0, s>>>(master, (bf16 *)param, (bf16 *)grad, m, v, n, lr, b1, b2, eps, wd, bc1, bc2, gradScale, zeroGrad);
+  return cudaGetLastError();
+}
+
+}  // extern "C"

@@ -1,0 +1,116 @@
+"""The "flagcx" ProcessGroup backend exercised with CPU tensors (TCP host
+path), world_size 2, mirroring the op list of the reference's API example
+(plugin/torch/example/example.py:81-331) but with assertions."""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _worker(rank, world, port, q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), FLAGCX_SOCKET_IFNAME="lo")
+        import flagcx  # noqa: F401
+        dist.init_process_group("flagcx", rank=rank, world_size=world)
+        out = {}
+        t = torch.full((1000,), float(rank + 1))
+        dist.all_reduce(t)
+        out["allreduce"] = bool((t == sum(range(1, world + 1))).all())
+        t = torch.full((10,), float(rank))
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out["max"] = bool((t == world - 1).all())
+        b = torch.arange(8.0) if rank == 1 else torch.zeros(8)
+        dist.broadcast(b, src=1)
+        out["broadcast"] = bool((b == torch.arange(8.0)).all())
+        r = torch.full((4,), float(rank + 1))
+        dist.reduce(r, dst=0)
+        if rank == 0:
+            out["reduce"] = bool((r == sum(range(1, world + 1))).all())
+        outs = [torch.zeros(3) for _ in range(world)]
+        dist.all_gather(outs, torch.full((3,), float(rank)))
+        out["allgather"] = all(bool((outs[p] == p).all()) for p in range(world))
+        flat = torch.zeros(3 * world)
+        dist.all_gather_into_tensor(flat, torch.full((3,), float(rank)))
+        out["allgather_base"] = bool((flat.view(world, 3)[:, 0] == torch.arange(float(world))).all())
+        rs = torch.zeros(2)
+        dist.reduce_scatter(rs, [torch.full((2,), float(p + rank)) for p in range(world)])
+        out["reducescatter"] = bool((rs == sum(rank + q for q in range(world))).all())
+        rsb = torch.zeros(2)
+        dist.reduce_scatter_tensor(rsb, torch.arange(2.0 * world))
+        out["reducescatter_base"] = bool((rsb == world * torch.arange(2.0 * world)[rank * 2:(rank + 1) * 2]).all())
+        g = [torch.zeros(2) for _ in range(world)] if rank == 0 else None
+        dist.gather(torch.full((2,), float(rank)), g, dst=0)
+        if rank == 0:
+            out["gather"] = all(bool((g[p] == p).all()) for p in range(world))
+        s = torch.zeros(2)
+        dist.scatter(s, [torch.full((2,), float(p * 10)) for p in range(world)] if rank == 0 else None, src=0)
+        out["scatter"] = bool((s == rank * 10).all())
+        a2a_out = torch.zeros(2 * world)
+        dist.all_to_all_single(a2a_out, torch.arange(2.0 * world) + 100 * rank)
+        exp = torch.cat([torch.arange(2.0 * world)[rank * 2:(rank + 1) * 2] + 100 * p for p in range(world)])
+        out["alltoall_single"] = bool((a2a_out == exp).all())
+        # uneven splits: rank r sends r+1 rows to everybody
+        inp = torch.full(((rank + 1) * world, 2), float(rank))
+        outp = torch.zeros(sum(p + 1 for p in range(world)), 2)
+        dist.all_to_all_single(outp, inp, output_split_sizes=[p + 1 for p in range(world)], input_split_sizes=[rank + 1] * world)
+        exp = torch.cat([torch.full((p + 1, 2), float(p)) for p in range(world)])
+        out["alltoall_splits"] = bool((outp == exp).all())
+        outs = [torch.zeros(2) for _ in range(world)]
+        dist.all_to_all(outs, [torch.full((2,), float(rank * 10 + p)) for p in range(world)])
+        out["alltoall_list"] = all(bool((outs[p] == p * 10 + rank).all()) for p in range(world))
+        # point to point: blocking, async and batched
+        nxt, prv = (rank + 1) % world, (rank - 1) % world
+        if rank % 2 == 0:
+            dist.send(torch.full((5,), float(rank)), nxt)
+            rcv = torch.zeros(5)
+            dist.recv(rcv, prv)
+        else:
+            rcv = torch.zeros(5)
+            dist.recv(rcv, prv)
+            dist.send(torch.full((5,), float(rank)), nxt)
+        out["sendrecv"] = bool((rcv == prv).all())
+        rcv = torch.zeros(1 << 18)
+        ops = [dist.P2POp(dist.isend, torch.full((1 << 18,), float(rank)), nxt), dist.P2POp(dist.irecv, rcv, prv)]
+        for w in dist.batch_isend_irecv(ops):
+            w.wait()
+        out["batch_isend_irecv"] = bool((rcv == prv).all())
+        w = dist.all_reduce(torch.ones(3), async_op=True)
+        w.wait()
+        out["async"] = w.is_completed()
+        dist.barrier()
+        obj = [None] * world
+        dist.all_gather_object(obj, {"rank": rank})
+        out["object"] = [o["rank"] for o in obj] == list(range(world))
+        dist.destroy_process_group()
+        q.put((rank, "ok", out))
+    except BaseException as e:  # noqa
+        import traceback
+        q.put((rank, "err", traceback.format_exc()))
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_backend_cpu(native_lib, world):
+    from flagcx_b200 import _build
+    _build.build_torch_ext()
+    import socket
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = {}
+    for _ in range(world):
+        rank, status, out = q.get(timeout=180)
+        res[rank] = (status, out)
+    for p in procs:
+        p.join(timeout=20)
+    for r in range(world):
+        assert res[r][0] == "ok", res[r][1]
+        for k, v in res[r][1].items():
+            assert v, (r, k)
