@@ -115,16 +115,16 @@ __device__ __forceinline__ uint4 llLoad(const char *line) {
 }
 
 template <typename T>
-__device__ void arLL(const FcxDevComm &dc, const FcxCollArgs &a, int cta, int nctas) {
+__device__ void arLL(const FcxDevComm &dc, const FcxCollArgs &a, uint64_t seq, int cta, int nctas) {
   using Acc = typename Elem<T>::Acc;
   constexpr int G = 16 / (int)sizeof(T);
   const int n = dc.nranks, me = dc.rank;
-  const uint32_t tag = (uint32_t)a.seq;
+  const uint32_t tag = (uint32_t)seq;
   const size_t gtid = (size_t)cta * blockDim.x + threadIdx.x, gstride = (size_t)nctas * blockDim.x;
   const size_t nunits = (a.count + G - 1) / G;
   const char *send = (const char *)a.send;
   const bool alS = aligned16(send), alR = aligned16(a.recv);
-  const size_t llOff = FCX_OFF_LL + (size_t)(a.seq & 1) * FCX_MAX_RANKS * FCX_LL_SLOT_BYTES;
+  const size_t llOff = FCX_OFF_LL + (size_t)(seq & 1) * FCX_MAX_RANKS * FCX_LL_SLOT_BYTES;
   bool ok = true;
   for (size_t u = gtid; u < nunits; u += gstride) {
     int nv = (int)min((size_t)G, a.count - u * G);
@@ -158,12 +158,12 @@ __device__ void arLL(const FcxDevComm &dc, const FcxCollArgs &a, int cta, int nc
             if ((++spins & 63u) == 0u) {
               if (*(volatile unsigned int *)&localOf(dc)->abortSeen) { ok = false; break; }
               if (globalTimerNs() - t0 > dc.timeoutNs) {
-                giveUp(dc, FCX_ERR_TIMEOUT, p, FCX_WAIT_LL, cta, tag, lo.y, a.seq);
+                giveUp(dc, FCX_ERR_TIMEOUT, p, FCX_WAIT_LL, cta, tag, lo.y, seq);
                 ok = false;
                 break;
               }
               if ((spins & 1023u) == 0u && *dc.abortWord) {
-                giveUp(dc, FCX_ERR_ABORT, p, FCX_WAIT_LL, cta, tag, lo.y, a.seq);
+                giveUp(dc, FCX_ERR_ABORT, p, FCX_WAIT_LL, cta, tag, lo.y, seq);
                 ok = false;
                 break;
               }
@@ -261,7 +261,7 @@ __device__ void fcxCollBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta,
   constexpr int G = 16 / (ESI < ESO ? ESI : ESO);
   constexpr int INB = G * ESI, OUTB = G * ESO;
   const int n = dc.nranks, me = dc.rank;
-  const uint64_t seq = a.seq;
+  const uint64_t seq = nextSeq(dc);
   const size_t gtid = (size_t)cta * blockDim.x + threadIdx.x, gstride = (size_t)nctas * blockDim.x;
 
   if (!prologue(dc, seq, cta)) return;
@@ -276,7 +276,7 @@ __device__ void fcxCollBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta,
     }
 
     case FCX_K_AR_LL: {
-      if constexpr (ESI == ESO) arLL<TIn>(dc, a, cta, nctas);
+      if constexpr (ESI == ESO) arLL<TIn>(dc, a, seq, cta, nctas);
       break;
     }
 
@@ -453,7 +453,7 @@ __device__ void fcxCollBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta,
 // Byte-moving collectives need no element type.
 __device__ void fcxMoveBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta, int nctas) {
   const int n = dc.nranks, me = dc.rank;
-  const uint64_t seq = a.seq;
+  const uint64_t seq = nextSeq(dc);
   const size_t gtid = (size_t)cta * blockDim.x + threadIdx.x, gstride = (size_t)nctas * blockDim.x;
   const size_t es = a.elemSize;
   if (!prologue(dc, seq, cta)) return;

@@ -108,7 +108,7 @@ struct FcxCollArgs {
   int useMc;             // broadcast: root stores through the multicast alias
   int outDtype;          // all-reduce with fused cast: element type of recv (== dtype when unused)
   float scale;           // multiplied into the result before the final rounding (1 = off)
-  uint64_t seq;          // collective sequence number of this communicator
+  uint64_t seq;          // unused by the kernels (they count in device memory); kept for logs
   const void *send;
   void *recv;
   size_t count;          // elements of the piece handled by this launch (per-rank piece for AG/RS/A2A/gather/scatter)

@@ -39,6 +39,7 @@ struct FcxLocal {
   unsigned int errClaim;       // first waiter to give up owns the host error record
   unsigned int abortSeen;      // set once any waiter gave up; later waits leave at once
   unsigned int pad;
+  unsigned long long seq;      // collectives completed by this rank; the next one runs as seq + 1
   unsigned int opCount[FCX_MAX_GROUP_OPS][2];  // arrivals per grouped p2p op and staging slot
 };
 
@@ -116,6 +117,13 @@ __device__ __forceinline__ bool ctaBarrier(const FcxDevComm &dc, int cta, uint64
 
 __device__ __forceinline__ uint64_t barrierValue(uint64_t seq, unsigned phase) { return (seq << 16) | phase; }
 
+// The sequence number of the collective that is starting.  It lives in device
+// memory (not in the launch arguments) so that a captured CUDA graph can be
+// replayed: every replay advances it exactly as a fresh launch would.
+__device__ __forceinline__ uint64_t nextSeq(const FcxDevComm &dc) {
+  return *(volatile unsigned long long *)&localOf(dc)->seq + 1;
+}
+
 // Before writing into a peer's parity-selected buffers for collective `seq`,
 // the peer must have finished collective seq-2 (which used the same parity).
 __device__ __forceinline__ bool prologue(const FcxDevComm &dc, uint64_t seq, int cta) {
@@ -138,7 +146,10 @@ __device__ __forceinline__ void epilogue(const FcxDevComm &dc, uint64_t seq, int
     __threadfence();
     unsigned int old = atomicAdd(&localOf(dc)->ctaDone, 1u);
     last = (old == (unsigned)nctas - 1u);
-    if (last) localOf(dc)->ctaDone = 0;
+    if (last) {
+      localOf(dc)->ctaDone = 0;
+      localOf(dc)->seq = seq;
+    }
   }
   __syncthreads();
   if (last && threadIdx.x < dc.nranks && threadIdx.x != dc.rank) {

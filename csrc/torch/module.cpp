@@ -4,6 +4,8 @@
 #include <pybind11/chrono.h>
 #include <torch/extension.h>
 
+#include "flagcx.h"
+#include "flagcx_ext.h"
 #include "train_ops.h"
 
 namespace fcxt {
@@ -109,7 +111,7 @@ static at::Tensor crossEntropy(at::Tensor &logits, const at::Tensor &targets, in
 }
 
 static void adamw(at::Tensor &master, at::Tensor &param, at::Tensor &grad, at::Tensor &m, at::Tensor &v, double lr, double b1, double b2,
-                  double eps, double wd, int64_t step, double gradScale, bool zeroGrad) {
+                  double eps, double wd, int64_t step, double gradScale, bool zeroGrad, const c10::optional<at::Tensor> &stepDev) {
   TORCH_CHECK(master.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat, "fp32 state");
   checkBf16(param, "param");
   checkBf16(grad, "grad");
@@ -117,7 +119,90 @@ static void adamw(at::Tensor &master, at::Tensor &param, at::Tensor &grad, at::T
   size_t n = master.numel();
   TORCH_CHECK((size_t)param.numel() == n && (size_t)grad.numel() == n && (size_t)m.numel() == n && (size_t)v.numel() == n, "size mismatch");
   CUDA_OK(fcxAdamW(master.data_ptr<float>(), param.data_ptr(), grad.data_ptr(), m.data_ptr<float>(), v.data_ptr<float>(), n, (float)lr,
-                   (float)b1, (float)b2, (float)eps, (float)wd, (int)step, (float)gradScale, zeroGrad ? 1 : 0, cur()));
+                   (float)b1, (float)b2, (float)eps, (float)wd, (int)step, (float)gradScale, zeroGrad ? 1 : 0,
+                   stepDev.has_value() && stepDev->defined() ? stepDev->data_ptr<int>() : nullptr, cur()));
+}
+
+// ---- direct access to a communicator from Python (raw flagcxComm_t as integer)
+
+struct StreamLayout { cudaStream_t base; };
+
+#define FCX_OK(call)                                                                                  \
+  do {                                                                                                \
+    flagcxResult_t _r = (call);                                                                       \
+    TORCH_CHECK(_r == flagcxSuccess, "flagcx: ", flagcxGetErrorString(_r), ": ", flagcxGetLastError(nullptr)); \
+  } while (0)
+
+static flagcxDataType_t dtypeOf(const at::Tensor &t) {
+  switch (t.scalar_type()) {
+    case at::kChar: return flagcxInt8;
+    case at::kByte: case at::kBool: return flagcxUint8;
+    case at::kInt: return flagcxInt32;
+    case at::kLong: return flagcxInt64;
+    case at::kHalf: return flagcxFloat16;
+    case at::kFloat: return flagcxFloat32;
+    case at::kDouble: return flagcxFloat64;
+    case at::kBFloat16: return flagcxBfloat16;
+    case at::kFloat8_e4m3fn: return flagcxFloat8e4m3;
+    case at::kFloat8_e5m2: return flagcxFloat8e5m2;
+    default: TORCH_CHECK(false, "unsupported dtype");
+  }
+}
+
+// A tensor whose storage lives in the communicator's symmetric heap.
+static at::Tensor heapTensor(uint64_t comm, std::vector<int64_t> sizes, at::ScalarType dtype) {
+  flagcxComm_t c = (flagcxComm_t)(uintptr_t)comm;
+  int64_t numel = 1;
+  for (auto s : sizes) numel *= s;
+  size_t bytes = (size_t)numel * c10::elementSize(dtype);
+  void *p = nullptr;
+  FCX_OK(flagcxMemAlloc(&p, std::max<size_t>(bytes, 16), c));
+  int dev = 0;
+  flagcxCommGetDeviceNumber(c, &dev);
+  return at::from_blob(p, sizes, [c](void *q) { flagcxMemFree(q, c); },
+                       at::TensorOptions().dtype(dtype).device(at::Device(at::kCUDA, (c10::DeviceIndex)dev)));
+}
+
+static void commAllReduce(uint64_t comm, const at::Tensor &send, at::Tensor &recv, int64_t op, double scale) {
+  flagcxComm_t c = (flagcxComm_t)(uintptr_t)comm;
+  StreamLayout st{cur()};
+  if (recv.scalar_type() != send.scalar_type() || scale != 1.0)
+    FCX_OK(flagcxAllReduceCast(send.data_ptr(), recv.data_ptr(), send.numel(), dtypeOf(send), dtypeOf(recv), (float)scale,
+                               (flagcxRedOp_t)op, c, (flagcxStream_t)&st));
+  else
+    FCX_OK(flagcxAllReduce(send.data_ptr(), recv.data_ptr(), send.numel(), dtypeOf(send), (flagcxRedOp_t)op, c, (flagcxStream_t)&st));
+}
+static void commAllGather(uint64_t comm, const at::Tensor &send, at::Tensor &recv) {
+  StreamLayout st{cur()};
+  FCX_OK(flagcxAllGather(send.data_ptr(), recv.data_ptr(), send.numel(), dtypeOf(send), (flagcxComm_t)(uintptr_t)comm, (flagcxStream_t)&st));
+}
+static void commReduceScatter(uint64_t comm, const at::Tensor &send, at::Tensor &recv, int64_t op) {
+  StreamLayout st{cur()};
+  FCX_OK(flagcxReduceScatter(send.data_ptr(), recv.data_ptr(), recv.numel(), dtypeOf(send), (flagcxRedOp_t)op,
+                             (flagcxComm_t)(uintptr_t)comm, (flagcxStream_t)&st));
+}
+static void commAlltoAll(uint64_t comm, const at::Tensor &send, at::Tensor &recv) {
+  flagcxComm_t c = (flagcxComm_t)(uintptr_t)comm;
+  int n = 1;
+  flagcxCommCount(c, &n);
+  StreamLayout st{cur()};
+  FCX_OK(flagcxAlltoAll(send.data_ptr(), recv.data_ptr(), send.numel() / n, dtypeOf(send), c, (flagcxStream_t)&st));
+}
+static void commBroadcast(uint64_t comm, at::Tensor &t, int64_t root) {
+  StreamLayout st{cur()};
+  FCX_OK(flagcxBroadcast(t.data_ptr(), t.data_ptr(), t.numel(), dtypeOf(t), (int)root, (flagcxComm_t)(uintptr_t)comm, (flagcxStream_t)&st));
+}
+static py::dict commCounters(uint64_t comm) {
+  flagcxCommCounters cc;
+  FCX_OK(flagcxCommGetCounters((flagcxComm_t)(uintptr_t)comm, &cc));
+  py::dict d;
+  d["launches"] = cc.launches;
+  py::list calls, kinds;
+  for (int i = 0; i < flagcxNumCommOps; i++) calls.append(cc.calls[i]);
+  for (int i = 0; i < 16; i++) kinds.append(cc.kindLaunches[i]);
+  d["calls"] = calls;
+  d["kind_launches"] = kinds;
+  return d;
 }
 
 }  // namespace fcxt
@@ -132,5 +217,14 @@ PYBIND11_MODULE(_flagcx_torch, m) {
   m.def("bias_gelu_bwd", &fcxt::biasGeluBwd);
   m.def("col_sum", &fcxt::colSum);
   m.def("cross_entropy_", &fcxt::crossEntropy);
-  m.def("adamw_", &fcxt::adamw);
+  m.def("adamw_", &fcxt::adamw, py::arg("master"), py::arg("param"), py::arg("grad"), py::arg("m"), py::arg("v"), py::arg("lr"),
+        py::arg("b1"), py::arg("b2"), py::arg("eps"), py::arg("wd"), py::arg("step"), py::arg("grad_scale"), py::arg("zero_grad"),
+        py::arg("step_dev") = py::none());
+  m.def("heap_tensor", &fcxt::heapTensor, "tensor allocated in the symmetric heap of a communicator");
+  m.def("comm_all_reduce", &fcxt::commAllReduce, py::arg("comm"), py::arg("send"), py::arg("recv"), py::arg("op") = 0, py::arg("scale") = 1.0);
+  m.def("comm_all_gather", &fcxt::commAllGather);
+  m.def("comm_reduce_scatter", &fcxt::commReduceScatter, py::arg("comm"), py::arg("send"), py::arg("recv"), py::arg("op") = 0);
+  m.def("comm_all_to_all", &fcxt::commAlltoAll);
+  m.def("comm_broadcast", &fcxt::commBroadcast);
+  m.def("comm_counters", &fcxt::commCounters);
 }

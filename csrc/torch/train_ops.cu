@@ -331,7 +331,13 @@ __global__ void __launch_bounds__(1024) ceFwdBwdKernel(bf16 *__restrict__ logits
 __global__ void __launch_bounds__(256) adamwKernel(float *__restrict__ master, bf16 *__restrict__ param, bf16 *__restrict__ grad,
                                                    float *__restrict__ m, float *__restrict__ v, size_t n, float lr, float b1,
                                                    float b2, float eps, float wd, float bc1, float bc2, float gradScale,
-                                                   int zeroGrad) {
+                                                   int zeroGrad, const int *__restrict__ stepDev) {
+  if (stepDev) {
+    // step counter kept on the device so that a captured graph stays exact
+    float st = (float)(*stepDev);
+    bc1 = 1.f - powf(b1, st);
+    bc2 = 1.f - powf(b2, st);
+  }
   const size_t nvec = n / 8;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
     float g[8];
@@ -462,10 +468,10 @@ cudaError_t fcxCrossEntropyFwdBwd(void *logits, const int64_t *targets, float *l
 }
 
 cudaError_t fcxAdamW(float *master, void *param, void *grad, float *m, float *v, size_t n, float lr, float b1, float b2, float eps,
-                     float wd, int step, float gradScale, int zeroGrad, cudaStream_t s) {
+                     float wd, int step, float gradScale, int zeroGrad, const int *stepDev, cudaStream_t s) {
   float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
   int grid = (int)std::min<size_t>((n / 8 + 255) / 256 + 1, (size_t)smCount() * 8);
-  adamwKernel<<<grid, 256, 0, s>>>(master, (bf16 *)param, (bf16 *)grad, m, v, n, lr, b1, b2, eps, wd, bc1, bc2, gradScale, zeroGrad);
+  adamwKernel<<<grid, 256, 0, s>>>(master, (bf16 *)param, (bf16 *)grad, m, v, n, lr, b1, b2, eps, wd, bc1, bc2, gradScale, zeroGrad, stepDev);
   return cudaGetLastError();
 }
 

@@ -21,7 +21,7 @@ cudaError_t fcxColSum(const void *a, void *out, float *partial, int M, int C, in
 cudaError_t fcxCrossEntropyFwdBwd(void *logits, const int64_t *targets, float *losses, int M, int V, int Vpad, float gradScale,
                                   cudaStream_t s);
 cudaError_t fcxAdamW(float *master, void *param, void *grad, float *m, float *v, size_t n, float lr, float b1, float b2, float eps,
-                     float wd, int step, float gradScale, int zeroGrad, cudaStream_t s);
+                     float wd, int step, float gradScale, int zeroGrad, const int *stepDev, cudaStream_t s);
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,5 @@
+"""Autograd wrappers over the fused sm_100a kernels of ``_flagcx_torch``.
+
+Every function here requires the native extension on a CUDA device and fails
+loudly when it is missing: there is no eager fallback."""
+from .fused import (add_layernorm, bias_gelu, cross_entropy, fused_adamw_step)  # noqa: F401

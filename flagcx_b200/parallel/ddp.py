@@ -1,0 +1,179 @@
+"""Data-parallel training engine.
+
+One process per GPU.  Parameters, gradients and optimizer state live in flat
+buffers; gradients are all-reduced in ~25 MB buckets as soon as the backward
+pass has finished writing a bucket, on a side stream, by the library's own
+NVLink kernels (average fused into the reduction); one fused AdamW kernel
+updates fp32 master weights and refreshes the bf16 parameters.  The whole
+step (forward, backward, bucket all-reduces, optimizer) is captured once in a
+CUDA graph and replayed, which removes the per-kernel launch cost of an
+eager step.  The collective kernels keep their sequence numbers in device
+memory, which is what makes them replayable.
+
+This is the framework's counterpart of running ``DistributedDataParallel``
+over the reference's process-group backend (plugin/torch/flagcx/src/backend_flagcx.cpp:505-532);
+that route is supported too (``torch_ddp=True``) and is what the c10d backend tests exercise.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+import flagcx_b200
+from flagcx_b200.models.gpt2 import flatten_parameters
+from flagcx_b200.ops import fused_adamw_step
+
+
+@dataclass
+class _Bucket:
+    start: int
+    end: int
+    nparams: int
+    pending: int = 0
+
+
+class DataParallelTrainer:
+    def __init__(self, model: torch.nn.Module, *, lr: float = 3e-4, betas=(0.9, 0.95), eps: float = 1e-8,
+                 weight_decay: float = 0.1, bucket_mb: float = 25.0, group=None, use_graph: bool = True,
+                 device: Optional[torch.device] = None):
+        self.model = model
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.native = flagcx_b200.native()
+        self.comm = 0
+        if self.world > 1:
+            self.comm = flagcx_b200.get_comm_handle(group, self.device)
+        self.lr, self.betas, self.eps, self.wd = lr, betas, eps, weight_decay
+        self.step_no = 0
+        self.launches_per_step = 0
+        self.step_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+        # ---- flat buffers
+        self.flat_params, self.specs = flatten_parameters(model, torch.bfloat16, self.device)
+        n = self.flat_params.numel()
+        if self.comm:
+            self.flat_grads = self.native.heap_tensor(self.comm, [n], torch.bfloat16)
+            self.flat_grads.zero_()
+        else:
+            self.flat_grads = torch.zeros(n, dtype=torch.bfloat16, device=self.device)
+        self.master = self.flat_params.float()
+        self.m = torch.zeros_like(self.master)
+        self.v = torch.zeros_like(self.master)
+        params = list(model.parameters())
+        for (name, off, cnt), p in zip(self.specs, params):
+            p.grad = self.flat_grads[off:off + cnt].view(p.shape)
+        if self.world > 1:
+            # all ranks start from rank 0's weights
+            self.native.comm_broadcast(self.comm, self.flat_params, 0)
+            self.master.copy_(self.flat_params)
+
+        # ---- buckets, built from the end of the buffer (gradients arrive roughly in reverse order)
+        self.buckets: List[_Bucket] = []
+        self.bucket_of = {}
+        if self.world > 1:
+            cap = int(bucket_mb * (1 << 20) / 2)
+            end = n
+            cur_params = []
+            for i in range(len(self.specs) - 1, -1, -1):
+                name, off, cnt = self.specs[i]
+                cur_params.append(i)
+                if end - off >= cap or i == 0:
+                    b = _Bucket(off, end, len(cur_params))
+                    for j in cur_params:
+                        self.bucket_of[j] = len(self.buckets)
+                    self.buckets.append(b)
+                    end = off
+                    cur_params = []
+            for i, p in enumerate(params):
+                p.register_post_accumulate_grad_hook(self._make_hook(i))
+            self.comm_stream = torch.cuda.Stream(device=self.device, priority=-1)
+            self.ready_event = torch.cuda.Event()
+            self.done_event = torch.cuda.Event()
+
+        self.use_graph = use_graph
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.static_tokens = None
+        self.static_targets = None
+        self.static_loss = None
+        self.eager_steps = 0
+
+    # ---- gradient bucket hooks
+    def _make_hook(self, idx):
+        def hook(_param):
+            b = self.buckets[self.bucket_of[idx]]
+            b.pending -= 1
+            if b.pending == 0:
+                self._reduce_bucket(b)
+        return hook
+
+    def _reduce_bucket(self, b: _Bucket):
+        cur = torch.cuda.current_stream(self.device)
+        self.ready_event.record(cur)
+        self.comm_stream.wait_event(self.ready_event)
+        g = self.flat_grads[b.start:b.end]
+        with torch.cuda.stream(self.comm_stream):
+            self.native.comm_all_reduce(self.comm, g, g, 4, 1.0)  # 4 = average
+        self.launches_per_step += 1
+
+    # ---- one optimisation step on tensors that already live on the device
+    def _step_device(self, tokens, targets):
+        for b in self.buckets:
+            b.pending = b.nparams
+        self.launches_per_step = 0
+        loss = self.model(tokens, targets)
+        loss.backward()
+        if self.world > 1:
+            self.done_event.record(self.comm_stream)
+            torch.cuda.current_stream(self.device).wait_event(self.done_event)
+        self.step_dev.add_(1)
+        fused_adamw_step(self.master, self.flat_params, self.flat_grads, self.m, self.v, lr=self.lr, betas=self.betas,
+                         eps=self.eps, weight_decay=self.wd, step=self.step_no + 1, zero_grad=True, step_dev=self.step_dev)
+        return loss.detach()
+
+    def _capture(self, tokens, targets):
+        self.static_tokens = tokens.clone()
+        self.static_targets = targets.clone()
+        self.graph = torch.cuda.CUDAGraph()
+        # the AdamW step counter lives on the device, so replays stay exact
+        with torch.cuda.graph(self.graph):
+            self.static_loss = self._step_device(self.static_tokens, self.static_targets)
+
+    def step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """One training step.  ``tokens``/``targets`` may be pinned host tensors
+        (they are copied to the device on the current stream) or device tensors.
+        Returns the loss as a device scalar; call ``.item()`` to read it back."""
+        if tokens.device.type != "cuda":
+            tokens = tokens.to(self.device, non_blocking=True)
+            targets = targets.to(self.device, non_blocking=True)
+        if not self.use_graph:
+            loss = self._step_device(tokens, targets)
+        elif self.graph is None and self.eager_steps < 2:
+            # warm-up on a side stream, as graph capture requires
+            s = torch.cuda.Stream(device=self.device)
+            s.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(s):
+                loss = self._step_device(tokens, targets)
+            torch.cuda.current_stream(self.device).wait_stream(s)
+            self.eager_steps += 1
+        else:
+            if self.graph is None:
+                self._capture(tokens, targets)
+            self.static_tokens.copy_(tokens, non_blocking=True)
+            self.static_targets.copy_(targets, non_blocking=True)
+            self.graph.replay()
+            loss = self.static_loss
+        self.step_no += 1
+        return loss
+
+    def kernels_per_step(self) -> int:
+        """Launches of this framework's own kernels in one step: 2 fused
+        LayerNorm forward + 2x2 backward and bias-GELU forward + 3 backward per
+        layer, the final LayerNorm, the loss kernel, AdamW, and one all-reduce
+        kernel per bucket (chunked by the staging size)."""
+        L = len(getattr(self.model, "blocks", []))
+        own = L * (2 + 4 + 1 + 3) + (1 + 2) + 1 + 1
+        return own + len(self.buckets)
