@@ -123,6 +123,13 @@ def main():
             if rank == 0:
                 print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref holds no reference install (flagcx plugin + libflagcx.so)"}))
             return 0
+        # The reference plugin was linked against a build-tree path; its libflagcx.so is found through
+        # LD_LIBRARY_PATH, which the loader only reads at process start: re-execute once with it set.
+        if os.environ.get("FLAGCX_REF_REEXEC") != "1":
+            env = dict(os.environ)
+            env["LD_LIBRARY_PATH"] = str(ref_dir) + os.pathsep + env.get("LD_LIBRARY_PATH", "")
+            env["FLAGCX_REF_REEXEC"] = "1"
+            os.execve(sys.executable, [sys.executable] + sys.argv, env)
 
     import torch
     if not torch.cuda.is_available():

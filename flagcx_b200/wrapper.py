@@ -242,7 +242,9 @@ class FLAGCXLibrary:
             lib = ctypes.CDLL(so_file, mode=ctypes.RTLD_GLOBAL)
             funcs = {}
             for name, (res, args) in _SIGNATURES.items():
-                f = getattr(lib, name)
+                f = getattr(lib, name, None)
+                if f is None:
+                    continue  # e.g. the reference's libflagcx.so has none of the extensions
                 f.restype = res
                 f.argtypes = args
                 funcs[name] = f
