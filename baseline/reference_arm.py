@@ -101,9 +101,10 @@ def build_reference(args, rank, world, local_rank, device):
             for m, p in zip(master, params):
                 if m.grad is None:
                     m.grad = torch.empty_like(m)
-            torch._foreach_copy_([m.grad for m in master], [p.grad for p in params])
-            opt.step()
-            torch._foreach_copy_(params, master)
+            with torch.no_grad():
+                torch._foreach_copy_([m.grad for m in master], [p.grad for p in params])
+                opt.step()
+                torch._foreach_copy_(params, master)
             ddp.zero_grad(set_to_none=False)
             return loss.detach()
 

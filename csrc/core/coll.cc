@@ -288,7 +288,8 @@ flagcxResult_t launchP2pBatch(flagcxComm *c, const std::vector<PendingOp> &ops) 
       d.buf = (void *)o.send;
       d.firstChunk = c->sendChunks[o.root];
       c->sendChunks[o.root] += nch;
-      d.heapOff = bytes ? heapOffOf(c, o.send, bytes) : ~0ull;
+      static const bool zeroCopy = envInt("P2P_ZEROCOPY", 0) != 0;
+      d.heapOff = (bytes && zeroCopy) ? heapOffOf(c, o.send, bytes) : ~0ull;
     } else {
       d.isRecv = 1;
       d.buf = o.recv;
@@ -299,7 +300,8 @@ flagcxResult_t launchP2pBatch(flagcxComm *c, const std::vector<PendingOp> &ops) 
     dops.push_back(d);
     maxBytes = std::max(maxBytes, bytes);
   }
-  int per = maxBytes <= (64u << 10) ? 1 : maxBytes <= (1u << 20) ? 4 : 8;
+  int per = maxBytes <= (64u << 10) ? 1 : maxBytes <= (1u << 20) ? 4 : maxBytes <= (16u << 20) ? 16 : 32;
+  per = (int)envInt("P2P_CTAS", per);
   for (size_t i = 0; i < dops.size(); i += FCX_MAX_GROUP_OPS) {
     FcxP2pArgs g;
     memset(&g, 0, sizeof g);

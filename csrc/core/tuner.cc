@@ -172,6 +172,13 @@ Plan Tuner::choose(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxR
     cur_ = nullptr;
     if (!s->decided && s->calls >= (long)nLoops_ * (long)s->cands.size()) decide(curKey_, *s);
   }
+  // Hot path: the answer for this exact (op, bytes, type, reduction, cast) was computed before.
+  const uint64_t fkey = ((uint64_t)bytes << 16) ^ ((uint64_t)op << 12) ^ ((uint64_t)dt << 8) ^ ((uint64_t)red << 4) ^ (cast ? 1u : 0u) ^
+                        ((uint64_t)bucket(bytes) << 56);
+  if (!search_) {
+    auto f = fast_.find(fkey);
+    if (f != fast_.end()) return f->second;
+  }
   std::vector<Plan> cands = candidates(op, bytes, dt, red, cast);
   auto legal = [&](const Plan &p) {
     for (auto &c : cands)
@@ -181,12 +188,18 @@ Plan Tuner::choose(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxR
   if (pinned_ && legal(pin_)) return pin_;
   Key k{(int)op, bucket(bytes)};
   auto it = best_.find(k);
-  if (it != best_.end() && legal(it->second)) return it->second;
+  if (it != best_.end() && legal(it->second)) {
+    if (!search_ && !pinned_ && fast_.size() < 4096) fast_[fkey] = it->second;
+    return it->second;
+  }
   // order by the prior
   std::sort(cands.begin(), cands.end(), [&](const Plan &a, const Plan &b) {
     return estimateUs(a, op, bytes, (int)dtypeSize(dt), caps_) < estimateUs(b, op, bytes, (int)dtypeSize(dt), caps_);
   });
-  if (!search_ || cands.size() < 2) return cands[0];
+  if (!search_ || cands.size() < 2) {
+    if (!search_ && !pinned_ && fast_.size() < 4096) fast_[fkey] = cands[0];
+    return cands[0];
+  }
   Search &s = searches_[k];
   if (s.cands.empty()) {
     s.cands = cands;
@@ -227,6 +240,7 @@ double Tuner::estimate(const Plan &p, flagcxCommOp_t op, size_t bytes, flagcxDat
 }
 
 void Tuner::pin(const Plan *p) {
+  fast_.clear();
   pinned_ = p != nullptr;
   if (p) pin_ = *p;
 }
@@ -244,6 +258,7 @@ void Tuner::record(flagcxCommOp_t op, size_t bytes, const Plan &p, double us) {
   if (it == bestUs_.end() || us < it->second) {
     best_[k] = p;
     bestUs_[k] = us;
+    fast_.clear();
   }
 }
 
@@ -267,6 +282,7 @@ flagcxResult_t Tuner::load(const std::string &path) {
     }
   }
   fclose(f);
+  fast_.clear();
   FCX_INFO(SUB_TUNING, "tuner: loaded %d decisions from %s", loaded, path.c_str());
   return flagcxSuccess;
 }

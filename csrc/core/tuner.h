@@ -95,6 +95,8 @@ class Tuner {
   int nLoops_ = 5;
   bool pinned_ = false;
   Plan pin_;
+  // decisions of earlier calls, keyed by everything that can change the answer
+  std::map<uint64_t, Plan> fast_;
   std::map<Key, Plan> best_;
   std::map<Key, double> bestUs_;
   std::map<Key, Search> searches_;

@@ -210,9 +210,10 @@ __device__ __forceinline__ void reduceUnits(const FcxDevComm &dc, const FcxCollA
   constexpr int INB = G * (int)sizeof(TIn), OUTB = G * (int)sizeof(TOut);
   const int n = dc.nranks, me = dc.rank;
   const size_t nunits = (nElems + G - 1) / G;
-  for (size_t u = gtid; u < nunits; u += gstride) {
+  // all loads of a unit, combined in rank order (no stores in here, so the
+  // compiler may overlap the loads of two units)
+  auto gather = [&](size_t u, AI *acc) {
     int nv = (int)min((size_t)G, nElems - u * G);
-    AI acc[G];
     for (int p = 0; p < n; p++) {
       AI in[G];
       if (p == me) loadUnit<TIn, G>(own + u * INB, ownAligned, nv, in);
@@ -225,6 +226,9 @@ __device__ __forceinline__ void reduceUnits(const FcxDevComm &dc, const FcxCollA
         for (int i = 0; i < G; i++) acc[i] = applyOp<AI>(acc[i], in[i], a.redop);
       }
     }
+  };
+  auto emit = [&](size_t u, const AI *acc) {
+    int nv = (int)min((size_t)G, nElems - u * G);
     AO res[G];
 #pragma unroll
     for (int i = 0; i < G; i++) res[i] = accCast<AO, AI>(finish<AI>(acc[i], a.redop, n, a.scale));
@@ -232,6 +236,19 @@ __device__ __forceinline__ void reduceUnits(const FcxDevComm &dc, const FcxCollA
     packUnit<TOut, G>(res, packed);
     if (dstUser) storeUnit<TOut, G>(dstUser + u * OUTB, dstAligned, nv, packed);
     for (int k = 0; k < nDstSlots; k++) storeUnit<TOut, G>(dstSlots[k] + u * OUTB, true, G, packed);
+  };
+  size_t u = gtid;
+  for (; u + gstride < nunits; u += 2 * gstride) {
+    AI acc0[G], acc1[G];
+    gather(u, acc0);
+    gather(u + gstride, acc1);
+    emit(u, acc0);
+    emit(u + gstride, acc1);
+  }
+  for (; u < nunits; u += gstride) {
+    AI acc[G];
+    gather(u, acc);
+    emit(u, acc);
   }
 }
 
@@ -649,25 +666,29 @@ __device__ void fcxMoveBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta,
 
 // ---------------------------------------------------------------- grouped send/recv
 
-// Each op owns `ctasPerOp` consecutive CTAs.  Staged sends copy a chunk into
-// this rank's per-peer staging slot and raise `ready` on the receiver; the
-// receiver pulls the chunk over NVLink and raises `consumed` on the sender.
-// A send whose buffer lives in the heap publishes the offset instead and the
-// receiver pulls straight from it.
+// Each op owns `ctasPerOp` consecutive CTAs.  A send pushes its data chunk by
+// chunk straight from the user buffer into the receiver's staging slots
+// (NVLink stores) and raises `ready` on the receiver; the receiver copies the
+// chunk out of its own memory and raises `consumed` on the sender, which
+// frees the slot.  Two slots per (receiver, sender) pair keep both sides busy.
+// With FLAGCX_P2P_ZEROCOPY=1 a send whose buffer lives in the heap publishes
+// its heap offset instead and the receiver reads it directly.
 __device__ __forceinline__ FcxP2pCtl *p2pCtl(const FcxDevComm &dc, int onRank, int dir, int peer) {
   return (FcxP2pCtl *)(dc.heap[onRank] + FCX_OFF_P2P) + dir * FCX_MAX_RANKS + peer;
 }
 
 // Arrive at the op's counter; returns true in every thread of the last CTA.
+// The fences are system-wide because the data written before arriving may
+// live in a peer's memory and is published by the last CTA's release store.
 __device__ __forceinline__ bool opArrive(const FcxDevComm &dc, int op, int slot, int ctasPerOp) {
   __shared__ unsigned int isLast;
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence();
+    __threadfence_system();
     unsigned int *c = &localOf(dc)->opCount[op][slot];
     unsigned int old = atomicAdd(c, 1u);
     isLast = (old == (unsigned)ctasPerOp - 1u);
-    if (isLast) { *c = 0; __threadfence(); }
+    if (isLast) { *c = 0; __threadfence_system(); }
   }
   __syncthreads();
   return isLast != 0;
@@ -683,7 +704,7 @@ __device__ void fcxP2pBody(const FcxDevComm &dc, const FcxP2pArgs &g, int cta) {
   const size_t chunk = dc.p2pChunkBytes;
   const uint64_t nchunks = op.bytes ? (op.bytes + chunk - 1) / chunk : 1;
 
-  if (op.isRecv == 2) {  // local copy (send to self matched with recv from self); peer field unused
+  if (op.isRecv == 2) {  // local copy (send to self matched with recv from self); heapOff carries the source pointer
     const char *s = (const char *)(uintptr_t)op.heapOff;
     char *d = (char *)op.buf;
     copyUnits(d, s, op.bytes, 16, gtid, gstride);
@@ -715,8 +736,8 @@ __device__ void fcxP2pBody(const FcxDevComm &dc, const FcxP2pArgs &g, int cta) {
         ok = waitGe(dc, &mine->consumed, gidx - 1, peer, FCX_WAIT_P2P_CONSUMED, cta, gidx);
       if (!__syncthreads_and(ok)) return;
       size_t lo = c * chunk, nb = op.bytes > lo ? min(chunk, op.bytes - lo) : 0;
-      char *st = dc.heap[me] + dc.p2pOff + ((size_t)peer * 2 + slot) * chunk;
-      if (nb) copyToSlot(st, (const char *)op.buf + lo, nb, 16, gtid, gstride);
+      char *st = dc.heap[peer] + dc.p2pOff + ((size_t)me * 2 + slot) * chunk;  // the receiver's slot for this sender
+      if (nb) copyUnits(st, (const char *)op.buf + lo, nb, 16, gtid, gstride);
       if (opArrive(dc, opIdx, slot, g.ctasPerOp) && threadIdx.x == 0) {
         if (c == 0) stRelaxed(&theirs->srcOff, ~0ull);
         stRelease(&theirs->ready, gidx + 1);
@@ -735,7 +756,7 @@ __device__ void fcxP2pBody(const FcxDevComm &dc, const FcxP2pArgs &g, int cta) {
   }
   const uint64_t srcOff = ldRelaxed(&mine->srcOff);
   if (srcOff != ~0ull) {
-    if (op.bytes) copyFromSlot((char *)op.buf, dc.heap[peer] + srcOff, op.bytes, 16, gtid, gstride);
+    if (op.bytes) copyUnits((char *)op.buf, dc.heap[peer] + srcOff, op.bytes, 16, gtid, gstride);
     if (opArrive(dc, opIdx, 0, g.ctasPerOp) && threadIdx.x == 0) stRelease(&theirs->consumed, op.firstChunk + nchunks);
     return;
   }
@@ -748,8 +769,8 @@ __device__ void fcxP2pBody(const FcxDevComm &dc, const FcxP2pArgs &g, int cta) {
       if (!__syncthreads_and(ok)) return;
     }
     size_t lo = c * chunk, nb = op.bytes > lo ? min(chunk, op.bytes - lo) : 0;
-    const char *st = dc.heap[peer] + dc.p2pOff + ((size_t)me * 2 + slot) * chunk;
-    if (nb) copyFromSlot((char *)op.buf + lo, st, nb, 16, gtid, gstride);
+    const char *st = dc.heap[me] + dc.p2pOff + ((size_t)peer * 2 + slot) * chunk;  // my slot for that sender
+    if (nb) copyUnits((char *)op.buf + lo, st, nb, 16, gtid, gstride);
     if (opArrive(dc, opIdx, slot, g.ctasPerOp) && threadIdx.x == 0) stRelease(&theirs->consumed, gidx + 1);
   }
 }

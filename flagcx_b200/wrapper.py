@@ -239,7 +239,7 @@ class FLAGCXLibrary:
     def __init__(self, so_file: Optional[str] = None):
         so_file = so_file or default_library_path()
         if so_file not in FLAGCXLibrary._cache:
-            lib = ctypes.CDLL(so_file, mode=ctypes.RTLD_GLOBAL)
+            lib = ctypes.CDLL(so_file)
             funcs = {}
             for name, (res, args) in _SIGNATURES.items():
                 f = getattr(lib, name, None)

@@ -186,7 +186,7 @@ def _collectives(lib, uid, rank, world):
 
 def test_collectives_all_ranks(native_lib):
     world = _world()
-    res, _ = run_ranks(_collectives, world, timeout=900, env={"FLAGCX_KERNEL_TIMEOUT_MS": "20000"})
+    res, _ = run_ranks(_collectives, world, timeout=900, env={"FLAGCX_KERNEL_TIMEOUT_MS": "20000", "FLAGCX_P2P_ZEROCOPY": "1"})
     for r in range(world):
         out = res[r][1]
         assert out["fails"] == [], out["fails"][:10]
@@ -196,9 +196,9 @@ def test_collectives_all_ranks(native_lib):
 
 def _timeout_path(lib, uid, rank, world):
     comm, st = _setup(lib, uid, rank, world)
-    lib.call("flagcxCommSetTimeoutMs", comm, 300)
     out = {}
     if rank == 0:
+        lib.call("flagcxCommSetTimeoutMs", comm, 300)
         # a wait that nothing satisfies: returns after the deadline with an error record, context stays usable
         lib.call("flagcxCommWaitTest", comm, st)
         torch.cuda.synchronize()
@@ -210,6 +210,7 @@ def _timeout_path(lib, uid, rank, world):
         out["still_works"] = float(torch.ones(4, device="cuda").sum().item())
         lib.call("flagcxCommClearError", comm)
         out["async_after_clear"] = lib.flagcxCommGetAsyncError(comm)
+        lib.call("flagcxCommSetTimeoutMs", comm, 20000)
     x = torch.ones(1000, device="cuda")
     lib.flagcxAllReduce(x.data_ptr(), x.data_ptr(), 1000, 7, 0, comm, st)
     torch.cuda.synchronize()
