@@ -1,0 +1,117 @@
+"""Small, self-contained workloads for profiling one kernel at a time.
+
+    python -m flagcx_b200.utils.profile_cases --case adamw
+
+Each case touches more than the 126 MB L2 but holds at most a few GB, runs a
+couple of warm-up launches and three measured ones, and prints the
+CUDA-event time with the achieved fraction of the measured HBM copy rate
+(MEASURED_PEAKS.json, else 6.65 TB/s).  Cases: adamw, cross_entropy,
+layernorm_fwd, layernorm_bwd, bias_gelu, emu_allreduce (8 emulated ranks,
+two-shot kernel, one cooperative launch on this GPU), emu_allgather."""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent.parent
+
+
+def hbm_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return json.loads(p.read_text())["hbm_gbs"] * 1e9, "of measured"
+    return 6.65e12, "of fallback"
+
+
+def timed(fn, reps=3, warm=2):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    best = 1e9
+    for _ in range(reps):
+        flush.zero_()  # evict L2 between measurements
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    return best
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", required=True)
+    args = ap.parse_args()
+    import flagcx_b200
+    nat = flagcx_b200.native()
+    peak, label = hbm_peak()
+    torch.manual_seed(0)
+    if args.case == "adamw":
+        n = 64 << 20
+        master = torch.randn(n, device="cuda")
+        param, grad = master.bfloat16(), torch.randn(n, device="cuda").bfloat16()
+        m, v = torch.zeros_like(master), torch.zeros_like(master)
+        ms = timed(lambda: nat.adamw_(master, param, grad, m, v, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1, 1.0, True))
+        nbytes = n * (4 * 3 * 2 + 2 + 2 + 2)  # master/m/v read+write, grad read+clear, param write
+    elif args.case == "cross_entropy":
+        M, V, Vp = 2048, 50257, 50304
+        logits = torch.randn(M, Vp, device="cuda").bfloat16()
+        tgt = torch.randint(0, V, (M,), device="cuda")
+        ms = timed(lambda: nat.cross_entropy_(logits, tgt, V, 1.0 / M))
+        nbytes = M * Vp * 2 * 2  # algorithmic: read once, write once (the two extra read passes should hit L2)
+    elif args.case in ("layernorm_fwd", "layernorm_bwd"):
+        M, C = 65536, 1024
+        x, d = torch.randn(M, C, device="cuda").bfloat16(), torch.randn(M, C, device="cuda").bfloat16()
+        g, b = torch.ones(C, device="cuda").bfloat16(), torch.zeros(C, device="cuda").bfloat16()
+        if args.case == "layernorm_fwd":
+            ms = timed(lambda: nat.layernorm_fwd(x, d, g, b, 1e-5))
+            nbytes = M * C * 2 * 4
+        else:
+            res, y, mean, rstd = nat.layernorm_fwd(x, d, g, b, 1e-5)
+            dy = torch.randn_like(y)
+            ms = timed(lambda: nat.layernorm_bwd(dy, res, g, mean, rstd, d))
+            nbytes = M * C * 2 * 4
+    elif args.case == "bias_gelu":
+        M, C = 32768, 4096
+        x, b = torch.randn(M, C, device="cuda").bfloat16(), torch.randn(C, device="cuda").bfloat16()
+        ms = timed(lambda: nat.bias_gelu_fwd(x, b))
+        nbytes = M * C * 2 * 2
+    elif args.case in ("emu_allreduce", "emu_allgather"):
+        from flagcx_b200.wrapper import FLAGCXLibrary
+        lib = FLAGCXLibrary()
+        n = 8
+        emu = ctypes.c_void_p()
+        lib.call("flagcxEmuCreate", ctypes.byref(emu), n, 64 << 20)
+        arr = ctypes.c_void_p * n
+        if args.case == "emu_allreduce":
+            count = 8 << 20  # 32 MiB of fp32 per rank
+            xs = [torch.randn(count, device="cuda") for _ in range(n)]
+            ys = [torch.empty_like(x) for x in xs]
+            op, kind = 6, b"ar_twoshot"
+            nbytes = n * count * 4 * (1 + 1 + 2.0 * (n - 1) / n * 2)  # read+write own, slices pushed and read back twice
+        else:
+            count = 1 << 20
+            xs = [torch.randn(count, device="cuda") for _ in range(n)]
+            ys = [torch.empty(count * n, device="cuda") for _ in range(n)]
+            op, kind = 7, b"ag"
+            nbytes = n * count * 4 * (1 + 2 * (n - 1) + n)
+        s = arr(*[x.data_ptr() for x in xs])
+        r = arr(*[y.data_ptr() for y in ys])
+        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        ms = timed(lambda: lib.call("flagcxEmuCollective", emu, op, kind, 16, s, r, count, 7, 7, ctypes.c_float(1.0), 0, 0, None, st))
+        lib.call("flagcxEmuDestroy", emu)
+    else:
+        raise SystemExit(f"unknown case {args.case}")
+    gbs = nbytes / (ms * 1e-3)
+    print(json.dumps({"case": args.case, "ms": round(ms, 4), "algorithmic_GBs": round(gbs / 1e9, 1), "fraction_of_hbm": round(gbs / peak, 3),
+                      "peak": label}))
+
+
+if __name__ == "__main__":
+    main()
