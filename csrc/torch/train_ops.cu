@@ -12,6 +12,9 @@
 #include <algorithm>
 
 #include "train_ops.h"
+#include "train_ops_noalloc.h"
+
+#include <mutex>
 
 namespace {
 
@@ -476,3 +479,59 @@ cudaError_t fcxAdamW(float *master, void *param, void *grad, float *m, float *v,
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------- allocation-free column sum
+// (contract in train_ops_noalloc.h)
+
+// Scratch that belongs to the library image.  In host code this name is only
+// a handle for the runtime; the address a kernel can use is obtained with
+// cudaGetSymbolAddress below.
+static __device__ __align__(256) float gNoAllocScratch[FCX_NOALLOC_MAX_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float *gScratchAddr[kMaxDevices];
+std::mutex gScratchMu;
+
+// Device address of the scratch array on the current device, looked up once per device.
+int scratchForCurrentDevice(float **out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return (int)cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lk(gScratchMu);
+  if (!gScratchAddr[dev]) {
+    float *p = nullptr;
+    e = cudaGetSymbolAddress((void **)&p, gNoAllocScratch);
+    if (e != cudaSuccess) return (int)e;
+    gScratchAddr[dev] = p;
+  }
+  *out = gScratchAddr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" int fcxColSumNoAlloc(const void *a, void *out, int M, int C, int accumulate, cudaStream_t stream) {
+  if (!a || !out) return FCX_NOALLOC_NULL_POINTER;
+  if (M <= 0 || C <= 0 || C % 64 != 0) return FCX_NOALLOC_BAD_SHAPE;
+  const int parts = fcxColSumPartials(M);
+  if ((long long)parts * C > (long long)FCX_NOALLOC_MAX_FLOATS) return FCX_NOALLOC_TOO_LARGE;
+  float *scratch = nullptr;
+  int rc = scratchForCurrentDevice(&scratch);
+  if (rc != 0) return rc;
+  // Every partial[p][c] with p < parts, c < C is written by colSumKernel before
+  // colSumReduceKernel reads it, so stale contents of earlier calls are harmless.
+  colSumKernel<<<dim3(C / 64, parts), 256, 0, stream>>>((const bf16 *)a, scratch, M, C);
+  colSumReduceKernel<<<(C + 255) / 256, 256, 0, stream>>>(scratch, parts, C, (bf16 *)out, accumulate);
+  return (int)cudaGetLastError();
+}
+
+extern "C" const char *fcxNoAllocErrorString(int code) {
+  switch (code) {
+    case 0: return "success";
+    case FCX_NOALLOC_TOO_LARGE: return "shape needs more than the built-in scratch (partials x C > 262144 floats); use fcxColSum with your own scratch";
+    case FCX_NOALLOC_BAD_SHAPE: return "M and C must be positive and C a multiple of 64";
+    case FCX_NOALLOC_NULL_POINTER: return "input and output pointers must not be null";
+    default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown code";
+  }
+}
