@@ -312,16 +312,18 @@ void rootThread(int listenFd, uint64_t magic) {
 
 }  // namespace
 
-flagcxResult_t Bootstrap::createId(BootstrapHandle *out) {
+static constexpr uint64_t kFixedIdMagic = 0x464c41474358ull;
+
+flagcxResult_t Bootstrap::createId(BootstrapHandle *out, bool allowFixedAddress) {
   memset(out, 0, sizeof *out);
-  const char *fixed = getEnv("FLAGCX_COMM_ID");
+  const char *fixed = allowFixedAddress ? getEnv("FLAGCX_COMM_ID") : nullptr;
   if (fixed) {
     // Static rendezvous: every rank derives the same handle; rank 0 opens it.
     if (!parseIpPort(fixed, &out->addr)) {
       FCX_WARN("FLAGCX_COMM_ID must be ip:port, got '%s'", fixed);
       return flagcxInvalidArgument;
     }
-    out->magic = 0x464c41474358ull;  // constant: all ranks must agree without talking
+    out->magic = kFixedIdMagic;  // constant: all ranks must agree without talking
     return flagcxSuccess;
   }
   std::random_device rd;
@@ -364,7 +366,7 @@ flagcxResult_t Bootstrap::init(const BootstrapHandle &h, int rank, int nranks) {
     faultKind_ = kind == "bad_magic" ? 1 : kind == "close_after" ? 2 : kind == "delay_ms" ? 3 : kind == "exit_after" ? 4 : 0;
   }
 
-  if (getEnv("FLAGCX_COMM_ID") && rank == 0) {
+  if (getEnv("FLAGCX_COMM_ID") && rank == 0 && h.magic == kFixedIdMagic) {
     int fd;
     SockAddr a;
     FCX_CHECK(sockListen(&fd, &a, &h.addr));

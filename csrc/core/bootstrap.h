@@ -41,7 +41,7 @@ class Bootstrap {
   // Creates the root listener + service thread and fills `out`.
   // With FLAGCX_COMM_ID=ip:port the address is fixed and only rank 0's
   // process actually starts the root thread (in init()).
-  static flagcxResult_t createId(BootstrapHandle *out);
+  static flagcxResult_t createId(BootstrapHandle *out, bool allowFixedAddress = true);
 
   flagcxResult_t init(const BootstrapHandle &h, int rank, int nranks);
   void close();

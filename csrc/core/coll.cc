@@ -349,6 +349,13 @@ static flagcxResult_t submit(flagcxComm_t c, PendingOp &&o) {
     c->pending.push_back(std::move(o));
     return flagcxSuccess;
   }
+  if (c->nclusters > 1 && c->nranks > 1 && o.op != flagcxCommNoOp && o.op != flagcxCommOpSend && o.op != flagcxCommOpRecv &&
+      o.count > 0) {
+    // several clusters: try the hierarchical plan first (its stages come back here on sub-communicators)
+    bool handled = false;
+    FCX_CHECK(c2cExecute(c, o, &handled));
+    if (handled) return flagcxSuccess;
+  }
   if (c->hostOnly || c->hostFallback) return hostCollective(c, o);
   if (o.op == flagcxCommOpSend || o.op == flagcxCommOpRecv) return launchP2pBatch(c, {o});
   if (o.count == 0 && o.op != flagcxCommNoOp && o.op != flagcxCommOpAlltoAllv) return flagcxSuccess;
@@ -367,11 +374,6 @@ static flagcxResult_t submit(flagcxComm_t c, PendingOp &&o) {
     if (o.op != flagcxCommNoOp && o.send != o.recv && nb)
       return cudaToResult(cudaMemcpyAsync(o.recv, o.send, nb, cudaMemcpyDeviceToDevice, o.stream), "single-rank copy");
     return flagcxSuccess;
-  }
-  if (c->nclusters > 1 && o.op != flagcxCommNoOp) {
-    bool handled = false;
-    FCX_CHECK(c2cExecute(c, o, &handled));
-    if (handled) return flagcxSuccess;
   }
   return launchCollective(c, o);
 }
@@ -491,7 +493,21 @@ flagcxResult_t flagcxGroupEnd(flagcxComm_t) {
     std::vector<PendingOp> ops;
     ops.swap(c->pending);
     if (res != flagcxSuccess) continue;
-    if (c->hostOnly || c->hostFallback) { res = hostGroup(c, ops); continue; }
+    if ((c->hostOnly || c->hostFallback) && c->nclusters == 1) { res = hostGroup(c, ops); continue; }
+    if (c->hostOnly || c->hostFallback) {
+      // hierarchical host communicator: point-to-point pairs first, then each collective through the planner
+      std::vector<PendingOp> p2pOnly, rest;
+      for (auto &o : ops) (o.op == flagcxCommOpSend || o.op == flagcxCommOpRecv ? p2pOnly : rest).push_back(o);
+      res = hostGroup(c, p2pOnly);
+      for (auto &o : rest) {
+        if (res != flagcxSuccess) break;
+        PendingOp copy = o;
+        res = submit(c, std::move(copy));
+        c->counters.calls[o.op]--;
+        c->counters.bytes[o.op] -= o.count * dtypeSize(o.dt);
+      }
+      continue;
+    }
     std::vector<PendingOp> p2p;
     for (auto &o : ops)
       if (o.op == flagcxCommOpSend || o.op == flagcxCommOpRecv) p2p.push_back(o);

@@ -101,25 +101,17 @@ __global__ void __launch_bounds__(256) lnFwdKernel(const bf16 *__restrict__ x, c
   }
 }
 
-// Backward: dx = rstd * (g*dy - mean(g*dy) - xhat * mean(g*dy*xhat)) [+ dres];
-// per-CTA partial sums of dgamma/dbeta go to `partial` ([gridDim.x][2][C],
-// fp32 scratch) and are folded by lnBwdReduceKernel.
+// Backward, part 1: dx = rstd * (g*dy - mean(g*dy) - xhat * mean(g*dy*xhat)) [+ dres].
+// One warp per row, few registers, so that several CTAs share an SM and hide
+// the memory latency.
 template <int MAXV>
-__global__ void __launch_bounds__(256) lnBwdKernel(const bf16 *__restrict__ dy, const bf16 *__restrict__ x,
-                                                   const bf16 *__restrict__ gamma, const float *__restrict__ mean,
-                                                   const float *__restrict__ rstd, const bf16 *__restrict__ dres,
-                                                   bf16 *__restrict__ dx, float *__restrict__ partial, int M, int C) {
-  extern __shared__ float sm[];  // [2][C] accumulators of this CTA
-  for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) sm[i] = 0.f;
-  __syncthreads();
+__global__ void __launch_bounds__(256, 3) lnBwdDxKernel(const bf16 *__restrict__ dy, const bf16 *__restrict__ x,
+                                                        const bf16 *__restrict__ gamma, const float *__restrict__ mean,
+                                                        const float *__restrict__ rstd, const bf16 *__restrict__ dres,
+                                                        bf16 *__restrict__ dx, int M, int C) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
   const int nv = C / 256;
-  float dg[MAXV][8], db[MAXV][8];
-#pragma unroll
-  for (int i = 0; i < MAXV; i++)
-#pragma unroll
-    for (int k = 0; k < 8; k++) dg[i][k] = db[i][k] = 0.f;
   for (int row = warp; row < M; row += nwarps) {
     const float mu = mean[row], rs = rstd[row];
     float gy[MAXV][8], xh[MAXV][8];
@@ -137,8 +129,6 @@ __global__ void __launch_bounds__(256) lnBwdKernel(const bf16 *__restrict__ dy, 
           gy[i][k] = g[k] * d[k];
           s1 += gy[i][k];
           s2 += gy[i][k] * xh[i][k];
-          dg[i][k] += d[k] * xh[i][k];
-          db[i][k] += d[k];
         }
       }
     s1 = warpSum(s1) / C;
@@ -156,19 +146,56 @@ __global__ void __launch_bounds__(256) lnBwdKernel(const bf16 *__restrict__ dy, 
         ((Bf8 *)(dx + (size_t)row * C))[i * 32 + lane] = pack8(o);
       }
   }
+}
+
+// Backward, part 2: dgamma[c] = sum_r dy[r,c] * xhat[r,c], dbeta[c] = sum_r dy[r,c].
+// A CTA owns 64 columns and one slice of the rows; partial sums go to
+// `partial` ([gridDim.y][2][C], fp32 scratch) and are folded by lnBwdReduceKernel.
+__global__ void __launch_bounds__(256) lnBwdParamKernel(const bf16 *__restrict__ dy, const bf16 *__restrict__ x,
+                                                        const float *__restrict__ mean, const float *__restrict__ rstd,
+                                                        float *__restrict__ partial, int M, int C) {
+  __shared__ float redG[32][64 + 1], redB[32][64 + 1];
+  const int col0 = blockIdx.x * 64;
+  const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
+  float dg[8] = {0, 0, 0, 0, 0, 0, 0, 0}, db[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  const int rowsPer = (M + gridDim.y - 1) / gridDim.y;
+  const int r0 = blockIdx.y * rowsPer, r1 = min(M, r0 + rowsPer);
+  int r = r0 + ty;
+  for (; r + 32 < r1; r += 64) {  // two rows in flight per thread
+    float d0[8], x0[8], d1[8], x1[8];
+    unpack8(*(const Bf8 *)(dy + (size_t)r * C + col0 + tx * 8), d0);
+    unpack8(*(const Bf8 *)(x + (size_t)r * C + col0 + tx * 8), x0);
+    unpack8(*(const Bf8 *)(dy + (size_t)(r + 32) * C + col0 + tx * 8), d1);
+    unpack8(*(const Bf8 *)(x + (size_t)(r + 32) * C + col0 + tx * 8), x1);
+    const float m0 = mean[r], s0 = rstd[r], m1 = mean[r + 32], s1 = rstd[r + 32];
 #pragma unroll
-  for (int i = 0; i < MAXV; i++)
-    if (i < nv) {
-#pragma unroll
-      for (int k = 0; k < 8; k++) {
-        int c = (i * 32 + lane) * 8 + k;
-        atomicAdd(&sm[c], dg[i][k]);
-        atomicAdd(&sm[C + c], db[i][k]);
-      }
+    for (int k = 0; k < 8; k++) {
+      dg[k] += d0[k] * (x0[k] - m0) * s0 + d1[k] * (x1[k] - m1) * s1;
+      db[k] += d0[k] + d1[k];
     }
+  }
+  for (; r < r1; r += 32) {
+    float d0[8], x0[8];
+    unpack8(*(const Bf8 *)(dy + (size_t)r * C + col0 + tx * 8), d0);
+    unpack8(*(const Bf8 *)(x + (size_t)r * C + col0 + tx * 8), x0);
+    const float m0 = mean[r], s0 = rstd[r];
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+      dg[k] += d0[k] * (x0[k] - m0) * s0;
+      db[k] += d0[k];
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 8; k++) { redG[ty][tx * 8 + k] = dg[k]; redB[ty][tx * 8 + k] = db[k]; }
   __syncthreads();
-  float *out = partial + (size_t)blockIdx.x * 2 * C;
-  for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) out[i] = sm[i];
+  if (threadIdx.x < 128) {
+    const int c = threadIdx.x & 63;
+    const bool isB = threadIdx.x >= 64;
+    float s = 0.f;
+#pragma unroll 8
+    for (int j = 0; j < 32; j++) s += isB ? redB[j][c] : redG[j][c];
+    partial[((size_t)blockIdx.y * 2 + (isB ? 1 : 0)) * C + col0 + c] = s;
+  }
 }
 
 __global__ void lnBwdReduceKernel(const float *__restrict__ partial, int nparts, int C, bf16 *__restrict__ dgamma,
@@ -176,6 +203,7 @@ __global__ void lnBwdReduceKernel(const float *__restrict__ partial, int nparts,
   int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= 2 * C) return;
   float s = 0.f;
+#pragma unroll 8
   for (int p = 0; p < nparts; p++) s += partial[(size_t)p * 2 * C + c];
   bf16 *dst = c < C ? dgamma + c : dbeta + (c - C);
   if (accumulate) s += __bfloat162float(*dst);
@@ -183,21 +211,42 @@ __global__ void lnBwdReduceKernel(const float *__restrict__ partial, int nparts,
 }
 
 // ---------------------------------------------------------------- bias + GELU (tanh form)
+__device__ __forceinline__ float fastTanh(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float geluF(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-  return 0.5f * x * (1.f + tanhf(k0 * (x + k1 * x * x * x)));
+  return 0.5f * x * (1.f + fastTanh(k0 * (x + k1 * x * x * x)));
 }
 __device__ __forceinline__ float geluGrad(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-  float u = k0 * (x + k1 * x * x * x), t = tanhf(u);
+  float u = k0 * (x + k1 * x * x * x), t = fastTanh(u);
   return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * k0 * (1.f + 3.f * k1 * x * x);
 }
 
-// y = gelu(x + bias); x is [M, C]
+// y = gelu(x + bias); x is [M, C].  Each thread keeps four 16-byte loads in flight.
 __global__ void __launch_bounds__(256) biasGeluFwdKernel(const bf16 *__restrict__ x, const bf16 *__restrict__ bias,
                                                          bf16 *__restrict__ y, size_t nvec, int C) {
   const int cv = C / 8;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < nvec; i += 4 * stride) {
+    Bf8 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) v[j] = ((const Bf8 *)x)[i + j * stride];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      float a[8], b[8];
+      unpack8(v[j], a);
+      unpack8(((const Bf8 *)bias)[(i + j * stride) % cv], b);
+#pragma unroll
+      for (int k = 0; k < 8; k++) a[k] = geluF(a[k] + b[k]);
+      ((Bf8 *)y)[i + j * stride] = pack8(a);
+    }
+  }
+  for (; i < nvec; i += stride) {
     float a[8], b[8];
     unpack8(((const Bf8 *)x)[i], a);
     unpack8(((const Bf8 *)bias)[i % cv], b);
@@ -211,7 +260,24 @@ __global__ void __launch_bounds__(256) biasGeluFwdKernel(const bf16 *__restrict_
 __global__ void __launch_bounds__(256) biasGeluBwdKernel(const bf16 *__restrict__ dy, const bf16 *__restrict__ x,
                                                          const bf16 *__restrict__ bias, bf16 *__restrict__ dx, size_t nvec, int C) {
   const int cv = C / 8;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + stride < nvec; i += 2 * stride) {
+    Bf8 xv[2], dv[2];
+#pragma unroll
+    for (int j = 0; j < 2; j++) { xv[j] = ((const Bf8 *)x)[i + j * stride]; dv[j] = ((const Bf8 *)dy)[i + j * stride]; }
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+      float a[8], b[8], d[8];
+      unpack8(xv[j], a);
+      unpack8(dv[j], d);
+      unpack8(((const Bf8 *)bias)[(i + j * stride) % cv], b);
+#pragma unroll
+      for (int k = 0; k < 8; k++) d[k] *= geluGrad(a[k] + b[k]);
+      ((Bf8 *)dx)[i + j * stride] = pack8(d);
+    }
+  }
+  for (; i < nvec; i += stride) {
     float a[8], b[8], d[8];
     unpack8(((const Bf8 *)x)[i], a);
     unpack8(((const Bf8 *)bias)[i % cv], b);
@@ -404,12 +470,12 @@ int smCount() {
 
 extern "C" {
 
-int fcxLnPartials(int M) { return min(smCount() * 2, (M + 7) / 8); }
+int fcxLnPartials(int M) { return max(1, min(32, M / 128)); }
 
 cudaError_t fcxLayerNormFwd(const void *x, const void *delta, const void *gamma, const void *beta, void *resOut, void *y,
                             float *mean, float *rstd, int M, int C, float eps, cudaStream_t s) {
   if (C % 256 != 0 || C > 256 * 8) return cudaErrorInvalidValue;
-  int grid = min(smCount() * 4, (M + 7) / 8);
+  int grid = min(smCount() * 8, (M + 7) / 8);
   if (C <= 1024)
     lnFwdKernel<4><<<grid, 256, 0, s>>>((const bf16 *)x, (const bf16 *)delta, (const bf16 *)gamma, (const bf16 *)beta,
                                         (bf16 *)resOut, (bf16 *)y, mean, rstd, M, C, eps);
@@ -424,15 +490,16 @@ cudaError_t fcxLayerNormBwd(const void *dy, const void *x, const void *gamma, co
                             const void *dres, void *dx, void *dgamma, void *dbeta, float *partial, int M, int C, int accumulate,
                             cudaStream_t s) {
   if (C % 256 != 0 || C > 256 * 8) return cudaErrorInvalidValue;
-  int grid = fcxLnPartials(M);
-  size_t smem = 2 * (size_t)C * sizeof(float);
+  int grid = min(smCount() * 6, (M + 7) / 8);
   if (C <= 1024)
-    lnBwdKernel<4><<<grid, 256, smem, s>>>((const bf16 *)dy, (const bf16 *)x, (const bf16 *)gamma, mean, rstd, (const bf16 *)dres,
-                                           (bf16 *)dx, partial, M, C);
+    lnBwdDxKernel<4><<<grid, 256, 0, s>>>((const bf16 *)dy, (const bf16 *)x, (const bf16 *)gamma, mean, rstd, (const bf16 *)dres,
+                                          (bf16 *)dx, M, C);
   else
-    lnBwdKernel<8><<<grid, 256, smem, s>>>((const bf16 *)dy, (const bf16 *)x, (const bf16 *)gamma, mean, rstd, (const bf16 *)dres,
-                                           (bf16 *)dx, partial, M, C);
-  lnBwdReduceKernel<<<(2 * C + 255) / 256, 256, 0, s>>>(partial, grid, C, (bf16 *)dgamma, (bf16 *)dbeta, accumulate);
+    lnBwdDxKernel<8><<<grid, 256, 0, s>>>((const bf16 *)dy, (const bf16 *)x, (const bf16 *)gamma, mean, rstd, (const bf16 *)dres,
+                                          (bf16 *)dx, M, C);
+  int parts = fcxLnPartials(M);
+  lnBwdParamKernel<<<dim3(C / 64, parts), 256, 0, s>>>((const bf16 *)dy, (const bf16 *)x, mean, rstd, partial, M, C);
+  lnBwdReduceKernel<<<(2 * C + 255) / 256, 256, 0, s>>>(partial, parts, C, (bf16 *)dgamma, (bf16 *)dbeta, accumulate);
   return cudaGetLastError();
 }
 

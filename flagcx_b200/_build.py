@@ -88,7 +88,7 @@ def build_native(force=False, verbose=False) -> Path:
     newest = max(o.stat().st_mtime for o in objs)
     if force or not out.exists() or out.stat().st_mtime < newest:
         cmd = [NVCC, "-shared", "-o", str(out)] + [str(o) for o in objs] + ARCH + [
-            "-cudart", "static", "-Xlinker", "--no-as-needed", "-lpthread", "-ldl", "-lrt"]
+            "-cudart", "static", "-Xlinker", "--no-as-needed", "-lpthread", "-ldl", "-lrt", "-Xlinker", "-z", "-Xlinker", "defs"]
         _run(cmd)
     if verbose:
         print(f"built {out}")
