@@ -21,6 +21,7 @@ flagcxResult_t cudaToResult(cudaError_t e, const char *what) {
 
 void fifoStop(flagcxComm *c);     // fifo.cc
 void c2cDestroy(flagcxComm *c);   // c2c/planner.cc
+flagcxResult_t topoProbeAndDump(flagcxComm *c);  // topo.cc
 
 // Clusters: ranks with the same vendor string form a cluster; each cluster
 // can further be cut into k equal parts with FLAGCX_CLUSTER_SPLIT_LIST
@@ -156,6 +157,8 @@ flagcxResult_t commCreate(flagcxComm **out, int nranks, const BootstrapHandle &h
     FCX_INFO(SUB_INIT, "comm %p rank %d/%d: heap %zu MiB (%s%s), stage 2x%zu MiB", (void *)c.get(), rank, nranks,
              c->heap.bytes >> 20, c->heap.vmm ? "vmm" : "ipc", c->heap.mcBase ? "+multicast" : "", stage >> 20);
   }
+
+  FCX_CHECK(topoProbeAndDump(c.get()));
 
   TunerCaps caps;
   caps.nranks = nranks;
