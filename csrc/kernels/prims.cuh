@@ -49,7 +49,7 @@ __device__ __forceinline__ FcxLocal *localOf(const FcxDevComm &dc) {
 
 // Record why a wait ended without its condition.  Never traps: the kernel
 // keeps running valid code and returns; the host reads the record.
-__device__ __noinline__ void giveUp(const FcxDevComm &dc, uint32_t code, int peer, int where, int cta,
+static __device__ __noinline__ void giveUp(const FcxDevComm &dc, uint32_t code, int peer, int where, int cta,
                                     uint64_t expected, uint64_t seen, uint64_t seq) {
   FcxLocal *loc = localOf(dc);
   if (atomicCAS(&loc->errClaim, 0u, 1u) == 0u) {

@@ -1,5 +1,76 @@
 // Bindings of the tcgen05 GEMM family (gemm_sm100.cu).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
+
+#include "flagcx.h"
+#include "flagcx_ext.h"
+#include "gemm_sm100.h"
+
 namespace fcxt {
-void bindGemm(py::module &) {}
+
+FcxDevComm devComm(uint64_t comm);                       // fused_ops.cpp
+size_t heapOffset(uint64_t comm, const at::Tensor &t);   // fused_ops.cpp
+
+static void checkMat(const at::Tensor &t, const char *name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 2 && t.stride(1) == 1, name, " must be a 2-D bf16 CUDA tensor with contiguous rows");
+}
+
+// c[M,N] = a[M,K] @ b[N,K]^T on the tcgen05 path.  err is an int32 device scalar that the kernel sets when a wait gives up.
+static at::Tensor gemmNT(const at::Tensor &a, const at::Tensor &b, at::Tensor &err) {
+  checkMat(a, "a");
+  checkMat(b, "b");
+  TORCH_CHECK(a.size(1) == b.size(1), "inner dimensions differ");
+  c10::cuda::CUDAGuard g(a.device());
+  auto c = at::empty({a.size(0), b.size(0)}, a.options());
+  auto e = fcxGemmBf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), (int)a.size(0), (int)b.size(0), (int)a.size(1), (int)a.stride(0),
+                       (int)b.stride(0), (int)c.stride(0), err.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(e == cudaSuccess, "tcgen05 GEMM launch failed: ", cudaGetErrorString(e));
+  return c;
+}
+
+// y[M,N] = all_gather(x_local)[M,K] @ w[N,K]^T.  gathered: heap tensor [M,K]; flags: heap int64 tensor [M/128];
+// epoch: 1-based use count of this (gathered, flags) pair.
+static at::Tensor agGemm(uint64_t comm, const at::Tensor &xLocal, at::Tensor &gathered, at::Tensor &flags, const at::Tensor &w,
+                         int64_t epoch, int64_t commCtas, at::Tensor &err) {
+  checkMat(xLocal, "x_local");
+  checkMat(w, "w");
+  TORCH_CHECK(xLocal.is_contiguous() && gathered.is_contiguous(), "x_local and gathered must be contiguous");
+  c10::cuda::CUDAGuard g(xLocal.device());
+  FcxDevComm dc = devComm(comm);
+  const int M = (int)xLocal.size(0) * dc.nranks, K = (int)xLocal.size(1), N = (int)w.size(0);
+  TORCH_CHECK(gathered.numel() >= (int64_t)M * K && flags.numel() >= M / 128, "workspace too small");
+  auto y = at::empty({M, N}, xLocal.options());
+  auto e = fcxAgGemmBf16(&dc, xLocal.data_ptr(), gathered.data_ptr(), heapOffset(comm, gathered), heapOffset(comm, flags), w.data_ptr(),
+                         y.data_ptr(), M, N, K, (int)w.stride(0), (int)y.stride(0), (uint64_t)epoch, (int)commCtas, err.data_ptr<int>(),
+                         at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(e == cudaSuccess, "fused all-gather GEMM launch failed: ", cudaGetErrorString(e));
+  return y;
+}
+
+// out[M/n,N] = reduce_scatter(a[M,K] @ w[N,K]^T).  stage: heap bf16 tensor [n, M/n, N]; counters: heap int64 tensor
+// [M/n/128 * ceil(N/256)]; epoch: 1-based use count of this (stage, counters) pair.
+static at::Tensor gemmRs(uint64_t comm, const at::Tensor &a, const at::Tensor &w, at::Tensor &stage, at::Tensor &counters, int64_t epoch,
+                         at::Tensor &err) {
+  checkMat(a, "a");
+  checkMat(w, "w");
+  c10::cuda::CUDAGuard g(a.device());
+  FcxDevComm dc = devComm(comm);
+  const int M = (int)a.size(0), K = (int)a.size(1), N = (int)w.size(0);
+  TORCH_CHECK(M % (dc.nranks * 128) == 0, "rows must be a multiple of 128 x ranks");
+  TORCH_CHECK(stage.numel() >= (int64_t)M * N && counters.numel() >= (M / dc.nranks / 128) * ((N + 255) / 256), "workspace too small");
+  auto out = at::empty({M / dc.nranks, N}, a.options());
+  auto e = fcxGemmRsBf16(&dc, a.data_ptr(), w.data_ptr(), out.data_ptr(), heapOffset(comm, stage), heapOffset(comm, counters), M, N, K,
+                         (int)a.stride(0), (int)w.stride(0), (int)out.stride(0), (uint64_t)epoch, err.data_ptr<int>(),
+                         at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(e == cudaSuccess, "fused GEMM reduce-scatter launch failed: ", cudaGetErrorString(e));
+  return out;
+}
+
+void bindGemm(py::module &m) {
+  m.def("gemm_nt", &gemmNT, "bf16 a[M,K] @ b[N,K]^T on tcgen05");
+  m.def("ag_gemm", &agGemm);
+  m.def("gemm_rs", &gemmRs);
+}
+
 }  // namespace fcxt

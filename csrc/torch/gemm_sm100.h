@@ -1,0 +1,36 @@
+// Parameters and launchers of the tcgen05 GEMM family (gemm_sm100.cu).
+#pragma once
+#include "../kernels/devcomm.h"
+#include <cuda_runtime_api.h>
+#include <stdint.h>
+
+#define FCX_GEMM_PLAIN 0
+#define FCX_GEMM_AG 1
+#define FCX_GEMM_RS 2
+
+struct FcxGemmParams {
+  int M, N, K;          // C[M,N] = A[M,K] * B[N,K]^T, bf16 in, fp32 accumulate, bf16 out
+  void *c;              // PLAIN/AG: C; RS: this rank's [M/n, N] result
+  int ldc;
+  int rotate;           // first row block (of 128 rows) this rank works on
+  int rowsPerRank;      // M / nranks (AG, RS)
+  int gemmCtas;         // AG: CTAs [0, gemmCtas) compute, the rest move data
+  const void *aLocal;   // AG: this rank's [rowsPerRank, K] block
+  size_t gatherOff;     // AG: heap offset of the gathered [M, K] buffer (same on every rank)
+  size_t stageOff;      // RS: heap offset of the partial-tile staging [n][rowsPerRank][N]
+  size_t flagOff;       // AG: heap offset of u64 flags [M/128]; RS: of u64 counters [rowsPerRank/128][ceil(N/256)]
+  uint64_t epoch;       // 1-based use count of the flag/counter array that flagOff points to
+  int *errFlag;         // device int, set to 1 when a bounded wait gave up
+};
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+cudaError_t fcxGemmBf16(const void *a, const void *b, void *c, int M, int N, int K, int lda, int ldb, int ldc, int *errFlag, cudaStream_t s);
+cudaError_t fcxAgGemmBf16(const FcxDevComm *dc, const void *aLocal, const void *gathered, size_t gatherOff, size_t flagOff, const void *b,
+                          void *c, int M, int N, int K, int ldb, int ldc, uint64_t epoch, int commCtas, int *errFlag, cudaStream_t s);
+cudaError_t fcxGemmRsBf16(const FcxDevComm *dc, const void *a, const void *b, void *out, size_t stageOff, size_t flagOff, int M, int N, int K,
+                          int lda, int ldb, int ldc, uint64_t epoch, int *errFlag, cudaStream_t s);
+#ifdef __cplusplus
+}
+#endif

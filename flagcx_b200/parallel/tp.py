@@ -1,0 +1,85 @@
+"""Tensor-parallel (sequence-parallel) building blocks on the fused tcgen05
+kernels: all-gather -> GEMM on entry of a sharded block and GEMM ->
+reduce-scatter on exit, each ONE kernel that moves the data over NVLink while
+the tensor cores work (csrc/torch/gemm_sm100.cu).
+
+``TensorParallelContext`` owns the symmetric-heap workspaces (gathered
+activations, partial-tile staging, flags and counters), double-buffered by
+call parity so that a rank that runs one call ahead of a peer never touches
+memory the peer still reads.
+
+The unfused equivalents (library all-gather / reduce-scatter followed by a
+library GEMM) are what a FlagCX user runs today; ``unfused_ag_gemm`` and
+``unfused_gemm_rs`` implement exactly that on this library's collectives for
+comparison.
+"""
+from __future__ import annotations
+
+import torch
+
+import flagcx_b200
+
+
+class TensorParallelContext:
+    def __init__(self, comm: int, nranks: int, rank: int, max_rows: int, max_k: int, max_n: int, comm_ctas: int = 16,
+                 device=None):
+        """``max_rows``: tokens of the full (gathered) sequence; ``max_k``: widest gathered activation;
+        ``max_n``: widest reduce-scattered output."""
+        self.nat = flagcx_b200.native()
+        self.comm, self.n, self.rank = comm, nranks, rank
+        self.comm_ctas = comm_ctas
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        ht = self.nat.heap_tensor
+        self.gathered = [ht(comm, [max_rows, max_k], torch.bfloat16) for _ in range(2)]
+        self.ag_flags = [ht(comm, [max(1, max_rows // 128)], torch.int64).zero_() for _ in range(2)]
+        self.rs_stage = [ht(comm, [nranks, max_rows // nranks, max_n], torch.bfloat16) for _ in range(2)]
+        self.rs_counters = [ht(comm, [max(1, max_rows // nranks // 128) * ((max_n + 255) // 256)], torch.int64).zero_() for _ in range(2)]
+        self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.ag_calls = 0
+        self.rs_calls = 0
+        torch.cuda.synchronize()
+        # nobody may push into a workspace that its owner has not cleared yet
+        if nranks > 1:
+            t = torch.zeros(1, device=self.device)
+            self.nat.comm_all_reduce(comm, t, t, 0, 1.0)
+            torch.cuda.synchronize()
+
+    def ag_gemm(self, x_local: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """``all_gather(x_local) @ w.T``; x_local [rows/n, K], w [N, K] -> [rows, N]."""
+        par = self.ag_calls & 1
+        epoch = (self.ag_calls >> 1) + 1
+        self.ag_calls += 1
+        rows, k = x_local.shape[0] * self.n, x_local.shape[1]
+        gathered = self.gathered[par].view(-1)[: rows * k].view(rows, k)
+        return self.nat.ag_gemm(self.comm, x_local, gathered, self.ag_flags[par], w, epoch, self.comm_ctas, self.err)
+
+    def gemm_rs(self, a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """``reduce_scatter(a @ w.T)`` over rows; a [rows, K], w [N, K] -> [rows/n, N]."""
+        par = self.rs_calls & 1
+        epoch = (self.rs_calls >> 1) + 1
+        self.rs_calls += 1
+        rows, n_out = a.shape[0], w.shape[0]
+        stage = self.rs_stage[par].view(-1)[: rows * n_out]
+        return self.nat.gemm_rs(self.comm, a, w, stage, self.rs_counters[par], epoch, self.err)
+
+    def check(self):
+        """Raise if a kernel of this context gave up on a wait (call after a synchronize)."""
+        if int(self.err.item()) != 0:
+            raise RuntimeError("a fused GEMM kernel gave up waiting (peer missing or too slow)")
+
+    # ---- the unfused baselines on the same library
+    def unfused_ag_gemm(self, x_local, w):
+        full = torch.empty(x_local.shape[0] * self.n, x_local.shape[1], dtype=x_local.dtype, device=x_local.device)
+        if self.n > 1:
+            self.nat.comm_all_gather(self.comm, x_local, full)
+        else:
+            full.copy_(x_local)
+        return full @ w.t()
+
+    def unfused_gemm_rs(self, a, w):
+        part = a @ w.t()
+        if self.n == 1:
+            return part
+        out = torch.empty(a.shape[0] // self.n, w.shape[0], dtype=a.dtype, device=a.device)
+        self.nat.comm_reduce_scatter(self.comm, part, out, 0)
+        return out

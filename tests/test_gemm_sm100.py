@@ -1,0 +1,82 @@
+"""tcgen05 GEMM family against fp32 PyTorch references, on one GPU.
+
+The fused all-gather/reduce-scatter forms run here on a one-rank communicator:
+that still exercises the comm CTAs, the per-block flags, the proxy fence in
+front of the TMA loads, the staging/counter path and the reduction phase."""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def nat():
+    import flagcx_b200
+    return flagcx_b200.native()
+
+
+def _ref(a, b):
+    return a.float() @ b.float().t()
+
+
+def _close(got, ref, k):
+    tol = 2e-2 * (k ** 0.5) * 0.05 + 2e-2
+    err = (got.float() - ref).abs().max().item()
+    scale = ref.abs().max().item() + 1e-6
+    assert err / scale < 2e-2, (err, scale)
+    return err
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (1024, 768, 4096), (8192, 3584, 4096), (384, 200, 136), (100, 72, 8)])
+def test_plain_gemm(nat, M, N, K):
+    torch.manual_seed(0)
+    a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    c = nat.gemm_nt(a, b, err)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    _close(c, _ref(a, b), K)
+
+
+def test_plain_gemm_strided_operands(nat):
+    torch.manual_seed(1)
+    big_a = (torch.randn(512, 1024, device="cuda")).bfloat16()
+    big_b = (torch.randn(512, 1024, device="cuda")).bfloat16()
+    a, b = big_a[:, 256:768], big_b[:384, 256:768]  # row stride 1024, 512-byte offset
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    c = nat.gemm_nt(a, b, err)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    _close(c, _ref(a, b), 512)
+
+
+@pytest.fixture(scope="module")
+def comm1():
+    from flagcx_b200.wrapper import FLAGCXLibrary
+    lib = FLAGCXLibrary()
+    torch.zeros(1, device="cuda")
+    uid = lib.flagcxGetUniqueId()
+    comm = lib.flagcxCommInitRank(1, uid, 0)
+    yield lib, comm
+    torch.cuda.synchronize()
+    lib.flagcxCommDestroy(comm)
+
+
+def test_fused_forms_on_one_rank(nat, comm1):
+    from flagcx_b200.parallel.tp import TensorParallelContext
+    lib, comm = comm1
+    tp = TensorParallelContext(comm.value, 1, 0, max_rows=1024, max_k=1024, max_n=1024, comm_ctas=4)
+    torch.manual_seed(2)
+    for rep in range(3):  # both workspace parities and a reused one
+        x = (torch.randn(1024, 512, device="cuda") * 0.5).bfloat16()
+        w = (torch.randn(768, 512, device="cuda") * 0.5).bfloat16()
+        y = tp.ag_gemm(x, w)
+        z = tp.gemm_rs(x, w)
+        torch.cuda.synchronize()
+        tp.check()
+        ref = _ref(x, w)
+        _close(y, ref, 512)
+        _close(z, ref, 512)
