@@ -257,7 +257,7 @@ flagcxResult_t dhStreamDestroy(flagcxStream_t s) {
 }
 flagcxResult_t dhStreamCopy(flagcxStream_t *out, void *old) {
   *out = new flagcxStream;
-  (*out)->base = *(cudaStream_t *)old;
+  (*out)->base = (cudaStream_t)old;  // the handle itself travels in the pointer, as in the reference's CUDA adaptor
   return flagcxSuccess;
 }
 flagcxResult_t dhStreamFree(flagcxStream_t s) { delete s; return flagcxSuccess; }

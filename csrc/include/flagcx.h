@@ -162,8 +162,9 @@ struct flagcxDeviceHandle {
   flagcxResult_t (*hostGetDevicePointer)(void **pDevice, void *pHost);
   flagcxResult_t (*streamCreate)(flagcxStream_t *stream);
   flagcxResult_t (*streamDestroy)(flagcxStream_t stream);
-  /* Wrap an existing cudaStream_t (pass its address); release the wrapper
-   * with streamFree, which leaves the CUDA stream alone. */
+  /* Wrap an existing cudaStream_t: pass the handle itself cast to void*
+   * (reference: flagcx/adaptor/device/cuda_adaptor.cc:190-196); release the
+   * wrapper with streamFree, which leaves the CUDA stream alone. */
   flagcxResult_t (*streamCopy)(flagcxStream_t *newStream, void *oldStream);
   flagcxResult_t (*streamFree)(flagcxStream_t stream);
   flagcxResult_t (*streamSynchronize)(flagcxStream_t stream);

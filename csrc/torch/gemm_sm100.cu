@@ -28,7 +28,8 @@
 //             tcgen05.commit releases smem stages / publishes the accumulator.
 //   warp 2    allocates and frees the 512 TMEM columns.
 //   warps 4-7 epilogue: tcgen05.ld (32 lanes x 32 columns per warp and step),
-//             fp32 -> bf16, 16-byte global stores (possibly into a peer).
+//             fp32 -> bf16, transposed through shared memory so that global
+//             stores (possibly into a peer) cover whole 128-byte lines.
 // Every wait (mbarrier, flag, counter) is bounded: after the limit the kernel
 // records an error, drains, frees its TMEM and returns.
 #include "../kernels/prims.cuh"
@@ -44,7 +45,8 @@ namespace {
 
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int EPI_BYTES = 4 * 32 * 128;  // per epilogue warp: 32 rows x 64 bf16
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr int THREADS = 256;
 constexpr uint32_t SPIN_LIMIT = 1u << 28;  // mbarrier polls before giving up (seconds of wall time)
 
@@ -181,7 +183,8 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
 
   // ------------------------------------------------------------ GEMM CTAs
   uint8_t *tiles = (uint8_t *)(((uintptr_t)smemRaw + 1023) & ~(uintptr_t)1023);
-  uint64_t *bars = (uint64_t *)(tiles + STAGES * STAGE_BYTES);
+  uint8_t *epiStage = tiles + STAGES * STAGE_BYTES;
+  uint64_t *bars = (uint64_t *)(epiStage + EPI_BYTES);
   uint64_t *fullBar = bars, *emptyBar = bars + STAGES, *tmemFull = bars + 2 * STAGES, *tmemEmpty = bars + 2 * STAGES + 2;
   uint32_t *tmemBaseSlot = (uint32_t *)(bars + 2 * STAGES + 4);
 
@@ -271,23 +274,29 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
       if (live) live = __all_sync(0xffffffffu, mbarWait(&tmemFull[buf], accPhase, err));
       if (live) {
         fenceAfter();
-        const int row = mb * BM + q * 32 + lane;
-        __nv_bfloat16 *dstRow;
+        // first row of this warp's 32-row band and where it goes
+        const int row0 = mb * BM + q * 32;
+        __nv_bfloat16 *dst0;
+        size_t ldd;
         if (MODE == FCX_GEMM_RS) {
-          const int owner = min(row / p.rowsPerRank, dc.nranks - 1), lrow = row - owner * p.rowsPerRank;
-          dstRow = (__nv_bfloat16 *)(dc.heap[owner] + p.stageOff) + ((size_t)dc.rank * p.rowsPerRank + lrow) * p.N;
+          const int owner = min(row0 / p.rowsPerRank, dc.nranks - 1), lrow0 = row0 - owner * p.rowsPerRank;
+          dst0 = (__nv_bfloat16 *)(dc.heap[owner] + p.stageOff) + ((size_t)dc.rank * p.rowsPerRank + lrow0) * p.N;
+          ldd = p.N;
         } else {
-          dstRow = (__nv_bfloat16 *)p.c + (size_t)row * p.ldc;
+          dst0 = (__nv_bfloat16 *)p.c + (size_t)row0 * p.ldc;
+          ldd = p.ldc;
         }
-        const bool rowOk = row < p.M;
+        // The accumulator comes out of TMEM one row per lane; a transposition through
+        // shared memory (32 rows x 128 bytes per warp, 16-byte chunks XOR-swizzled by row)
+        // turns that into stores where 8 lanes write one full 128-byte line of a row.
+        uint4 *stg = (uint4 *)(epiStage + (size_t)q * 32 * 128);
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
+        for (int c0 = 0; c0 < BN; c0 += 64) {
           uint32_t r[32];
-          tmemLd32(tmemBase + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c0), r);
-          tmemLdWait();
-          const int col = nb * BN + c0;
-          if (rowOk && col + 32 <= p.N) {
-            uint4 *d = (uint4 *)(dstRow + col);
+#pragma unroll
+          for (int h = 0; h < 2; h++) {
+            tmemLd32(tmemBase + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c0 + 32 * h), r);
+            tmemLdWait();
 #pragma unroll
             for (int v = 0; v < 4; v++) {
               uint4 o;
@@ -295,11 +304,25 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
               o.y = pack2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
               o.z = pack2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
               o.w = pack2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-              d[v] = o;
+              stg[lane * 8 + ((4 * h + v) ^ (lane & 7))] = o;
             }
-          } else if (rowOk) {
-            for (int j = 0; j < 32 && col + j < p.N; j++) dstRow[col + j] = __float2bfloat16_rn(__uint_as_float(r[j]));
           }
+          __syncwarp();
+          const int col = nb * BN + c0 + (lane & 7) * 8;
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            const int rr = i * 4 + (lane >> 3);
+            uint4 o = stg[rr * 8 + ((lane & 7) ^ (rr & 7))];
+            if (row0 + rr < p.M) {
+              __nv_bfloat16 *d = dst0 + (size_t)rr * ldd + col;
+              if (col + 8 <= p.N) *(uint4 *)d = o;
+              else {
+                const __nv_bfloat16 *e = (const __nv_bfloat16 *)&o;
+                for (int j = 0; j < 8 && col + j < p.N; j++) d[j] = e[j];
+              }
+            }
+          }
+          __syncwarp();
         }
         fenceBefore();
         __syncwarp();

@@ -392,7 +392,7 @@ class FLAGCXLibrary:
         """Wrap a ``torch.cuda.Stream`` (or a raw cudaStream_t integer)."""
         s = flagcxStream_t()
         raw = ctypes.c_void_p(getattr(old_stream, "cuda_stream", old_stream))
-        self.FLAGCX_CHECK(self.handler.contents.devHandle.contents.streamCopy(ctypes.byref(s), ctypes.byref(raw)))
+        self.FLAGCX_CHECK(self.handler.contents.devHandle.contents.streamCopy(ctypes.byref(s), raw))
         return s
 
     def adaptor_stream_free(self, stream):
