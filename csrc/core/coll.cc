@@ -300,7 +300,7 @@ flagcxResult_t launchP2pBatch(flagcxComm *c, const std::vector<PendingOp> &ops) 
     dops.push_back(d);
     maxBytes = std::max(maxBytes, bytes);
   }
-  int per = maxBytes <= (64u << 10) ? 1 : maxBytes <= (1u << 20) ? 4 : maxBytes <= (16u << 20) ? 16 : 32;
+  int per = maxBytes <= (64u << 10) ? 1 : maxBytes <= (1u << 20) ? 4 : maxBytes <= (8u << 20) ? 16 : 64;
   per = (int)envInt("P2P_CTAS", per);
   for (size_t i = 0; i < dops.size(); i += FCX_MAX_GROUP_OPS) {
     FcxP2pArgs g;

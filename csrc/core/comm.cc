@@ -118,7 +118,7 @@ flagcxResult_t commCreate(flagcxComm **out, int nranks, const BootstrapHandle &h
     }
     size_t stage = (size_t)((double)envInt("STAGE_BYTES", 128ll << 20) * heapScale);
     stage = std::max<size_t>(stage, 1u << 20) & ~(size_t)4095;
-    size_t chunk = (size_t)envInt("P2P_CHUNK_BYTES", 4ll << 20) & ~(size_t)4095;
+    size_t chunk = (size_t)envInt("P2P_CHUNK_BYTES", 16ll << 20) & ~(size_t)4095;
     size_t user = (size_t)((double)envInt("HEAP_USER_BYTES", 512ll << 20) * heapScale);
     size_t p2pOff = FCX_OFF_STAGE + 2 * stage;
     size_t userOff = p2pOff + (size_t)FCX_MAX_RANKS * 2 * chunk;
@@ -164,7 +164,7 @@ flagcxResult_t commCreate(flagcxComm **out, int nranks, const BootstrapHandle &h
   caps.nranks = nranks;
   caps.multicast = c->heap.mcBase != nullptr;
   caps.stageBytes = c->dev.stageBytes;
-  caps.maxCtas = (int)std::min<int64_t>(envInt("MAX_CTAS", 64), FCX_MAX_CTAS);
+  caps.maxCtas = (int)std::min<int64_t>(envInt("MAX_CTAS", 128), FCX_MAX_CTAS);
   c->tuner.reset(new Tuner(&c->bs, caps));
   *out = c.release();
   return flagcxSuccess;

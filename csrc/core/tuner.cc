@@ -27,9 +27,11 @@ int kindFromName(const std::string &s) {
 // ones for this class of machine (peer copy ~770 GB/s per direction, device
 // copy ~6.5 TB/s read+write); per-CTA figures bound what few CTAs can move.
 namespace {
+// Per-CTA NVLink figures come from a CTA-count sweep on two B200s: bus bandwidth kept growing up to
+// 128 CTAs (all-gather 215 / 324 / 400 / 446 GB/s with 16 / 32 / 64 / 128 CTAs), i.e. roughly 7 GB/s per CTA.
 constexpr double kLaunchUs = 2.2, kBarrierUs = 1.8, kLLUs = 1.6;
-constexpr double kLinkRate = 700e3, kCtaPushRate = 26e3, kCtaMmRate = 45e3;
-constexpr double kHbmRate = 5500e3, kCtaLocalRate = 90e3;
+constexpr double kLinkRate = 700e3, kCtaPushRate = 7e3, kCtaMmRate = 5e3;
+constexpr double kHbmRate = 5500e3, kCtaLocalRate = 60e3;
 
 double pushUs(double bytes, int nctas) { return bytes / std::min(kLinkRate, nctas * kCtaPushRate); }
 double mmUs(double bytes, int nctas) { return bytes / std::min(kLinkRate, nctas * kCtaMmRate); }
@@ -114,24 +116,24 @@ std::vector<Plan> Tuner::candidates(flagcxCommOp_t op, size_t bytes, flagcxDataT
   switch (op) {
     case flagcxCommOpAllReduce:
       if (!cast && bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_AR_LL, {1, 2, 4}, units, mx);
-      if ((bytes + 64) * n <= caps_.stageBytes && bytes <= (8u << 20)) addCtas(out, FCX_K_AR_ONESHOT, {2, 8, 16, 32}, units, mx);
-      if (bytes > 2048 || out.empty()) addCtas(out, FCX_K_AR_TWOSHOT, {8, 16, 32, 64}, units / n + 1, mx);
-      if (nvls && bytes >= 4096) addCtas(out, FCX_K_AR_NVLS, {4, 8, 16, 32}, units / n + 1, mx);
+      if ((bytes + 64) * n <= caps_.stageBytes && bytes <= (8u << 20)) addCtas(out, FCX_K_AR_ONESHOT, {2, 8, 16, 32, 64}, units, mx);
+      if (bytes > 2048 || out.empty()) addCtas(out, FCX_K_AR_TWOSHOT, {8, 16, 32, 64, 128}, units / n + 1, mx);
+      if (nvls && bytes >= 4096) addCtas(out, FCX_K_AR_NVLS, {8, 16, 32, 64, 128}, units / n + 1, mx);
       break;
     case flagcxCommOpReduceScatter:
-      addCtas(out, FCX_K_RS, {2, 8, 16, 32, 64}, units, mx);
-      if (nvls && bytes >= 4096) addCtas(out, FCX_K_RS_NVLS, {4, 8, 16, 32}, units, mx);
+      addCtas(out, FCX_K_RS, {2, 8, 16, 32, 64, 128}, units, mx);
+      if (nvls && bytes >= 4096) addCtas(out, FCX_K_RS_NVLS, {8, 16, 32, 64, 128}, units, mx);
       break;
     case flagcxCommOpAllGather:
-      addCtas(out, FCX_K_AG, {2, 8, 16, 32, 64}, units, mx);
-      if (caps_.multicast && n > 1 && bytes >= 4096) addCtas(out, FCX_K_AG_NVLS, {4, 8, 16, 32}, units, mx);
+      addCtas(out, FCX_K_AG, {2, 8, 16, 32, 64, 128}, units, mx);
+      if (caps_.multicast && n > 1 && bytes >= 4096) addCtas(out, FCX_K_AG_NVLS, {8, 16, 32, 64, 128}, units, mx);
       break;
-    case flagcxCommOpReduce: addCtas(out, FCX_K_REDUCE, {2, 8, 16, 32, 64}, units / n + 1, mx); break;
-    case flagcxCommOpBroadcast: addCtas(out, FCX_K_BCAST, {1, 4, 8, 16, 32}, units, mx); break;
-    case flagcxCommOpGather: addCtas(out, FCX_K_GATHER, {1, 4, 16, 32}, units, mx); break;
-    case flagcxCommOpScatter: addCtas(out, FCX_K_SCATTER, {1, 4, 16, 32}, units, mx); break;
-    case flagcxCommOpAlltoAll: addCtas(out, FCX_K_A2A, {2, 8, 16, 32, 64}, units, mx); break;
-    case flagcxCommOpAlltoAllv: addCtas(out, FCX_K_A2AV, {2, 8, 16, 32, 64}, units, mx); break;
+    case flagcxCommOpReduce: addCtas(out, FCX_K_REDUCE, {2, 8, 16, 32, 64, 128}, units / n + 1, mx); break;
+    case flagcxCommOpBroadcast: addCtas(out, FCX_K_BCAST, {1, 4, 16, 32, 64, 128}, units, mx); break;
+    case flagcxCommOpGather: addCtas(out, FCX_K_GATHER, {1, 4, 16, 64, 128}, units, mx); break;
+    case flagcxCommOpScatter: addCtas(out, FCX_K_SCATTER, {1, 4, 16, 64, 128}, units, mx); break;
+    case flagcxCommOpAlltoAll: addCtas(out, FCX_K_A2A, {2, 8, 16, 32, 64, 128}, units, mx); break;
+    case flagcxCommOpAlltoAllv: addCtas(out, FCX_K_A2AV, {2, 8, 16, 32, 64, 128}, units, mx); break;
     default: out.push_back({FCX_K_BARRIER, 1}); break;
   }
   return out;
@@ -159,6 +161,13 @@ void Tuner::decide(const Key &k, Search &s) {
 
 Plan Tuner::choose(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red, bool cast, bool *timed) {
   if (timed) *timed = false;
+  // FLAGCX_FORCE_CTAS overrides the CTA count of whatever variant is chosen (for experiments)
+  static const int forceCtas = (int)envInt("FORCE_CTAS", 0);
+  if (forceCtas > 0) {
+    Plan p = peek(op, bytes, dt, red, cast);
+    p.nctas = forceCtas;
+    return p;
+  }
   // Close the timing of the previous searched call.
   if (cur_) {
     cudaEventSynchronize(ev1_);

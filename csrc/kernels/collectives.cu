@@ -45,6 +45,14 @@ __device__ __forceinline__ void copyUnits(char *dst, const char *src, size_t byt
   if ((both & 15u) == 0) {
     size_t u = gtid;
     if (unitBytes == 16) {
+      // eight independent 16-byte loads in flight per thread, then eight stores
+      for (; u + 7 * gstride < nfull; u += 8 * gstride) {
+        uint4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = ld16(src + (u + i * gstride) * 16);
+#pragma unroll
+        for (int i = 0; i < 8; i++) st16(dst + (u + i * gstride) * 16, v[i]);
+      }
       for (; u + 3 * gstride < nfull; u += 4 * gstride) {
         uint4 v0 = ld16(src + u * 16), v1 = ld16(src + (u + gstride) * 16), v2 = ld16(src + (u + 2 * gstride) * 16),
               v3 = ld16(src + (u + 3 * gstride) * 16);

@@ -144,9 +144,22 @@ def build_torch_ext(force=False, verbose=False) -> Path:
     return out
 
 
+def build_tools(force=False, verbose=False) -> Path:
+    """Build build/bin/flagcx_perf, the MPI-free perf binary with the reference's command line."""
+    src = CSRC / "tools" / "flagcx_perf.cc"
+    out = ROOT / "build" / "bin" / "flagcx_perf"
+    out.parent.mkdir(parents=True, exist_ok=True)
+    if force or not out.exists() or out.stat().st_mtime < src.stat().st_mtime:
+        _run([NVCC, "-O2", "-std=c++17", "-x", "cu"] + ARCH + COMMON_INC + [str(src), "-o", str(out), "-ldl"])
+    if verbose:
+        print(f"built {out}")
+    return out
+
+
 def build_all(force=False, verbose=True):
     build_native(force=force, verbose=verbose)
     build_torch_ext(force=force, verbose=verbose)
+    build_tools(force=force, verbose=verbose)
 
 
 if __name__ == "__main__":
