@@ -52,11 +52,13 @@ static int64_t allocSignals(uint64_t comm, int64_t n) {
 }
 
 void bindGemm(py::module &m);  // gemm_bind.cpp
+void bindMoe(py::module &m);   // moe_bind.cpp
 
 void bindFused(py::module &m) {
   m.def("ring_exchange", &ringExchange, py::arg("comm"), py::arg("src"), py::arg("inbox"), py::arg("dst"), py::arg("slot"), py::arg("epoch"));
   m.def("alloc_signals", &allocSignals);
   bindGemm(m);
+  bindMoe(m);
 }
 
 }  // namespace fcxt

@@ -34,6 +34,8 @@
 // records an error, drains, frees its TMEM and returns.
 #include "../kernels/prims.cuh"
 
+#include <algorithm>
+#include <cstdlib>
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -131,8 +133,17 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 // Tile t of this CTA's sequence -> (row block, column block).  Row blocks are
 // visited in rotated order so that (AG) the local block comes first and (RS)
 // the blocks this rank owns come last.
-__device__ __forceinline__ void tileCoord(const FcxGemmParams &p, int t, int *mb, int *nb) {
-  const int nN = (p.N + BN - 1) / BN, nM = (p.M + BM - 1) / BM;
+__device__ __forceinline__ void tileCoord(const FcxGemmParams &p, int nM, int t, int *mb, int *nb) {
+  const int nN = (p.N + BN - 1) / BN;
+  if (p.group > 0) {
+    // Row blocks in bands of `group`; inside a band the row block changes fastest, so the CTAs of one wave
+    // share a few A row blocks and a few B column blocks and both stay in L2.
+    const int perBand = p.group * nN, band = t / perBand, first = band * p.group;
+    const int rowsHere = min(p.group, nM - first), within = t - band * perBand;
+    *mb = first + within % rowsHere;
+    *nb = within / rowsHere;
+    return;
+  }
   int g = t / nN;
   *nb = t % nN;
   *mb = (g + p.rotate) % nM;
@@ -188,7 +199,8 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
   uint64_t *fullBar = bars, *emptyBar = bars + STAGES, *tmemFull = bars + 2 * STAGES, *tmemEmpty = bars + 2 * STAGES + 2;
   uint32_t *tmemBaseSlot = (uint32_t *)(bars + 2 * STAGES + 4);
 
-  const int nN = (p.N + BN - 1) / BN, nM = (p.M + BM - 1) / BM;
+  const int Mrows = p.mPtr ? min(*p.mPtr, p.M) : p.M;  // the row count may live on the device
+  const int nN = (p.N + BN - 1) / BN, nM = (Mrows + BM - 1) / BM;
   const int nTiles = nN * nM, nK = (p.K + BK - 1) / BK;
   const int gemmCtas = (MODE == FCX_GEMM_AG) ? p.gemmCtas : gridDim.x;
 
@@ -214,7 +226,7 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
       bool ok = true;
       for (int t = blockIdx.x; t < nTiles && ok; t += gemmCtas) {
         int mb, nb;
-        tileCoord(p, t, &mb, &nb);
+        tileCoord(p, nM, t, &mb, &nb);
         if (MODE == FCX_GEMM_AG) {
           // rows of block mb must have arrived in the gathered buffer
           const uint64_t *flag = (const uint64_t *)(dc.heap[dc.rank] + p.flagOff) + mb;
@@ -270,7 +282,7 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
     bool live = true;
     for (int t = blockIdx.x; t < nTiles; t += gemmCtas) {
       int mb, nb;
-      tileCoord(p, t, &mb, &nb);
+      tileCoord(p, nM, t, &mb, &nb);
       if (live) live = __all_sync(0xffffffffu, mbarWait(&tmemFull[buf], accPhase, err));
       if (live) {
         fenceAfter();
@@ -313,8 +325,12 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
           for (int i = 0; i < 8; i++) {
             const int rr = i * 4 + (lane >> 3);
             uint4 o = stg[rr * 8 + ((lane & 7) ^ (rr & 7))];
-            if (row0 + rr < p.M) {
+            if (row0 + rr < Mrows) {
               __nv_bfloat16 *d = dst0 + (size_t)rr * ldd + col;
+              if (MODE == FCX_GEMM_ROWMAP) {
+                const int4 info = p.rowInfo[row0 + rr];
+                d = (__nv_bfloat16 *)(dc.heap[info.x] + p.combineOff) + ((size_t)info.y * p.topk + info.z) * p.N + col;
+              }
               if (col + 8 <= p.N) *(uint4 *)d = o;
               else {
                 const __nv_bfloat16 *e = (const __nv_bfloat16 *)&o;
@@ -347,6 +363,16 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
   __syncthreads();
   fenceAfter();
   if (warp == 2) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmemBase), "r"(512) : "memory");
+
+  if (MODE == FCX_GEMM_ROWMAP) {
+    // every row this CTA produced has been stored (possibly on peers): tell every rank that this CTA is done
+    __threadfence_system();
+    __syncthreads();
+    if ((int)threadIdx.x < dc.nranks) {
+      uint64_t *cnt = (uint64_t *)(dc.heap[threadIdx.x] + p.doneOff);
+      asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(cnt), "l"((uint64_t)1) : "memory");
+    }
+  }
 
   // ------------------------------------------------------------ RS: reduce the tiles this rank owns
   if (MODE == FCX_GEMM_RS) {
@@ -432,6 +458,16 @@ cudaError_t launch(const CUtensorMap &a, const CUtensorMap &b, const FcxGemmPara
   return cudaGetLastError();
 }
 
+// Row blocks per band of the tile order (FLAGCX_GEMM_TILE_GROUP; 0 = plain row-major order).
+int tileGroup() {
+  static int g = -1;
+  if (g < 0) {
+    const char *e = getenv("FLAGCX_GEMM_TILE_GROUP");
+    g = e ? std::max(0, atoi(e)) : 8;
+  }
+  return g;
+}
+
 int smCount() {
   static int n = 0;
   if (!n) {
@@ -452,10 +488,38 @@ extern "C" cudaError_t fcxGemmBf16(const void *a, const void *b, void *c, int M,
   CUtensorMap ma, mb;
   if (!makeMap(&ma, a, M, K, lda, BM) || !makeMap(&mb, b, N, K, ldb, BN)) return cudaErrorNotSupported;
   FcxGemmParams p{};
-  p.M = M; p.N = N; p.K = K; p.c = c; p.ldc = ldc; p.errFlag = errFlag; p.rotate = 0;
+  p.M = M; p.N = N; p.K = K; p.c = c; p.ldc = ldc; p.errFlag = errFlag; p.rotate = 0; p.group = tileGroup();
   FcxDevComm dc{};
   int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   return launch<FCX_GEMM_PLAIN>(ma, mb, p, dc, std::min(tiles, smCount()), s);
+}
+
+extern "C" cudaError_t fcxGemmBf16DynM(const void *a, const void *b, void *c, int Mmax, const int *mPtr, int N, int K, int lda, int ldb, int ldc,
+                                       int *errFlag, cudaStream_t s) {
+  if (K % 8 || lda % 8 || ldb % 8 || ldc % 8 || Mmax <= 0 || N <= 0 || K <= 0) return cudaErrorInvalidValue;
+  CUtensorMap ma, mb;
+  if (!makeMap(&ma, a, Mmax, K, lda, BM) || !makeMap(&mb, b, N, K, ldb, BN)) return cudaErrorNotSupported;
+  FcxGemmParams p{};
+  p.M = Mmax; p.N = N; p.K = K; p.c = c; p.ldc = ldc; p.errFlag = errFlag; p.mPtr = mPtr; p.group = tileGroup();
+  FcxDevComm dc{};
+  int tiles = ((Mmax + BM - 1) / BM) * ((N + BN - 1) / BN);
+  return launch<FCX_GEMM_PLAIN>(ma, mb, p, dc, std::min(tiles, smCount()), s);
+}
+
+extern "C" cudaError_t fcxGemmRowMapBf16(const FcxDevComm *dc, const void *a, const void *b, int Mmax, const int *mPtr, int N, int K, int lda,
+                                         int ldb, const void *rowInfo, size_t combineOff, size_t doneOff, int topk, int *errFlag,
+                                         int *gridOut, cudaStream_t s) {
+  if (K % 8 || lda % 8 || ldb % 8 || N % 8 || Mmax <= 0) return cudaErrorInvalidValue;
+  CUtensorMap ma, mb;
+  if (!makeMap(&ma, a, Mmax, K, lda, BM) || !makeMap(&mb, b, N, K, ldb, BN)) return cudaErrorNotSupported;
+  FcxGemmParams p{};
+  p.M = Mmax; p.N = N; p.K = K; p.c = nullptr; p.ldc = N; p.errFlag = errFlag; p.mPtr = mPtr;
+  p.group = tileGroup();
+  p.rowInfo = (const int4 *)rowInfo; p.combineOff = combineOff; p.doneOff = doneOff; p.topk = topk;
+  // a fixed grid: the receivers count one arrival per CTA of every rank
+  int grid = smCount();
+  if (gridOut) *gridOut = grid;
+  return launch<FCX_GEMM_ROWMAP>(ma, mb, p, *dc, grid, s);
 }
 
 extern "C" cudaError_t fcxAgGemmBf16(const FcxDevComm *dc, const void *aLocal, const void *gathered, size_t gatherOff, size_t flagOff,

@@ -7,12 +7,14 @@
 #define FCX_GEMM_PLAIN 0
 #define FCX_GEMM_AG 1
 #define FCX_GEMM_RS 2
+#define FCX_GEMM_ROWMAP 3
 
 struct FcxGemmParams {
   int M, N, K;          // C[M,N] = A[M,K] * B[N,K]^T, bf16 in, fp32 accumulate, bf16 out
   void *c;              // PLAIN/AG: C; RS: this rank's [M/n, N] result
   int ldc;
   int rotate;           // first row block (of 128 rows) this rank works on
+  int group;            // PLAIN/ROWMAP: row blocks per band of the tile order (0: row-major)
   int rowsPerRank;      // M / nranks (AG, RS)
   int gemmCtas;         // AG: CTAs [0, gemmCtas) compute, the rest move data
   const void *aLocal;   // AG: this rank's [rowsPerRank, K] block
@@ -21,6 +23,13 @@ struct FcxGemmParams {
   size_t flagOff;       // AG: heap offset of u64 flags [M/128]; RS: of u64 counters [rowsPerRank/128][ceil(N/256)]
   uint64_t epoch;       // 1-based use count of the flag/counter array that flagOff points to
   int *errFlag;         // device int, set to 1 when a bounded wait gave up
+  const int *mPtr;      // optional device-resident row count (<= M); rows beyond it are neither computed nor stored
+  // ROWMAP (mixture-of-experts combine): output row r goes to rank rowInfo[r].x, token rowInfo[r].y, choice rowInfo[r].z:
+  // heap[rank] + combineOff + ((token * topk + choice) * N) bf16 elements; afterwards every CTA adds 1 to the u64 counter
+  // at doneOff on every rank.
+  const int4 *rowInfo;
+  size_t combineOff, doneOff;
+  int topk;
 };
 
 #ifdef __cplusplus
@@ -31,6 +40,12 @@ cudaError_t fcxAgGemmBf16(const FcxDevComm *dc, const void *aLocal, const void *
                           void *c, int M, int N, int K, int ldb, int ldc, uint64_t epoch, int commCtas, int *errFlag, cudaStream_t s);
 cudaError_t fcxGemmRsBf16(const FcxDevComm *dc, const void *a, const void *b, void *out, size_t stageOff, size_t flagOff, int M, int N, int K,
                           int lda, int ldb, int ldc, uint64_t epoch, int *errFlag, cudaStream_t s);
+// c[Mmax,N] = a[*mPtr rows, K] @ b^T with the row count read on the device.
+cudaError_t fcxGemmBf16DynM(const void *a, const void *b, void *c, int Mmax, const int *mPtr, int N, int K, int lda, int ldb, int ldc,
+                            int *errFlag, cudaStream_t s);
+// Expert output GEMM with the combine all-to-all fused into its epilogue (see FcxGemmParams::rowInfo).
+cudaError_t fcxGemmRowMapBf16(const FcxDevComm *dc, const void *a, const void *b, int Mmax, const int *mPtr, int N, int K, int lda, int ldb,
+                              const void *rowInfo, size_t combineOff, size_t doneOff, int topk, int *errFlag, int *gridOut, cudaStream_t s);
 #ifdef __cplusplus
 }
 #endif

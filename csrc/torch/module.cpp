@@ -188,6 +188,15 @@ static void commAlltoAll(uint64_t comm, const at::Tensor &send, at::Tensor &recv
   StreamLayout st{cur()};
   FCX_OK(flagcxAlltoAll(send.data_ptr(), recv.data_ptr(), send.numel() / n, dtypeOf(send), c, (flagcxStream_t)&st));
 }
+// counts and displacements in elements, one entry per rank, host lists as in flagcxAlltoAllv
+static void commAlltoAllv(uint64_t comm, const at::Tensor &send, std::vector<int64_t> scounts, std::vector<int64_t> sdispls, at::Tensor &recv,
+                          std::vector<int64_t> rcounts, std::vector<int64_t> rdispls) {
+  StreamLayout st{cur()};
+  std::vector<size_t> sc(scounts.begin(), scounts.end()), sd(sdispls.begin(), sdispls.end()), rc(rcounts.begin(), rcounts.end()),
+      rd(rdispls.begin(), rdispls.end());
+  FCX_OK(flagcxAlltoAllv(send.data_ptr(), sc.data(), sd.data(), recv.data_ptr(), rc.data(), rd.data(), dtypeOf(send),
+                         (flagcxComm_t)(uintptr_t)comm, (flagcxStream_t)&st));
+}
 static void commBroadcast(uint64_t comm, at::Tensor &t, int64_t root) {
   StreamLayout st{cur()};
   FCX_OK(flagcxBroadcast(t.data_ptr(), t.data_ptr(), t.numel(), dtypeOf(t), (int)root, (flagcxComm_t)(uintptr_t)comm, (flagcxStream_t)&st));
@@ -225,6 +234,7 @@ PYBIND11_MODULE(_flagcx_torch, m) {
   m.def("comm_all_gather", &fcxt::commAllGather);
   m.def("comm_reduce_scatter", &fcxt::commReduceScatter, py::arg("comm"), py::arg("send"), py::arg("recv"), py::arg("op") = 0);
   m.def("comm_all_to_all", &fcxt::commAlltoAll);
+  m.def("comm_all_to_all_v", &fcxt::commAlltoAllv);
   m.def("comm_broadcast", &fcxt::commBroadcast);
   m.def("comm_counters", &fcxt::commCounters);
 }

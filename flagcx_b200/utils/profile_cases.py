@@ -7,7 +7,9 @@ couple of warm-up launches and three measured ones, and prints the
 CUDA-event time with the achieved fraction of the measured HBM copy rate
 (MEASURED_PEAKS.json, else 6.65 TB/s).  Cases: adamw, cross_entropy,
 layernorm_fwd, layernorm_bwd, bias_gelu, emu_allreduce (8 emulated ranks,
-two-shot kernel, one cooperative launch on this GPU), emu_allgather."""
+two-shot kernel, one cooperative launch on this GPU), emu_allgather, gemm
+(tcgen05 GEMM, against the measured cuBLAS rate), moe_dispatch and moe_layer
+(expert-parallel kernels on a one-rank communicator)."""
 from __future__ import annotations
 
 import argparse
@@ -106,6 +108,52 @@ def main():
         st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
         ms = timed(lambda: lib.call("flagcxEmuCollective", emu, op, kind, 16, s, r, count, 7, 7, ctypes.c_float(1.0), 0, 0, None, st))
         lib.call("flagcxEmuDestroy", emu)
+    elif args.case == "gemm":
+        # tensor-core bound: reported against the measured cuBLAS bf16 rate instead of the copy rate
+        M, N, K = 8192, 4096, 4096
+        a = (torch.randn(M, K, device="cuda") * 0.1).bfloat16()
+        b = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+        err = torch.zeros(1, dtype=torch.int32, device="cuda")
+        ms = timed(lambda: nat.gemm_nt(a, b, err))
+        pk = ROOT / "MEASURED_PEAKS.json"
+        tf_peak = json.loads(pk.read_text())["bf16_tflops"] if pk.exists() else 1590.0
+        tf = 2.0 * M * N * K / (ms * 1e-3) / 1e12
+        print(json.dumps({"case": "gemm", "shape": [M, N, K], "ms": round(ms, 4), "tflops": round(tf, 1),
+                          "fraction_of_gemm_peak": round(tf / tf_peak, 3), "peak": label, "err": int(err.item())}))
+        return
+    elif args.case in ("moe_dispatch", "moe_layer"):
+        # one-rank communicator: the dispatch kernel (count, exchange, push), the device-row-count GEMMs,
+        # the ROWMAP epilogue and the combine kernel all run, with this GPU as its own peer
+        import os
+        os.environ.setdefault("FLAGCX_HEAP_USER_BYTES", "1G")
+        from flagcx_b200.parallel.ep import ExpertParallelContext
+        from flagcx_b200.wrapper import FLAGCXLibrary
+        lib = FLAGCXLibrary()
+        comm = lib.flagcxCommInitRank(1, lib.flagcxGetUniqueId(), 0)
+        T, H, F, K = 16384, 4096, 2048, 2
+        ep = ExpertParallelContext(comm.value, 1, 0, T, H, F, K)
+        x = torch.randn(T, H, device="cuda").bfloat16()
+        idx = torch.zeros(T, K, dtype=torch.int32, device="cuda")
+        wts = torch.rand(T, K, device="cuda")
+        w1 = (torch.randn(2 * F, H, device="cuda") * 0.02).bfloat16()
+        w2 = (torch.randn(H, F, device="cuda") * 0.02).bfloat16()
+        if args.case == "moe_dispatch":
+            state = {"calls": 0}
+
+            def disp():
+                par, epoch = state["calls"] & 1, (state["calls"] >> 1) + 1
+                state["calls"] += 1
+                nat.moe_dispatch(comm.value, x, idx, ep.count_mat[par], ep.count_flags[par], ep.recv[par], ep.info[par], ep.disp_done[par],
+                                 epoch, ep.slot, ep.local_counts, ep.recv_total, ep.err, ep.dispatch_ctas)
+            ms = timed(disp)
+            nbytes = T * K * H * 2 * 2  # every (token, choice) row read once and written once
+        else:
+            ms = timed(lambda: ep.forward(x, idx, wts, w1, w2))
+            nbytes = T * K * H * 2 * 2
+        torch.cuda.synchronize()
+        ep.check()
+        del ep
+        lib.flagcxCommDestroy(comm)
     else:
         raise SystemExit(f"unknown case {args.case}")
     gbs = nbytes / (ms * 1e-3)
