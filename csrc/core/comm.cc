@@ -141,6 +141,7 @@ flagcxResult_t commCreate(flagcxComm **out, int nranks, const BootstrapHandle &h
     d.mcHeap = c->heap.mcBase;
     d.heapBytes = c->heap.bytes;
     d.stageBytes = stage;
+    d.pipeBytes = (unsigned int)std::min<int64_t>(envInt("PIPE_BYTES", 8ll << 20), 1ll << 30);
     d.p2pOff = p2pOff;
     d.p2pChunkBytes = chunk;
     d.userOff = userOff;
@@ -164,6 +165,7 @@ flagcxResult_t commCreate(flagcxComm **out, int nranks, const BootstrapHandle &h
   caps.nranks = nranks;
   caps.multicast = c->heap.mcBase != nullptr;
   caps.stageBytes = c->dev.stageBytes;
+  caps.pipeBytes = c->dev.pipeBytes;
   caps.maxCtas = (int)std::min<int64_t>(envInt("MAX_CTAS", 128), FCX_MAX_CTAS);
   c->tuner.reset(new Tuner(&c->bs, caps));
   *out = c.release();

@@ -27,15 +27,28 @@ int kindFromName(const std::string &s) {
 // ones for this class of machine (peer copy ~770 GB/s per direction, device
 // copy ~6.5 TB/s read+write); per-CTA figures bound what few CTAs can move.
 namespace {
-// Per-CTA NVLink figures come from a CTA-count sweep on two B200s: bus bandwidth kept growing up to
-// 128 CTAs (all-gather 215 / 324 / 400 / 446 GB/s with 16 / 32 / 64 / 128 CTAs), i.e. roughly 7 GB/s per CTA.
-constexpr double kLaunchUs = 2.2, kBarrierUs = 1.8, kLLUs = 1.6;
-constexpr double kLinkRate = 700e3, kCtaPushRate = 7e3, kCtaMmRate = 5e3;
+// Per-CTA figures come from a copy probe on two B200s: one CTA of 512 threads moves about 45 GB/s to a peer
+// with plain loads and stores and sixteen CTAs saturate a direction of NVLink at about 685 GB/s, both
+// directions at once; a CTA copies about 60 GB/s inside its own memory.  Large messages run as a software
+// pipeline over sub-chunks in which about half of the CTAs are on the link and half on local memory.
+constexpr double kLaunchUs = 2.2, kBarrierUs = 1.8, kLLUs = 1.6, kPipeBarrierUs = 0.4;
+constexpr double kLinkRate = 680e3, kCtaPushRate = 40e3, kCtaMmRate = 30e3;
 constexpr double kHbmRate = 5500e3, kCtaLocalRate = 60e3;
 
-double pushUs(double bytes, int nctas) { return bytes / std::min(kLinkRate, nctas * kCtaPushRate); }
-double mmUs(double bytes, int nctas) { return bytes / std::min(kLinkRate, nctas * kCtaMmRate); }
-double localUs(double bytes, int nctas) { return bytes / std::min(kHbmRate, nctas * kCtaLocalRate); }
+double pushUs(double bytes, double nctas) { return bytes / std::min(kLinkRate, std::max(1.0, nctas) * kCtaPushRate); }
+double mmUs(double bytes, double nctas) { return bytes / std::min(kLinkRate, std::max(1.0, nctas) * kCtaMmRate); }
+double localUs(double bytes, double nctas) { return bytes / std::min(kHbmRate, std::max(1.0, nctas) * kCtaLocalRate); }
+
+// A kind with `depth` phases that moves linkBytes over NVLink and localBytes inside the GPU, cut into
+// sub-chunks of pipeBytes / (n-1) per piece.
+double pipelinedUs(double linkBytes, double localBytes, double pieceBytes, int depth, bool mm, int c, const TunerCaps &caps) {
+  const double n = caps.nranks, sub = std::max(16384.0, (double)(caps.pipeBytes ? caps.pipeBytes : (8u << 20)) / std::max(1.0, n - 1));
+  const double chunks = std::max(1.0, std::ceil(pieceBytes / sub));
+  auto link = [&](double ctas) { return mm ? mmUs(linkBytes, ctas) : pushUs(linkBytes, ctas); };
+  if (chunks <= 1.0) return kLaunchUs + (depth - 1) * kBarrierUs + link(c) + localUs(localBytes, c);
+  const double l = link(c * 0.5), h = localUs(localBytes, c * 0.5);
+  return kLaunchUs + kBarrierUs + (chunks + depth - 2) * kPipeBarrierUs + std::max(l, h) + (link(c) + localUs(localBytes, c)) / chunks;
+}
 }  // namespace
 
 double estimateUs(const Plan &p, flagcxCommOp_t, size_t bytesIn, int, const TunerCaps &caps) {
@@ -45,18 +58,18 @@ double estimateUs(const Plan &p, flagcxCommOp_t, size_t bytesIn, int, const Tune
     case FCX_K_BARRIER: return kLaunchUs + kBarrierUs;
     case FCX_K_AR_LL: return kLaunchUs + kLLUs + pushUs(2 * (n - 1) * b, c) + localUs(2 * n * b, c);
     case FCX_K_AR_ONESHOT: return kLaunchUs + kBarrierUs + pushUs((n - 1) * b, c) + localUs((n + 1) * b, c);
-    case FCX_K_AR_TWOSHOT: return kLaunchUs + 2 * kBarrierUs + pushUs(2 * (n - 1) / n * b, c) + localUs(4 * b, c);
-    case FCX_K_AR_NVLS: return kLaunchUs + 2 * kBarrierUs + mmUs(b, c) + localUs(4 * b, c);
-    case FCX_K_REDUCE: return kLaunchUs + 2 * kBarrierUs + pushUs(2 * (n - 1) / n * b, c) + localUs(3 * b, c);
+    case FCX_K_AR_TWOSHOT: return pipelinedUs(2 * (n - 1) / n * b, 4 * b, b / n, 3, false, c, caps);
+    case FCX_K_AR_NVLS: return pipelinedUs(2 * b / n, 4 * b, b / n, 3, true, c, caps);
+    case FCX_K_REDUCE: return pipelinedUs(2 * (n - 1) / n * b, 3 * b, b / n, 3, false, c, caps);
     // below, b is the per-rank piece
-    case FCX_K_RS: return kLaunchUs + kBarrierUs + pushUs((n - 1) * b, c) + localUs((n + 1) * b, c);
-    case FCX_K_RS_NVLS: return kLaunchUs + kBarrierUs + mmUs(n * b, c) + localUs(2 * n * b, c);
-    case FCX_K_AG: return kLaunchUs + kBarrierUs + pushUs((n - 1) * b, c) + localUs(2 * n * b, c);
-    case FCX_K_AG_NVLS: return kLaunchUs + kBarrierUs + mmUs((n - 1) * b, c) + localUs(2 * n * b, c);
-    case FCX_K_BCAST: return kLaunchUs + kBarrierUs + (caps.multicast ? mmUs(b, c) : pushUs((n - 1) * b, c)) + localUs(2 * b, c);
+    case FCX_K_RS: return pipelinedUs((n - 1) * b, (n + 1) * b, b, 2, false, c, caps);
+    case FCX_K_RS_NVLS: return pipelinedUs(b, 2 * n * b, b, 2, true, c, caps);
+    case FCX_K_AG: return pipelinedUs((n - 1) * b, 2 * n * b, b, 2, false, c, caps);
+    case FCX_K_AG_NVLS: return pipelinedUs(b, 2 * n * b, b, 2, true, c, caps);
+    case FCX_K_BCAST: return pipelinedUs(caps.multicast ? b : (n - 1) * b, 2 * b, b, 2, caps.multicast, c, caps);
     case FCX_K_GATHER:
-    case FCX_K_SCATTER: return kLaunchUs + kBarrierUs + pushUs((n - 1) * b, c) + localUs(2 * b, c);
-    case FCX_K_A2A:
+    case FCX_K_SCATTER: return pipelinedUs((n - 1) * b, 2 * b, b, 2, false, c, caps);
+    case FCX_K_A2A: return pipelinedUs((n - 1) * b, 2 * n * b, b, 2, false, c, caps);
     case FCX_K_A2AV: return kLaunchUs + 2 * kBarrierUs + pushUs((n - 1) * b, c) + localUs(2 * n * b, c);
     default: return 1e9;
   }

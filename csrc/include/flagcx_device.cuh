@@ -95,6 +95,84 @@ __device__ __forceinline__ bool fcx_barrier(const DevComm &dc, int slot, uint64_
   return __syncthreads_and(ok);
 }
 
+// ---------------------------------------------------------------- bulk-copy engine (TMA) transfers
+//
+// One thread streams a large block between this GPU's memory and a peer's through a ring in shared memory:
+// cp.async.bulk global -> shared (completion on an mbarrier), then cp.async.bulk shared -> global (bulk groups).
+// No load is multicast.  The other threads of the CTA stay free (or idle): one SM sustains a high NVLink rate
+// without spending its load/store units.  Requirements: both addresses 16-byte aligned, `bytes` a multiple of 16.
+//
+//   __shared__ (or dynamic) ring of FCX_BULK_STAGES x FCX_BULK_CHUNK bytes, 128-byte aligned, and FCX_BULK_STAGES mbarriers;
+//   fcx_bulk_init(ring) once by one thread, then __syncthreads();
+//   fcx_bulk_copy(ring, dst, src, bytes, &err) by that thread, as often as needed;
+//   the data is complete at the destination when the call returns; publish with fcx_bulk_release_fence() + fcx_signal.
+#define FCX_BULK_STAGES 6
+#define FCX_BULK_CHUNK 32768
+
+struct fcx_bulk_ring {
+  unsigned char *buf;   // FCX_BULK_STAGES * FCX_BULK_CHUNK bytes of shared memory
+  uint64_t *bars;       // FCX_BULK_STAGES mbarriers in shared memory
+  uint32_t phases;      // bit s: parity of the next completion on stage s
+};
+
+__device__ __forceinline__ uint32_t fcx_smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void fcx_bulk_init(fcx_bulk_ring &r, void *buf, uint64_t *bars) {
+  r.buf = (unsigned char *)buf;
+  r.bars = bars;
+  r.phases = 0;
+  for (int s = 0; s < FCX_BULK_STAGES; s++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(fcx_smem_addr(&bars[s])));
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void fcx_bulk_load_(fcx_bulk_ring &r, int stage, const char *src, uint32_t bytes) {
+  const uint32_t bar = fcx_smem_addr(&r.bars[stage]), dst = fcx_smem_addr(r.buf + (size_t)stage * FCX_BULK_CHUNK);
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes),
+               "r"(bar) : "memory");
+}
+
+// Bounded wait on a stage's mbarrier; false = gave up (sets *err).
+__device__ __forceinline__ bool fcx_bulk_wait_(fcx_bulk_ring &r, int stage, volatile int *err) {
+  const uint32_t bar = fcx_smem_addr(&r.bars[stage]), parity = (r.phases >> stage) & 1u;
+  uint32_t done = 0;
+  for (uint32_t spin = 0; spin < (1u << 26); spin++) {
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) { r.phases ^= 1u << stage; return true; }
+  }
+  *err = 1;
+  return false;
+}
+
+// One thread.  Copies src -> dst through the ring; either side may be a peer's memory.
+__device__ __forceinline__ bool fcx_bulk_copy(fcx_bulk_ring &r, void *dst, const void *src, size_t bytes, volatile int *err) {
+  const char *s = (const char *)src;
+  char *d = (char *)dst;
+  const int n = (int)((bytes + FCX_BULK_CHUNK - 1) / FCX_BULK_CHUNK);
+  auto sizeOf = [&](int c) { return (uint32_t)min((size_t)FCX_BULK_CHUNK, bytes - (size_t)c * FCX_BULK_CHUNK); };
+  int ld = 0;
+  bool ok = true;
+  for (; ld < n && ld < FCX_BULK_STAGES - 2; ld++) fcx_bulk_load_(r, ld % FCX_BULK_STAGES, s + (size_t)ld * FCX_BULK_CHUNK, sizeOf(ld));
+  for (int c = 0; c < n; c++) {
+    const int st = c % FCX_BULK_STAGES;
+    if (!fcx_bulk_wait_(r, st, err)) { ok = false; break; }
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(d + (size_t)c * FCX_BULK_CHUNK),
+                 "r"(fcx_smem_addr(r.buf + (size_t)st * FCX_BULK_CHUNK)), "r"(sizeOf(c)) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    if (ld < n) {
+      // the stage about to be refilled belongs to chunk c-2, whose store has been read once at most one group is pending
+      asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      fcx_bulk_load_(r, ld % FCX_BULK_STAGES, s + (size_t)ld * FCX_BULK_CHUNK, sizeOf(ld));
+      ld++;
+    }
+  }
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  return ok;
+}
+// Orders the bulk engine's writes before a following release store of the same thread.
+__device__ __forceinline__ void fcx_bulk_release_fence() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
 // NVSwitch: sum the same 16 bytes of every rank's heap (4 floats / 8 bf16) and broadcast 16 bytes to all.
 __device__ __forceinline__ uint4 fcx_multimem_sum_f32x4(const DevComm &dc, size_t heapOffset) {
   return fcxdev::Mm<float>::ldReduce(dc.mcHeap + heapOffset, 0);

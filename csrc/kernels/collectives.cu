@@ -106,6 +106,39 @@ __device__ __forceinline__ void copyFromSlot(char *user, const char *slot, size_
   copyUnits(user, slot, bytes, unitBytes, gtid, gstride);
 }
 
+
+// ---------------------------------------------------------------- software pipeline over sub-chunks
+//
+// Large messages are cut into sub-chunks so that the phases of a collective overlap: while sub-chunk i is
+// pushed over NVLink, sub-chunk i-1 is reduced or copied out of local memory (and i-2 copied out, for the
+// three-phase kinds).  One cross-GPU CTA barrier per iteration orders phase k of a sub-chunk before phase
+// k+1 of the same sub-chunk.  Odd CTAs run the phases of an iteration in reverse order, so that at any time
+// about half of the CTAs are on the link and the others on local memory.  Sixteen CTAs saturate a
+// direction of NVLink; the rest of the grid hides the local traffic and the barrier latency behind it.
+__device__ __forceinline__ size_t subLen(size_t total, size_t sub, int c, size_t *lo) {
+  *lo = (size_t)c * sub;
+  return *lo < total ? min(sub, total - *lo) : 0;
+}
+__device__ __forceinline__ size_t pipeBytesOf(const FcxDevComm &dc) { return dc.pipeBytes ? (size_t)dc.pipeBytes : ((size_t)8 << 20); }
+
+template <int DEPTH, class FA, class FB, class FC>
+__device__ __forceinline__ bool pipelined(const FcxDevComm &dc, int cta, uint64_t seq, int chunks, FA stageA, FB stageB, FC stageC) {
+  const int iters = chunks + DEPTH - 1;
+  for (int i = 0; i < iters; i++) {
+    if (cta & 1) {
+      if (DEPTH == 3 && i >= 2 && i - 2 < chunks) stageC(i - 2);
+      if (i >= 1 && i - 1 < chunks) stageB(i - 1);
+      if (i < chunks) stageA(i);
+    } else {
+      if (i < chunks) stageA(i);
+      if (i >= 1 && i - 1 < chunks) stageB(i - 1);
+      if (DEPTH == 3 && i >= 2 && i - 2 < chunks) stageC(i - 2);
+    }
+    if (i + 1 < iters && !ctaBarrier(dc, cta, barrierValue(seq, 1 + (unsigned)i), seq)) return false;
+  }
+  return true;
+}
+
 // ---------------------------------------------------------------- LL one-shot all-reduce
 
 // A 16-byte LL line carries 8 payload bytes and two copies of the 32-bit
@@ -330,48 +363,57 @@ __device__ void fcxCollBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta,
         size_t lo = (size_t)p * sliceElems;
         return lo >= a.count ? 0 : min(sliceElems, a.count - lo);
       };
+      // sub-chunks of every slice, in units
+      const size_t cu = max((size_t)1024, pipeBytesOf(dc) / (size_t)max(1, n - 1) / 16);
+      const int chunks = (int)max((size_t)1, (sliceUnits + cu - 1) / cu);
+      auto rangeOf = [&](int p, int c, size_t *loU) -> size_t {  // elements of slice p that fall into sub-chunk c
+        *loU = (size_t)c * cu;
+        size_t ne = elemsOf(p), lo = *loU * G;
+        return lo >= ne ? 0 : min(cu * G, ne - lo);
+      };
       // phase 1: slice p of my vector goes to rank p
-      for (int k = 1; k < n; k++) {
-        int p = (me + k) % n;
-        size_t ne = elemsOf(p);
-        if (ne)
-          copyToSlot(stagePtr(dc, p, seq) + (size_t)me * slotA, send + (size_t)p * sliceElems * ESI, ne * ESI, INB,
-                     gtid, gstride);
-      }
-      if (!ctaBarrier(dc, cta, barrierValue(seq, 1), seq)) break;
+      auto push = [&](int c) {
+        for (int k = 1; k < n; k++) {
+          int p = (me + k) % n;
+          size_t loU, ne = rangeOf(p, c, &loU);
+          if (ne)
+            copyToSlot(stagePtr(dc, p, seq) + (size_t)me * slotA + loU * INB, send + ((size_t)p * sliceElems + loU * G) * ESI, ne * ESI,
+                       INB, gtid, gstride);
+        }
+      };
       // phase 2: combine my slice, hand the result to whoever needs it
-      {
-        size_t ne = elemsOf(me);
+      auto combine = [&](int c) {
+        size_t loU, ne = rangeOf(me, c, &loU);
+        if (!ne) return;
         char *dstSlots[FCX_MAX_RANKS];
         int nd = 0;
         char *dstUser = nullptr;
         if (toRootOnly) {
-          if (me == a.root) dstUser = recv + (size_t)me * sliceElems * ESO;
-          else dstSlots[nd++] = stagePtr(dc, a.root, seq) + (size_t)n * slotA + (size_t)me * slotB;
+          if (me == a.root) dstUser = recv + ((size_t)me * sliceElems + loU * G) * ESO;
+          else dstSlots[nd++] = stagePtr(dc, a.root, seq) + (size_t)n * slotA + (size_t)me * slotB + loU * OUTB;
         } else {
-          dstUser = recv + (size_t)me * sliceElems * ESO;
+          dstUser = recv + ((size_t)me * sliceElems + loU * G) * ESO;
           for (int k = 1; k < n; k++) {
             int p = (me + k) % n;
-            dstSlots[nd++] = stagePtr(dc, p, seq) + (size_t)n * slotA + (size_t)me * slotB;
+            dstSlots[nd++] = stagePtr(dc, p, seq) + (size_t)n * slotA + (size_t)me * slotB + loU * OUTB;
           }
         }
-        if (ne) {
-          const char *own = send + (size_t)me * sliceElems * ESI;
-          reduceUnits<TIn, TOut, G>(dc, a, own, aligned16(own), stagePtr(dc, me, seq), slotA, ne, dstUser,
-                                    dstUser && aligned16(dstUser), dstSlots, nd, gtid, gstride);
-        }
-      }
-      if (!ctaBarrier(dc, cta, barrierValue(seq, 2), seq)) break;
+        const char *own = send + ((size_t)me * sliceElems + loU * G) * ESI;
+        reduceUnits<TIn, TOut, G>(dc, a, own, aligned16(own), stagePtr(dc, me, seq) + loU * INB, slotA, ne, dstUser,
+                                  dstUser && aligned16(dstUser), dstSlots, nd, gtid, gstride);
+      };
       // phase 3: collect the other ranks' finished slices
-      if (!toRootOnly || me == a.root) {
+      auto collect = [&](int c) {
+        if (toRootOnly && me != a.root) return;
         for (int k = 1; k < n; k++) {
           int p = (me + k) % n;
-          size_t ne = elemsOf(p);
+          size_t loU, ne = rangeOf(p, c, &loU);
           if (ne)
-            copyFromSlot(recv + (size_t)p * sliceElems * ESO,
-                         stagePtr(dc, me, seq) + (size_t)n * slotA + (size_t)p * slotB, ne * ESO, OUTB, gtid, gstride);
+            copyFromSlot(recv + ((size_t)p * sliceElems + loU * G) * ESO,
+                         stagePtr(dc, me, seq) + (size_t)n * slotA + (size_t)p * slotB + loU * OUTB, ne * ESO, OUTB, gtid, gstride);
         }
-      }
+      };
+      pipelined<3>(dc, cta, seq, chunks, push, combine, collect);
       break;
     }
 
@@ -399,56 +441,70 @@ __device__ void fcxCollBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta,
           return lo >= a.count ? 0 : min(sliceElems, a.count - lo);
         };
         const size_t srcStride = isRS ? a.sendStride : sliceElems;
-        for (int p = 0; p < n; p++) {
-          size_t ne = elemsOf(p);
-          if (ne)
-            copyToSlot(stagePtr(dc, me, seq) + (size_t)p * sliceBytes, send + (size_t)p * srcStride * ESI, ne * ESI, 16,
-                       gtid, gstride);
-        }
-        if (!ctaBarrier(dc, cta, barrierValue(seq, 1), seq)) break;
+        const size_t cu = max((size_t)1024, pipeBytesOf(dc) / (size_t)max(1, n - 1) / 16);  // units of a slice per sub-chunk
+        const int chunks = (int)max((size_t)1, (sliceBytes / 16 + cu - 1) / cu);
+        auto rangeOf = [&](int p, int c, size_t *loU) -> size_t {
+          *loU = (size_t)c * cu;
+          size_t ne = elemsOf(p), lo = *loU * G;
+          return lo >= ne ? 0 : min(cu * G, ne - lo);
+        };
         const size_t stageOff = FCX_OFF_STAGE + (size_t)(seq & 1) * dc.stageBytes;
         char *mcSlice = dc.mcHeap + stageOff + (size_t)me * sliceBytes;
-        const size_t myElems = elemsOf(me);
-        const size_t myUnits = (myElems + G - 1) / G;
-        if (isRS) {
-          bool alR = aligned16(recv);
-          size_t u = gtid;
-          for (; u + 3 * gstride < myUnits; u += 4 * gstride) {
-            uint4 r[4];
+        const bool alR = aligned16(recv);
+        auto copyIn = [&](int c) {
+          for (int p = 0; p < n; p++) {
+            size_t loU, ne = rangeOf(p, c, &loU);
+            if (ne)
+              copyToSlot(stagePtr(dc, me, seq) + (size_t)p * sliceBytes + loU * 16, send + ((size_t)p * srcStride + loU * G) * ESI, ne * ESI,
+                         16, gtid, gstride);
+          }
+        };
+        auto reduce = [&](int c) {
+          size_t loU, ne = rangeOf(me, c, &loU);
+          if (!ne) return;
+          const size_t myUnits = (ne + G - 1) / G;
+          char *mcp = mcSlice + loU * 16;
+          if (isRS) {
+            char *out = recv + loU * 16;
+            size_t u = gtid;
+            for (; u + 3 * gstride < myUnits; u += 4 * gstride) {
+              uint4 r[4];
 #pragma unroll
-            for (int i = 0; i < 4; i++) r[i] = Mm<TIn>::ldReduce(mcSlice + (u + i * gstride) * 16, a.redop);
+              for (int i = 0; i < 4; i++) r[i] = Mm<TIn>::ldReduce(mcp + (u + i * gstride) * 16, a.redop);
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-              size_t uu = u + i * gstride;
-              uint4 f = mmFinish<TIn>(r[i], a.redop, n, a.scale);
-              storeUnit<TIn, G>(recv + uu * 16, alR, (int)min((size_t)G, myElems - uu * G), &f);
+              for (int i = 0; i < 4; i++) {
+                size_t uu = u + i * gstride;
+                uint4 f = mmFinish<TIn>(r[i], a.redop, n, a.scale);
+                storeUnit<TIn, G>(out + uu * 16, alR, (int)min((size_t)G, ne - uu * G), &f);
+              }
             }
+            for (; u < myUnits; u += gstride) {
+              uint4 f = mmFinish<TIn>(Mm<TIn>::ldReduce(mcp + u * 16, a.redop), a.redop, n, a.scale);
+              storeUnit<TIn, G>(out + u * 16, alR, (int)min((size_t)G, ne - u * G), &f);
+            }
+            return;
           }
-          for (; u < myUnits; u += gstride) {
-            uint4 f = mmFinish<TIn>(Mm<TIn>::ldReduce(mcSlice + u * 16, a.redop), a.redop, n, a.scale);
-            storeUnit<TIn, G>(recv + u * 16, alR, (int)min((size_t)G, myElems - u * G), &f);
-          }
-          break;
-        }
-        {
           size_t u = gtid;
           for (; u + 3 * gstride < myUnits; u += 4 * gstride) {
             uint4 r[4];
 #pragma unroll
-            for (int i = 0; i < 4; i++) r[i] = Mm<TIn>::ldReduce(mcSlice + (u + i * gstride) * 16, a.redop);
+            for (int i = 0; i < 4; i++) r[i] = Mm<TIn>::ldReduce(mcp + (u + i * gstride) * 16, a.redop);
 #pragma unroll
-            for (int i = 0; i < 4; i++) mmStore(mcSlice + (u + i * gstride) * 16, mmFinish<TIn>(r[i], a.redop, n, a.scale));
+            for (int i = 0; i < 4; i++) mmStore(mcp + (u + i * gstride) * 16, mmFinish<TIn>(r[i], a.redop, n, a.scale));
           }
           for (; u < myUnits; u += gstride)
-            mmStore(mcSlice + u * 16, mmFinish<TIn>(Mm<TIn>::ldReduce(mcSlice + u * 16, a.redop), a.redop, n, a.scale));
-        }
-        if (!ctaBarrier(dc, cta, barrierValue(seq, 2), seq)) break;
-        for (int p = 0; p < n; p++) {
-          size_t ne = elemsOf(p);
-          if (ne)
-            copyFromSlot(recv + (size_t)p * sliceElems * ESI, stagePtr(dc, me, seq) + (size_t)p * sliceBytes, ne * ESI, 16,
-                         gtid, gstride);
-        }
+            mmStore(mcp + u * 16, mmFinish<TIn>(Mm<TIn>::ldReduce(mcp + u * 16, a.redop), a.redop, n, a.scale));
+        };
+        auto copyOut = [&](int c) {
+          for (int p = 0; p < n; p++) {
+            size_t loU, ne = rangeOf(p, c, &loU);
+            if (ne)
+              copyFromSlot(recv + ((size_t)p * sliceElems + loU * G) * ESI, stagePtr(dc, me, seq) + (size_t)p * sliceBytes + loU * 16,
+                           ne * ESI, 16, gtid, gstride);
+          }
+        };
+        if (isRS) pipelined<2>(dc, cta, seq, chunks, copyIn, reduce, copyOut);
+        else pipelined<3>(dc, cta, seq, chunks, copyIn, reduce, copyOut);
       }
       break;
     }
@@ -456,15 +512,32 @@ __device__ void fcxCollBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta,
     case FCX_K_RS: {
       const size_t bytes = a.count * ESI;
       const size_t slot = (bytes + INB - 1) / INB * INB;
-      for (int k = 1; k < n; k++) {
-        int p = (me + k) % n;
-        copyToSlot(stagePtr(dc, p, seq) + (size_t)me * slot, send + (size_t)p * a.sendStride * ESI, bytes, INB, gtid,
-                   gstride);
-      }
-      if (!ctaBarrier(dc, cta, barrierValue(seq, 1), seq)) break;
-      const char *own = send + (size_t)me * a.sendStride * ESI;
-      reduceUnits<TIn, TOut, G>(dc, a, own, aligned16(own), stagePtr(dc, me, seq), slot, a.count, recv, aligned16(recv),
-                                nullptr, 0, gtid, gstride);
+      const size_t units = (a.count + G - 1) / G;
+      const size_t cu = max((size_t)1024, pipeBytesOf(dc) / (size_t)max(1, n - 1) / INB);
+      const int chunks = (int)max((size_t)1, (units + cu - 1) / cu);
+      auto rangeOf = [&](int c, size_t *loU) -> size_t {
+        *loU = (size_t)c * cu;
+        size_t lo = *loU * G;
+        return lo >= a.count ? 0 : min(cu * G, a.count - lo);
+      };
+      auto push = [&](int c) {
+        size_t loU, ne = rangeOf(c, &loU);
+        if (!ne) return;
+        for (int k = 1; k < n; k++) {
+          int p = (me + k) % n;
+          copyToSlot(stagePtr(dc, p, seq) + (size_t)me * slot + loU * INB, send + ((size_t)p * a.sendStride + loU * G) * ESI, ne * ESI, INB,
+                     gtid, gstride);
+        }
+      };
+      auto combine = [&](int c) {
+        size_t loU, ne = rangeOf(c, &loU);
+        if (!ne) return;
+        const char *own = send + ((size_t)me * a.sendStride + loU * G) * ESI;
+        char *out = recv + loU * G * ESO;
+        reduceUnits<TIn, TOut, G>(dc, a, own, aligned16(own), stagePtr(dc, me, seq) + loU * INB, slot, ne, out, aligned16(out), nullptr, 0,
+                                  gtid, gstride);
+      };
+      pipelined<2>(dc, cta, seq, chunks, push, combine, combine);
       break;
     }
 
@@ -487,134 +560,119 @@ __device__ void fcxMoveBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta,
   const size_t bytes = a.count * es;
   const size_t slot = (bytes + 15) / 16 * 16;
 
-  switch (a.kind) {
-    case FCX_K_AG: {
-      for (int k = 1; k < n; k++) {
-        int p = (me + k) % n;
-        copyToSlot(stagePtr(dc, p, seq) + (size_t)me * slot, send, bytes, 16, gtid, gstride);
-      }
-      char *mine = recv + (size_t)me * a.recvStride * es;
-      if (mine != send) copyUnits(mine, send, bytes, 16, gtid, gstride);
-      if (!ctaBarrier(dc, cta, barrierValue(seq, 1), seq)) break;
-      for (int k = 1; k < n; k++) {
-        int p = (me + k) % n;
-        copyFromSlot(recv + (size_t)p * a.recvStride * es, stagePtr(dc, me, seq) + (size_t)p * slot, bytes, 16, gtid,
-                     gstride);
-      }
-      break;
-    }
-
-    case FCX_K_AG_NVLS: {
-      // one multicast store per line instead of n-1 unicast stores
-      const size_t stageOff = FCX_OFF_STAGE + (size_t)(seq & 1) * dc.stageBytes;
-      char *mc = dc.mcHeap + stageOff + (size_t)me * slot;
-      bool al = aligned16(send);
-      size_t nunits = (bytes + 15) / 16;
-      for (size_t u = gtid; u < nunits; u += gstride) {
-        uint4 v;
-        int nv = (int)min((size_t)16, bytes - u * 16);
-        if (al && nv == 16) v = ld16(send + u * 16);
-        else {
-          union { uint4 q; char c[16]; } w;
-          w.q = make_uint4(0, 0, 0, 0);
-          for (int i = 0; i < nv; i++) w.c[i] = send[u * 16 + i];
-          v = w.q;
-        }
-        mmStore(mc + u * 16, v);
-      }
-      if (!ctaBarrier(dc, cta, barrierValue(seq, 1), seq)) break;
-      for (int p = 0; p < n; p++) {
-        char *dst = recv + (size_t)p * a.recvStride * es;
-        if (p == me && dst == send) continue;
-        copyFromSlot(dst, stagePtr(dc, me, seq) + (size_t)p * slot, bytes, 16, gtid, gstride);
-      }
-      break;
-    }
-
-    case FCX_K_BCAST: {
-      const bool useMc = dc.mcHeap != nullptr && a.useMc;
-      if (me == a.root) {
-        if (useMc) {
-          const size_t stageOff = FCX_OFF_STAGE + (size_t)(seq & 1) * dc.stageBytes;
-          char *mc = dc.mcHeap + stageOff;
-          bool al = aligned16(send);
-          size_t nunits = (bytes + 15) / 16;
-          for (size_t u = gtid; u < nunits; u += gstride) {
-            int nv = (int)min((size_t)16, bytes - u * 16);
-            uint4 v;
-            if (al && nv == 16) v = ld16(send + u * 16);
-            else {
-              union { uint4 q; char c[16]; } w;
-              w.q = make_uint4(0, 0, 0, 0);
-              for (int i = 0; i < nv; i++) w.c[i] = send[u * 16 + i];
-              v = w.q;
-            }
-            mmStore(mc + u * 16, v);
+  if (a.kind != FCX_K_A2AV) {
+    // Every fixed-size byte mover is one exchange: piece out[p] goes into a slot of rank p's staging area,
+    // piece in[p] arrives in a slot of this rank's staging area and is copied to its place, and the piece a
+    // rank keeps for itself is copied locally.  With the multicast alias one store reaches every rank.
+    const char *outSrc[FCX_MAX_RANKS];
+    char *outDst[FCX_MAX_RANKS];
+    const char *inSrc[FCX_MAX_RANKS];
+    char *inDst[FCX_MAX_RANKS];
+    for (int p = 0; p < n; p++) { outSrc[p] = nullptr; outDst[p] = nullptr; inSrc[p] = nullptr; inDst[p] = nullptr; }
+    const char *selfSrc = nullptr, *mcSrc = nullptr;
+    char *selfDst = nullptr, *mcDst = nullptr;
+    const size_t stageOff = FCX_OFF_STAGE + (size_t)(seq & 1) * dc.stageBytes;
+    char *myStage = stagePtr(dc, me, seq);
+    switch (a.kind) {
+      case FCX_K_AG:
+      case FCX_K_AG_NVLS:
+        for (int p = 0; p < n; p++)
+          if (p != me) {
+            if (a.kind == FCX_K_AG) { outSrc[p] = send; outDst[p] = stagePtr(dc, p, seq) + (size_t)me * slot; }
+            inSrc[p] = myStage + (size_t)p * slot;
+            inDst[p] = recv + (size_t)p * a.recvStride * es;
           }
+        if (a.kind == FCX_K_AG_NVLS) { mcSrc = send; mcDst = dc.mcHeap + stageOff + (size_t)me * slot; }
+        selfSrc = send;
+        selfDst = recv + (size_t)me * a.recvStride * es;
+        break;
+      case FCX_K_BCAST:
+        if (me == a.root) {
+          if (dc.mcHeap != nullptr && a.useMc) { mcSrc = send; mcDst = dc.mcHeap + stageOff; }
+          else
+            for (int p = 0; p < n; p++)
+              if (p != me) { outSrc[p] = send; outDst[p] = stagePtr(dc, p, seq); }
+          selfSrc = send;
+          selfDst = recv;
         } else {
-          for (int k = 1; k < n; k++) {
-            int p = (me + k) % n;
-            copyToSlot(stagePtr(dc, p, seq), send, bytes, 16, gtid, gstride);
+          inSrc[a.root] = myStage;
+          inDst[a.root] = recv;
+        }
+        break;
+      case FCX_K_GATHER:
+        if (me != a.root) { outSrc[a.root] = send; outDst[a.root] = stagePtr(dc, a.root, seq) + (size_t)me * slot; }
+        else {
+          for (int p = 0; p < n; p++)
+            if (p != me) { inSrc[p] = myStage + (size_t)p * slot; inDst[p] = recv + (size_t)p * a.recvStride * es; }
+          selfSrc = send;
+          selfDst = recv + (size_t)me * a.recvStride * es;
+        }
+        break;
+      case FCX_K_SCATTER:
+        if (me == a.root) {
+          for (int p = 0; p < n; p++)
+            if (p != me) { outSrc[p] = send + (size_t)p * a.sendStride * es; outDst[p] = stagePtr(dc, p, seq); }
+          selfSrc = send + (size_t)me * a.sendStride * es;
+          selfDst = recv;
+        } else {
+          inSrc[a.root] = myStage;
+          inDst[a.root] = recv;
+        }
+        break;
+      case FCX_K_A2A:
+        for (int p = 0; p < n; p++)
+          if (p != me) {
+            outSrc[p] = send + (size_t)p * a.sendStride * es;
+            outDst[p] = stagePtr(dc, p, seq) + (size_t)me * slot;
+            inSrc[p] = myStage + (size_t)p * slot;
+            inDst[p] = recv + (size_t)p * a.recvStride * es;
           }
-        }
-        if (recv != send) copyUnits(recv, send, bytes, 16, gtid, gstride);
-      }
-      if (!ctaBarrier(dc, cta, barrierValue(seq, 1), seq)) break;
-      if (me != a.root) copyFromSlot(recv, stagePtr(dc, me, seq), bytes, 16, gtid, gstride);
-      break;
+        selfSrc = send + (size_t)me * a.sendStride * es;
+        selfDst = recv + (size_t)me * a.recvStride * es;
+        break;
+      default: break;
     }
-
-    case FCX_K_GATHER: {
-      if (me != a.root) {
-        copyToSlot(stagePtr(dc, a.root, seq) + (size_t)me * slot, send, bytes, 16, gtid, gstride);
-      } else {
-        char *mine = recv + (size_t)me * a.recvStride * es;
-        if (mine != send) copyUnits(mine, send, bytes, 16, gtid, gstride);
-      }
-      if (!ctaBarrier(dc, cta, barrierValue(seq, 1), seq)) break;
-      if (me == a.root)
-        for (int k = 1; k < n; k++) {
-          int p = (me + k) % n;
-          copyFromSlot(recv + (size_t)p * a.recvStride * es, stagePtr(dc, me, seq) + (size_t)p * slot, bytes, 16, gtid,
-                       gstride);
+    const size_t sub = max((size_t)16384, (pipeBytesOf(dc) / (size_t)max(1, n - 1)) & ~(size_t)15);
+    const int chunks = (int)max((size_t)1, (bytes + sub - 1) / sub);
+    auto push = [&](int c) {
+      size_t lo, len = subLen(bytes, sub, c, &lo);
+      if (!len) return;
+      if (mcDst) {
+        const bool al = aligned16(mcSrc);
+        const size_t nunits = (len + 15) / 16;
+        for (size_t u = gtid; u < nunits; u += gstride) {
+          int nv = (int)min((size_t)16, len - u * 16);
+          uint4 v;
+          if (al && nv == 16) v = ld16(mcSrc + lo + u * 16);
+          else {
+            union { uint4 q; char c[16]; } w;
+            w.q = make_uint4(0, 0, 0, 0);
+            for (int i = 0; i < nv; i++) w.c[i] = mcSrc[lo + u * 16 + i];
+            v = w.q;
+          }
+          mmStore(mcDst + lo + u * 16, v);
         }
-      break;
-    }
-
-    case FCX_K_SCATTER: {
-      if (me == a.root) {
-        for (int k = 1; k < n; k++) {
-          int p = (me + k) % n;
-          copyToSlot(stagePtr(dc, p, seq), send + (size_t)p * a.sendStride * es, bytes, 16, gtid, gstride);
-        }
-        const char *mine = send + (size_t)me * a.sendStride * es;
-        if (mine != recv) copyUnits(recv, mine, bytes, 16, gtid, gstride);
       }
-      if (!ctaBarrier(dc, cta, barrierValue(seq, 1), seq)) break;
-      if (me != a.root) copyFromSlot(recv, stagePtr(dc, me, seq), bytes, 16, gtid, gstride);
-      break;
-    }
-
-    case FCX_K_A2A: {
       for (int k = 1; k < n; k++) {
         int p = (me + k) % n;
-        copyToSlot(stagePtr(dc, p, seq) + (size_t)me * slot, send + (size_t)p * a.sendStride * es, bytes, 16, gtid,
-                   gstride);
+        if (outSrc[p]) copyToSlot(outDst[p] + lo, outSrc[p] + lo, len, 16, gtid, gstride);
       }
-      {
-        const char *s = send + (size_t)me * a.sendStride * es;
-        char *d = recv + (size_t)me * a.recvStride * es;
-        if (s != d) copyUnits(d, s, bytes, 16, gtid, gstride);
-      }
-      if (!ctaBarrier(dc, cta, barrierValue(seq, 1), seq)) break;
+      if (selfSrc && selfSrc != selfDst) copyUnits(selfDst + lo, selfSrc + lo, len, 16, gtid, gstride);
+    };
+    auto pull = [&](int c) {
+      size_t lo, len = subLen(bytes, sub, c, &lo);
+      if (!len) return;
       for (int k = 1; k < n; k++) {
         int p = (me + k) % n;
-        copyFromSlot(recv + (size_t)p * a.recvStride * es, stagePtr(dc, me, seq) + (size_t)p * slot, bytes, 16, gtid,
-                     gstride);
+        if (inSrc[p]) copyFromSlot(inDst[p] + lo, inSrc[p] + lo, len, 16, gtid, gstride);
       }
-      break;
-    }
+    };
+    pipelined<2>(dc, cta, seq, chunks, push, pull, pull);
+    epilogue(dc, seq, nctas);
+    return;
+  }
 
+  switch (a.kind) {
     case FCX_K_A2AV: {
       // Variable blocks move in rounds through per-source slots that are cut
       // in two halves, so that round k+1 can be pushed while the receiver

@@ -113,7 +113,20 @@ struct Opts {
   double factor = 2;
 };
 
-struct Row { size_t bytes; double devUs, hostUs; int bad; };
+struct Row { size_t bytes; double devUs, hostUs; int bad; int op; };
+
+// "-o a,b,c": several operations on one communicator (one process start-up for the whole list)
+std::vector<std::string> splitOps(const std::string &s) {
+  std::vector<std::string> v;
+  size_t a = 0;
+  while (a <= s.size()) {
+    size_t b = s.find(',', a);
+    if (b == std::string::npos) b = s.size();
+    if (b > a) v.push_back(s.substr(a, b - a));
+    a = b + 1;
+  }
+  return v;
+}
 
 #define CK(call)                                                             \
   do {                                                                       \
@@ -181,32 +194,35 @@ int worker(const Opts &o, int rank, int n, int idRead, int idWrite[], int outFd)
     cudaMemset(recv, 0, cap);
   }
   std::vector<Row> rows;
-  const bool whole = o.op == "allreduce" || o.op == "broadcast" || o.op == "reduce" || o.op == "sendrecv";
+  const std::vector<std::string> ops = splitOps(o.op);
+  for (size_t oi = 0; oi < ops.size(); oi++) {
+  const std::string &opn = ops[oi];
+  const bool whole = opn == "allreduce" || opn == "broadcast" || opn == "reduce" || opn == "sendrecv";
   for (size_t size = o.minB; size <= o.maxB;) {
     size_t count = std::max<size_t>(whole ? size / es : size / es / n, 1);
     size_t nbytes = count * es * (whole ? 1 : n);
     std::vector<int> roots;
-    const bool rooted = o.op == "broadcast" || o.op == "reduce" || o.op == "gather" || o.op == "scatter";
+    const bool rooted = opn == "broadcast" || opn == "reduce" || opn == "gather" || opn == "scatter";
     if (rooted && o.root < 0) for (int r = 0; r < n; r++) roots.push_back(r);
     else roots.push_back(std::max(o.root, 0));
     std::vector<size_t> cnt(n, count), dsp(n);
     for (int i = 0; i < n; i++) dsp[i] = i * count;
     auto call = [&](int root) {
-      if (o.op == "allreduce") CK(api.AllReduce(send, recv, count, dt, flagcxSum, comm, st));
-      else if (o.op == "allgather") CK(api.AllGather(send, recv, count, dt, comm, st));
-      else if (o.op == "reducescatter") CK(api.ReduceScatter(send, recv, count, dt, flagcxSum, comm, st));
-      else if (o.op == "alltoall") CK(api.AlltoAll(send, recv, count, dt, comm, st));
-      else if (o.op == "alltoallv") CK(api.AlltoAllv(send, cnt.data(), dsp.data(), recv, cnt.data(), dsp.data(), dt, comm, st));
-      else if (o.op == "broadcast") CK(api.Broadcast(send, recv, count, dt, root, comm, st));
-      else if (o.op == "reduce") CK(api.Reduce(send, recv, count, dt, flagcxSum, root, comm, st));
-      else if (o.op == "gather") CK(api.Gather(send, recv, count, dt, root, comm, st));
-      else if (o.op == "scatter") CK(api.Scatter(send, recv, count, dt, root, comm, st));
-      else if (o.op == "sendrecv") {
+      if (opn == "allreduce") CK(api.AllReduce(send, recv, count, dt, flagcxSum, comm, st));
+      else if (opn == "allgather") CK(api.AllGather(send, recv, count, dt, comm, st));
+      else if (opn == "reducescatter") CK(api.ReduceScatter(send, recv, count, dt, flagcxSum, comm, st));
+      else if (opn == "alltoall") CK(api.AlltoAll(send, recv, count, dt, comm, st));
+      else if (opn == "alltoallv") CK(api.AlltoAllv(send, cnt.data(), dsp.data(), recv, cnt.data(), dsp.data(), dt, comm, st));
+      else if (opn == "broadcast") CK(api.Broadcast(send, recv, count, dt, root, comm, st));
+      else if (opn == "reduce") CK(api.Reduce(send, recv, count, dt, flagcxSum, root, comm, st));
+      else if (opn == "gather") CK(api.Gather(send, recv, count, dt, root, comm, st));
+      else if (opn == "scatter") CK(api.Scatter(send, recv, count, dt, root, comm, st));
+      else if (opn == "sendrecv") {
         CK(api.GroupStart(comm));
         CK(api.Send(send, count, dt, (rank + 1) % n, comm, st));
         CK(api.Recv(recv, count, dt, (rank + n - 1) % n, comm, st));
         CK(api.GroupEnd(comm));
-      } else { fprintf(stderr, "unknown op %s\n", o.op.c_str()); _exit(2); }
+      } else { fprintf(stderr, "unknown op %s\n", opn.c_str()); _exit(2); }
     };
     int iters = size <= (256u << 20) ? o.iters : std::max(5, o.iters / 4);
     double devUs = 0, hostUs = 0;
@@ -230,19 +246,19 @@ int worker(const Opts &o, int rank, int n, int idRead, int idWrite[], int outFd)
       hostUs += std::chrono::duration<double, std::micro>(t1 - t0).count() / iters / roots.size();
       cudaEventDestroy(e0);
       cudaEventDestroy(e1);
-      if (o.check && es != 1 && !isHalf && (o.op == "allreduce" || o.op == "allgather" || o.op == "reducescatter" || o.op == "alltoall")) {
-        size_t outElems = o.op == "allreduce" ? count : o.op == "reducescatter" ? count : count * n;
+      if (o.check && es != 1 && !isHalf && (opn == "allreduce" || opn == "allgather" || opn == "reducescatter" || opn == "alltoall")) {
+        size_t outElems = opn == "allreduce" ? count : opn == "reducescatter" ? count : count * n;
         outElems = std::min<size_t>(outElems, 1 << 20);
         std::vector<char> h(outElems * es);
         cudaMemcpy(h.data(), recv, outElems * es, cudaMemcpyDeviceToHost);
         for (size_t i = 0; i < outElems; i++) {
           float got = es == 4 ? ((float *)h.data())[i] : bf16ToF(((uint16_t *)h.data())[i]);
           float want = 0;
-          if (o.op == "allreduce") for (int r = 0; r < n; r++) want += (float)((i + r) % 10);
-          else if (o.op == "reducescatter") for (int r = 0; r < n; r++) want += (float)((rank * count + i + r) % 10);
-          else if (o.op == "allgather") want = (float)((i % count + i / count) % 10);
+          if (opn == "allreduce") for (int r = 0; r < n; r++) want += (float)((i + r) % 10);
+          else if (opn == "reducescatter") for (int r = 0; r < n; r++) want += (float)((rank * count + i + r) % 10);
+          else if (opn == "allgather") want = (float)((i % count + i / count) % 10);
           else want = (float)((rank * count + i % count + i / count) % 10);
-          if (std::fabs(got - want) > (es == 2 ? 0.51f : 1e-3f)) { bad++; if (bad < 4) fprintf(stderr, "rank %d %s[%zu] = %g, expected %g\n", rank, o.op.c_str(), i, got, want); }
+          if (std::fabs(got - want) > (es == 2 ? 0.51f : 1e-3f)) { bad++; if (bad < 4) fprintf(stderr, "rank %d %s[%zu] = %g, expected %g\n", rank, opn.c_str(), i, got, want); }
         }
       }
     }
@@ -253,9 +269,10 @@ int worker(const Opts &o, int rank, int n, int idRead, int idWrite[], int outFd)
       for (int i = 0; i < 10; i++) printf(" %g", h[i]);
       printf("\n");
     }
-    rows.push_back({nbytes, devUs, hostUs, bad});
+    rows.push_back({nbytes, devUs, hostUs, bad, (int)oi});
     size_t next = (size_t)(size * o.factor);
     size = next > size ? next : size + 1;
+  }
   }
   CK(api.Barrier(comm, st));
   if (o.reg) {
@@ -349,11 +366,17 @@ int main(int argc, char **argv) {
     if (!WIFEXITED(status) || WEXITSTATUS(status) != 0) { fprintf(stderr, "rank %d exited abnormally (%d)\n", r, status); fail = true; }
   }
   if (fail) return 1;
-  const double f = busFactor(o.op, n);
-  printf("# %s, %d ranks, %s, library %s\n", o.op.c_str(), n, o.dtype.c_str(), o.lib.c_str());
-  printf("# %12s %12s %12s %12s %14s %6s\n", "bytes", "time_us", "algbw_GB/s", "busbw_GB/s", "host_mean_us", "wrong");
+  const std::vector<std::string> ops = splitOps(o.op);
   FILE *jf = o.json.empty() ? nullptr : fopen(o.json.c_str(), "a");
+  int lastOp = -1;
   for (size_t i = 0; i < all[0].size(); i++) {
+    const std::string &opn = ops[all[0][i].op];
+    const double f = busFactor(opn, n);
+    if (all[0][i].op != lastOp) {
+      lastOp = all[0][i].op;
+      printf("# %s, %d ranks, %s, library %s\n", opn.c_str(), n, o.dtype.c_str(), o.lib.c_str());
+      printf("# %12s %12s %12s %12s %14s %6s\n", "bytes", "time_us", "algbw_GB/s", "busbw_GB/s", "host_mean_us", "wrong");
+    }
     double dev = 0, host = 0;
     int bad = 0;
     for (int r = 0; r < n; r++) { dev = std::max(dev, all[r][i].devUs); host += all[r][i].hostUs / n; bad += all[r][i].bad; }
@@ -362,7 +385,7 @@ int main(int argc, char **argv) {
     if (jf)
       fprintf(jf, "{\"op\": \"%s\", \"lib\": \"%s\", \"dtype\": \"%s\", \"ranks\": %d, \"bytes\": %zu, \"time_us\": %.3f, \"algbw_gbs\": %.3f, "
                   "\"busbw_gbs\": %.3f, \"host_mean_us\": %.3f, \"wrong\": %d, \"registered\": %d}\n",
-              o.op.c_str(), o.lib.c_str(), o.dtype.c_str(), n, all[0][i].bytes, dev, alg, alg * f, host, bad, o.reg);
+              opn.c_str(), o.lib.c_str(), o.dtype.c_str(), n, all[0][i].bytes, dev, alg, alg * f, host, bad, o.reg);
   }
   if (jf) fclose(jf);
   return 0;

@@ -97,8 +97,10 @@ class FlagcxWork : public c10d::Work {
     future_->markCompleted(c10::IValue(outputs_));
     done_ = true;
   }
-  void finishCudaEnqueue() {
-    // the result tensors are valid for stream-ordered consumers as soon as the future's events are respected
+  void finishCudaEnqueue(const c10::cuda::CUDAStream &s) {
+    // A device-aware future records its events on the streams that are current when it is completed, and
+    // whoever waits on it synchronises with those events: the communication stream must be current here.
+    c10::cuda::CUDAStreamGuard g(s);
     future_->markCompleted(c10::IValue(outputs_));
   }
 
@@ -224,7 +226,7 @@ class FlagcxBackend : public c10d::Backend {
       coalescedDev_ = dev;
     } else {
       work->record(*stream_);
-      work->finishCudaEnqueue();
+      work->finishCudaEnqueue(*stream_);
     }
     return work;
   }
@@ -526,10 +528,10 @@ class FlagcxBackend : public c10d::Backend {
       }
       work = c10::make_intrusive<FlagcxWork>(c10d::OpType::COALESCED, getRank(), comms_["cuda"], true, coalescedDev_.index(), timeout_);
       work->record(*stream_);
-      work->finishCudaEnqueue();
+      work->finishCudaEnqueue(*stream_);
       for (auto &w : cudaPending_) {
         w->record(*stream_);
-        w->finishCudaEnqueue();
+        w->finishCudaEnqueue(*stream_);
       }
     } else {
       FCX_TORCH_CHECK(flagcxGroupEnd(nullptr));

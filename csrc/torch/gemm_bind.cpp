@@ -5,6 +5,7 @@
 
 #include "flagcx.h"
 #include "flagcx_ext.h"
+#include "gemm_fp8_sm100.h"
 #include "gemm_sm100.h"
 
 namespace fcxt {
@@ -67,7 +68,53 @@ static at::Tensor gemmRs(uint64_t comm, const at::Tensor &a, const at::Tensor &w
   return out;
 }
 
+// bf16 [M,K] -> (e4m3 [M,K], fp32 scales [K/128, M])
+static std::tuple<at::Tensor, at::Tensor> quantFp8Act(const at::Tensor &x) {
+  checkMat(x, "x");
+  TORCH_CHECK(x.size(1) % 128 == 0, "K must be a multiple of 128");
+  c10::cuda::CUDAGuard g(x.device());
+  auto q = at::empty({x.size(0), x.size(1)}, x.options().dtype(at::kFloat8_e4m3fn));
+  auto sa = at::empty({x.size(1) / 128, x.size(0)}, x.options().dtype(at::kFloat));
+  auto e = fcxQuantFp8Act(x.data_ptr(), q.data_ptr(), sa.data_ptr<float>(), (int)x.size(0), (int)x.size(1), (int)x.stride(0),
+                          at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(e == cudaSuccess, "fp8 quantisation launch failed: ", cudaGetErrorString(e));
+  return {q, sa};
+}
+
+// bf16 [N,K] -> (e4m3 [N,K], fp32 scales [ceil(N/128), K/128])
+static std::tuple<at::Tensor, at::Tensor> quantFp8Weight(const at::Tensor &w) {
+  checkMat(w, "w");
+  TORCH_CHECK(w.size(1) % 128 == 0, "K must be a multiple of 128");
+  c10::cuda::CUDAGuard g(w.device());
+  auto q = at::empty({w.size(0), w.size(1)}, w.options().dtype(at::kFloat8_e4m3fn));
+  auto sb = at::empty({(w.size(0) + 127) / 128, w.size(1) / 128}, w.options().dtype(at::kFloat));
+  auto e = fcxQuantFp8Weight(w.data_ptr(), q.data_ptr(), sb.data_ptr<float>(), (int)w.size(0), (int)w.size(1), (int)w.stride(0),
+                             at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(e == cudaSuccess, "fp8 quantisation launch failed: ", cudaGetErrorString(e));
+  return {q, sb};
+}
+
+// bf16 c[M,N] = dequant(aq, sa) @ dequant(bq, sb)^T with the scales applied per 128-deep slice of K on the tcgen05 path
+static at::Tensor gemmFp8NT(const at::Tensor &aq, const at::Tensor &sa, const at::Tensor &bq, const at::Tensor &sb, at::Tensor &err) {
+  TORCH_CHECK(aq.is_cuda() && aq.scalar_type() == at::kFloat8_e4m3fn && aq.is_contiguous() && bq.scalar_type() == at::kFloat8_e4m3fn &&
+                  bq.is_contiguous() && aq.dim() == 2 && bq.dim() == 2 && aq.size(1) == bq.size(1),
+              "aq [M,K] and bq [N,K] must be contiguous e4m3 matrices");
+  const int M = (int)aq.size(0), N = (int)bq.size(0), K = (int)aq.size(1);
+  TORCH_CHECK(sa.scalar_type() == at::kFloat && sa.is_contiguous() && sa.numel() == (int64_t)(K / 128) * M, "sa must be fp32 [K/128, M]");
+  TORCH_CHECK(sb.scalar_type() == at::kFloat && sb.is_contiguous() && sb.numel() == (int64_t)((N + 127) / 128) * (K / 128),
+              "sb must be fp32 [ceil(N/128), K/128]");
+  c10::cuda::CUDAGuard g(aq.device());
+  auto c = at::empty({M, N}, aq.options().dtype(at::kBFloat16));
+  auto e = fcxGemmFp8Blockwise(aq.data_ptr(), sa.data_ptr<float>(), bq.data_ptr(), sb.data_ptr<float>(), c.data_ptr(), M, N, K, (int)c.stride(0),
+                               err.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(e == cudaSuccess, "fp8 GEMM launch failed: ", cudaGetErrorString(e));
+  return c;
+}
+
 void bindGemm(py::module &m) {
+  m.def("quant_fp8_act", &quantFp8Act);
+  m.def("quant_fp8_weight", &quantFp8Weight);
+  m.def("gemm_fp8_nt", &gemmFp8NT, "block-scaled e4m3 GEMM (1x128 activation scales, 128x128 weight scales) on tcgen05");
   m.def("gemm_nt", &gemmNT, "bf16 a[M,K] @ b[N,K]^T on tcgen05");
   m.def("ag_gemm", &agGemm);
   m.def("gemm_rs", &gemmRs);

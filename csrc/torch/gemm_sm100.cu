@@ -6,8 +6,9 @@
 //                [M/n, K] block.  Dedicated "comm" CTAs push this rank's block
 //                into every peer's gathered buffer over NVLink (plain stores)
 //                and raise one flag per 128-row block; the GEMM CTAs start
-//                with the local block and consume remote blocks as their
-//                flags arrive, so the transfer hides behind the math.
+//                with the local block, read in place through its own tensor
+//                map, and consume remote blocks as their flags arrive, so
+//                the transfer hides behind the math.
 //   mode RS      GEMM -> reduce-scatter: every finished 128x256 tile is
 //                written straight from TMEM (through registers) into the
 //                staging area of the rank that owns those rows, tiles owned by
@@ -42,99 +43,28 @@
 #include <stdint.h>
 
 #include "gemm_sm100.h"
+#include "tcgen05.cuh"
 
 namespace {
+
+using namespace fcxmma;
 
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int EPI_BYTES = 4 * 32 * 128;  // per epilogue warp: 32 rows x 64 bf16
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr int THREADS = 256;
-constexpr uint32_t SPIN_LIMIT = 1u << 28;  // mbarrier polls before giving up (seconds of wall time)
-
-__device__ __forceinline__ uint32_t smemAddr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbarInit(uint64_t *bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smemAddr(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbarExpectTx(uint64_t *bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smemAddr(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbarArrive(uint64_t *bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smemAddr(bar)) : "memory");
-}
-// Bounded wait for the phase with the given parity.  false = gave up.
-__device__ __forceinline__ bool mbarWait(uint64_t *bar, uint32_t parity, volatile int *errFlag) {
-  uint32_t addr = smemAddr(bar), done = 0;
-  for (uint32_t spin = 0; spin < SPIN_LIMIT; spin++) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-    if (done) return true;
-    if ((spin & 0xffff) == 0xffff && *errFlag) return false;
-  }
-  *errFlag = 1;
-  return false;
-}
-
-__device__ __forceinline__ void tmaLoad2d(void *smemDst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-               ::"r"(smemAddr(smemDst)), "l"(map), "r"(x), "r"(y), "r"(smemAddr(bar)) : "memory");
-}
-
-// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows 128 bytes apart,
-// 8-row groups 1024 bytes apart (descriptor version 1 = Blackwell).
-__device__ __forceinline__ uint64_t smemDesc(uint32_t addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr & 0x3ffff) >> 4);        // start address, 16-byte units
-  d |= (uint64_t)1 << 16;                        // leading byte offset (unused for swizzled K-major)
-  d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset
-  d |= (uint64_t)1 << 46;                        // version
-  d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
-  return d;
-}
 
 // Instruction descriptor: D fp32, A/B bf16, both K-major, M = 128, N = 256.
-__device__ __forceinline__ constexpr uint32_t instrDesc() {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
-
-__device__ __forceinline__ void mmaF16(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(dTmem), "l"(aDesc), "l"(bDesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void mmaCommit(uint64_t *bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smemAddr(bar)) : "memory");
-}
-__device__ __forceinline__ void tmemLd32(uint32_t taddr, uint32_t *r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-}
-__device__ __forceinline__ void tmemLdWait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void fenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ uint32_t pack2(float a, float b) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-  return *(uint32_t *)&v;
+__device__ __forceinline__ uint32_t instrDesc(int bn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
 // Tile t of this CTA's sequence -> (row block, column block).  Row blocks are
 // visited in rotated order so that (AG) the local block comes first and (RS)
 // the blocks this rank owns come last.
 __device__ __forceinline__ void tileCoord(const FcxGemmParams &p, int nM, int t, int *mb, int *nb) {
-  const int nN = (p.N + BN - 1) / BN;
+  const int nN = (p.N + p.bn - 1) / p.bn;
   if (p.group > 0) {
     // Row blocks in bands of `group`; inside a band the row block changes fastest, so the CTAs of one wave
     // share a few A row blocks and a few B column blocks and both stay in L2.
@@ -151,7 +81,8 @@ __device__ __forceinline__ void tileCoord(const FcxGemmParams &p, int nM, int t,
 
 template <int MODE>
 __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                                                            const FcxGemmParams p, const FcxDevComm dc) {
+                                                            const __grid_constant__ CUtensorMap tmALocal, const FcxGemmParams p,
+                                                            const FcxDevComm dc) {
   extern __shared__ uint8_t smemRaw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int *err = p.errFlag;
@@ -164,13 +95,12 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
     const int n = dc.nranks, me = dc.rank;
     const int blocksPerRank = p.rowsPerRank / BM;
     const size_t blockBytes = (size_t)BM * p.K * 2;
-    const int work = blocksPerRank * n;  // (destination, block) pairs
+    const int work = blocksPerRank * (n - 1);  // (remote destination, block) pairs; the local block is read where it lies
     for (int w = commCta; w < work; w += nComm) {
-      // destinations rotate so that the ranks do not all write to the same GPU at once;
-      // the local copy (k == 0) is made first because the GEMM CTAs start on it;
-      // step k goes to rank me-k, so every rank receives from itself, then rank+1, rank+2, ...
-      // which is the order in which its GEMM CTAs consume the blocks
-      const int k = w / blocksPerRank, b = w % blocksPerRank;
+      // destinations rotate so that the ranks do not all write to the same GPU at once:
+      // step k goes to rank me-k, so every rank receives from rank+1, rank+2, ... which is the
+      // order in which its GEMM CTAs consume the remote blocks
+      const int k = 1 + w / blocksPerRank, b = w % blocksPerRank;
       const int dst = (me - k + n) % n;
       const char *src = (const char *)p.aLocal + (size_t)b * blockBytes;
       char *d = dc.heap[dst] + p.gatherOff + ((size_t)me * blocksPerRank + b) * blockBytes;
@@ -200,7 +130,8 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
   uint32_t *tmemBaseSlot = (uint32_t *)(bars + 2 * STAGES + 4);
 
   const int Mrows = p.mPtr ? min(*p.mPtr, p.M) : p.M;  // the row count may live on the device
-  const int nN = (p.N + BN - 1) / BN, nM = (Mrows + BM - 1) / BM;
+  const int bn = p.bn;  // columns per tile: 256, or 128 when that fills the SMs better
+  const int nN = (p.N + bn - 1) / bn, nM = (Mrows + BM - 1) / BM;
   const int nTiles = nN * nM, nK = (p.K + BK - 1) / BK;
   const int gemmCtas = (MODE == FCX_GEMM_AG) ? p.gemmCtas : gridDim.x;
 
@@ -227,19 +158,28 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
       for (int t = blockIdx.x; t < nTiles && ok; t += gemmCtas) {
         int mb, nb;
         tileCoord(p, nM, t, &mb, &nb);
+        const CUtensorMap *mapA = &tmA;
+        int rowA = mb * BM;
         if (MODE == FCX_GEMM_AG) {
-          // rows of block mb must have arrived in the gathered buffer
-          const uint64_t *flag = (const uint64_t *)(dc.heap[dc.rank] + p.flagOff) + mb;
-          ok = fcxdev::waitGe(dc, flag, p.epoch, mb / (p.rowsPerRank / BM), FCX_WAIT_DEVAPI, blockIdx.x, p.epoch);
-          if (!ok) { *err = 1; break; }
-          asm volatile("fence.proxy.async;" ::: "memory");  // remote generic-proxy writes -> this CTA's TMA reads
+          const int blocksPerRank = p.rowsPerRank / BM, owner = mb / blocksPerRank;
+          if (owner == dc.rank) {
+            // this rank's own rows are read straight from the caller's tensor
+            mapA = &tmALocal;
+            rowA = (mb - owner * blocksPerRank) * BM;
+          } else {
+            // rows of block mb must have arrived in the gathered buffer
+            const uint64_t *flag = (const uint64_t *)(dc.heap[dc.rank] + p.flagOff) + mb;
+            ok = fcxdev::waitGe(dc, flag, p.epoch, owner, FCX_WAIT_DEVAPI, blockIdx.x, p.epoch);
+            if (!ok) { *err = 1; break; }
+            asm volatile("fence.proxy.async;" ::: "memory");  // remote generic-proxy writes -> this CTA's TMA reads
+          }
         }
         for (int kb = 0; kb < nK; kb++) {
           if (!mbarWait(&emptyBar[stage], phase ^ 1, err)) { ok = false; break; }
-          mbarExpectTx(&fullBar[stage], STAGE_BYTES);
+          mbarExpectTx(&fullBar[stage], A_BYTES + bn * BK * 2);
           uint8_t *sa = tiles + stage * STAGE_BYTES, *sb = sa + A_BYTES;
-          tmaLoad2d(sa, &tmA, kb * BK, mb * BM, &fullBar[stage]);
-          tmaLoad2d(sb, &tmB, kb * BK, nb * BN, &fullBar[stage]);
+          tmaLoad2d(sa, mapA, kb * BK, rowA, &fullBar[stage]);
+          tmaLoad2d(sb, &tmB, kb * BK, nb * bn, &fullBar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -250,11 +190,11 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
       int stage = 0, buf = 0;
       uint32_t phase = 0, accPhase = 0;
       bool ok = true;
-      const uint32_t idesc = instrDesc();
+      const uint32_t idesc = instrDesc(bn);
       for (int t = blockIdx.x; t < nTiles && ok; t += gemmCtas) {
         if (!mbarWait(&tmemEmpty[buf], accPhase ^ 1, err)) break;
         fenceAfter();
-        const uint32_t dTmem = tmemBase + (uint32_t)buf * BN;
+        const uint32_t dTmem = tmemBase + (uint32_t)buf * bn;
         for (int kb = 0; kb < nK; kb++) {
           if (!mbarWait(&fullBar[stage], phase, err)) { ok = false; break; }
           fenceAfter();
@@ -303,11 +243,11 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
         // turns that into stores where 8 lanes write one full 128-byte line of a row.
         uint4 *stg = (uint4 *)(epiStage + (size_t)q * 32 * 128);
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 64) {
+        for (int c0 = 0; c0 < bn; c0 += 64) {
           uint32_t r[32];
 #pragma unroll
           for (int h = 0; h < 2; h++) {
-            tmemLd32(tmemBase + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c0 + 32 * h), r);
+            tmemLd32(tmemBase + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * bn + c0 + 32 * h), r);
             tmemLdWait();
 #pragma unroll
             for (int v = 0; v < 4; v++) {
@@ -320,7 +260,7 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
             }
           }
           __syncwarp();
-          const int col = nb * BN + c0 + (lane & 7) * 8;
+          const int col = nb * bn + c0 + (lane & 7) * 8;
 #pragma unroll
           for (int i = 0; i < 8; i++) {
             const int rr = i * 4 + (lane >> 3);
@@ -418,54 +358,42 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
 
 // ------------------------------------------------------------------ host side
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encodeFn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void *p = nullptr;
-    cudaDriverEntryPointQueryResult st;
-    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault, &st) == cudaSuccess &&
-        st == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  }
-  return fn;
-}
-
 // Row-major [rows, cols] bf16 matrix with `ld` elements between rows; box = [boxRows, 64 columns], 128-byte swizzle.
 bool makeMap(CUtensorMap *m, const void *base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t boxRows) {
-  EncodeTiledFn fn = encodeFn();
-  if (!fn) return false;
-  cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, boxRows};
-  cuuint32_t estr[2] = {1, 1};
-  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void *)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return makeTileMap(m, base, rows, cols, ld, boxRows, 2);
 }
 
 template <int MODE>
-cudaError_t launch(const CUtensorMap &a, const CUtensorMap &b, const FcxGemmParams &p, const FcxDevComm &dc, int grid, cudaStream_t s) {
+cudaError_t launch(const CUtensorMap &a, const CUtensorMap &b, const FcxGemmParams &p, const FcxDevComm &dc, int grid, cudaStream_t s,
+                   const CUtensorMap *aLocal = nullptr) {
   static bool attr = false;
   if (!attr) {
     cudaError_t e = cudaFuncSetAttribute(fcxGemmKernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return e;
     attr = true;
   }
-  fcxGemmKernel<MODE><<<grid, THREADS, SMEM_BYTES, s>>>(a, b, p, dc);
+  fcxGemmKernel<MODE><<<grid, THREADS, SMEM_BYTES, s>>>(a, b, aLocal ? *aLocal : a, p, dc);
   return cudaGetLastError();
 }
 
 // Row blocks per band of the tile order (FLAGCX_GEMM_TILE_GROUP; 0 = plain row-major order).
-int tileGroup() {
-  static int g = -1;
-  if (g < 0) {
+int tileGroup(int nN) {
+  static int g = -2;
+  if (g == -2) {
     const char *e = getenv("FLAGCX_GEMM_TILE_GROUP");
-    g = e ? std::max(0, atoi(e)) : 8;
+    g = e ? std::max(0, atoi(e)) : -1;
   }
-  return g;
+  return g >= 0 ? g : (nN >= 24 ? 16 : 8);  // wide outputs: taller bands keep more of B in L2 per wave
+}
+
+// Columns per tile for a grid of `ctas`: 128 when the shorter last wave outweighs the smaller tile's overhead.
+int pickBn(int M, int N, int ctas) {
+  const int nM = (M + BM - 1) / BM;
+  const long t256 = (long)nM * ((N + 255) / 256), t128 = (long)nM * ((N + 127) / 128);
+  const double c256 = (double)((t256 + ctas - 1) / ctas), c128 = (double)((t128 + ctas - 1) / ctas) * 0.5 * 1.1;
+  const char *e = getenv("FLAGCX_GEMM_BN");
+  if (e) return atoi(e) == 128 ? 128 : 256;
+  return c128 < c256 ? 128 : 256;
 }
 
 int smCount() {
@@ -486,11 +414,12 @@ extern "C" cudaError_t fcxGemmBf16(const void *a, const void *b, void *c, int M,
   if (K % 8 || lda % 8 || ldb % 8 || ldc % 8 || M <= 0 || N <= 0 || K <= 0) return cudaErrorInvalidValue;
   if (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) return cudaErrorInvalidValue;
   CUtensorMap ma, mb;
-  if (!makeMap(&ma, a, M, K, lda, BM) || !makeMap(&mb, b, N, K, ldb, BN)) return cudaErrorNotSupported;
+  const int bn = pickBn(M, N, smCount());
+  if (!makeMap(&ma, a, M, K, lda, BM) || !makeMap(&mb, b, N, K, ldb, bn)) return cudaErrorNotSupported;
   FcxGemmParams p{};
-  p.M = M; p.N = N; p.K = K; p.c = c; p.ldc = ldc; p.errFlag = errFlag; p.rotate = 0; p.group = tileGroup();
+  p.M = M; p.N = N; p.K = K; p.c = c; p.ldc = ldc; p.errFlag = errFlag; p.rotate = 0; p.bn = bn; p.group = tileGroup((N + bn - 1) / bn);
   FcxDevComm dc{};
-  int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
   return launch<FCX_GEMM_PLAIN>(ma, mb, p, dc, std::min(tiles, smCount()), s);
 }
 
@@ -498,11 +427,12 @@ extern "C" cudaError_t fcxGemmBf16DynM(const void *a, const void *b, void *c, in
                                        int *errFlag, cudaStream_t s) {
   if (K % 8 || lda % 8 || ldb % 8 || ldc % 8 || Mmax <= 0 || N <= 0 || K <= 0) return cudaErrorInvalidValue;
   CUtensorMap ma, mb;
-  if (!makeMap(&ma, a, Mmax, K, lda, BM) || !makeMap(&mb, b, N, K, ldb, BN)) return cudaErrorNotSupported;
+  const int bn = pickBn(Mmax, N, smCount());
+  if (!makeMap(&ma, a, Mmax, K, lda, BM) || !makeMap(&mb, b, N, K, ldb, bn)) return cudaErrorNotSupported;
   FcxGemmParams p{};
-  p.M = Mmax; p.N = N; p.K = K; p.c = c; p.ldc = ldc; p.errFlag = errFlag; p.mPtr = mPtr; p.group = tileGroup();
+  p.M = Mmax; p.N = N; p.K = K; p.c = c; p.ldc = ldc; p.errFlag = errFlag; p.mPtr = mPtr; p.bn = bn; p.group = tileGroup((N + bn - 1) / bn);
   FcxDevComm dc{};
-  int tiles = ((Mmax + BM - 1) / BM) * ((N + BN - 1) / BN);
+  int tiles = ((Mmax + BM - 1) / BM) * ((N + bn - 1) / bn);
   return launch<FCX_GEMM_PLAIN>(ma, mb, p, dc, std::min(tiles, smCount()), s);
 }
 
@@ -511,10 +441,11 @@ extern "C" cudaError_t fcxGemmRowMapBf16(const FcxDevComm *dc, const void *a, co
                                          int *gridOut, cudaStream_t s) {
   if (K % 8 || lda % 8 || ldb % 8 || N % 8 || Mmax <= 0) return cudaErrorInvalidValue;
   CUtensorMap ma, mb;
-  if (!makeMap(&ma, a, Mmax, K, lda, BM) || !makeMap(&mb, b, N, K, ldb, BN)) return cudaErrorNotSupported;
+  const int bn = pickBn(Mmax, N, smCount());
+  if (!makeMap(&ma, a, Mmax, K, lda, BM) || !makeMap(&mb, b, N, K, ldb, bn)) return cudaErrorNotSupported;
   FcxGemmParams p{};
   p.M = Mmax; p.N = N; p.K = K; p.c = nullptr; p.ldc = N; p.errFlag = errFlag; p.mPtr = mPtr;
-  p.group = tileGroup();
+  p.bn = bn; p.group = tileGroup((N + bn - 1) / bn);
   p.rowInfo = (const int4 *)rowInfo; p.combineOff = combineOff; p.doneOff = doneOff; p.topk = topk;
   // a fixed grid: the receivers count one arrival per CTA of every rank
   int grid = smCount();
@@ -528,15 +459,18 @@ extern "C" cudaError_t fcxAgGemmBf16(const FcxDevComm *dc, const void *aLocal, c
   const int n = dc->nranks;
   if (K % 8 || ldb % 8 || ldc % 8 || M % (n * BM) || commCtas < 1) return cudaErrorInvalidValue;
   CUtensorMap ma, mb;
-  if (!makeMap(&ma, gathered, M, K, K, BM) || !makeMap(&mb, b, N, K, ldb, BN)) return cudaErrorNotSupported;
+  const int bn = pickBn(M, N, std::max(1, smCount() - commCtas));
+  CUtensorMap mal;
+  if (!makeMap(&ma, gathered, M, K, K, BM) || !makeMap(&mb, b, N, K, ldb, bn) || !makeMap(&mal, aLocal, M / n, K, K, BM))
+    return cudaErrorNotSupported;
   FcxGemmParams p{};
-  p.M = M; p.N = N; p.K = K; p.c = c; p.ldc = ldc; p.errFlag = errFlag;
+  p.M = M; p.N = N; p.K = K; p.c = c; p.ldc = ldc; p.errFlag = errFlag; p.bn = bn;
   p.rowsPerRank = M / n;
   p.rotate = dc->rank * (p.rowsPerRank / BM);
   p.aLocal = aLocal; p.gatherOff = gatherOff; p.flagOff = flagOff; p.epoch = epoch;
-  int tiles = (M / BM) * ((N + BN - 1) / BN);
+  int tiles = (M / BM) * ((N + bn - 1) / bn);
   p.gemmCtas = std::max(1, std::min(tiles, smCount() - commCtas));
-  return launch<FCX_GEMM_AG>(ma, mb, p, *dc, p.gemmCtas + commCtas, s);
+  return launch<FCX_GEMM_AG>(ma, mb, p, *dc, p.gemmCtas + commCtas, s, &mal);
 }
 
 extern "C" cudaError_t fcxGemmRsBf16(const FcxDevComm *dc, const void *a, const void *b, void *out, size_t stageOff, size_t flagOff, int M,
@@ -546,7 +480,7 @@ extern "C" cudaError_t fcxGemmRsBf16(const FcxDevComm *dc, const void *a, const 
   CUtensorMap ma, mb;
   if (!makeMap(&ma, a, M, K, lda, BM) || !makeMap(&mb, b, N, K, ldb, BN)) return cudaErrorNotSupported;
   FcxGemmParams p{};
-  p.M = M; p.N = N; p.K = K; p.c = out; p.ldc = ldc; p.errFlag = errFlag;
+  p.M = M; p.N = N; p.K = K; p.c = out; p.ldc = ldc; p.errFlag = errFlag; p.bn = BN;  // counters are laid out per 256 columns
   p.rowsPerRank = M / n;
   p.rotate = ((dc->rank + 1) % n) * (p.rowsPerRank / BM);
   p.stageOff = stageOff; p.flagOff = flagOff; p.epoch = epoch;

@@ -14,6 +14,7 @@ struct FcxGemmParams {
   void *c;              // PLAIN/AG: C; RS: this rank's [M/n, N] result
   int ldc;
   int rotate;           // first row block (of 128 rows) this rank works on
+  int bn;               // columns per tile: 256 or 128 (RS: 256)
   int group;            // PLAIN/ROWMAP: row blocks per band of the tile order (0: row-major)
   int rowsPerRank;      // M / nranks (AG, RS)
   int gemmCtas;         // AG: CTAs [0, gemmCtas) compute, the rest move data

@@ -33,7 +33,7 @@ def main():
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--comm-ctas", type=int, default=16)
+    ap.add_argument("--comm-ctas", type=int, default=0, help="0: sized per call")
     args = ap.parse_args()
     rank, world, lr = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     os.environ.setdefault("FLAGCX_SOCKET_IFNAME", "lo")
@@ -66,7 +66,7 @@ def main():
         import flagcx_b200
         from flagcx_b200.parallel.tp import TensorParallelContext
         comm = flagcx_b200.get_comm_handle(None, dev)
-        tp = TensorParallelContext(comm, world, rank, max_rows=T, max_k=H, max_n=H, comm_ctas=args.comm_ctas, device=dev)
+        tp = TensorParallelContext(comm, world, rank, max_rows=T, max_k=H, max_n=H, comm_ctas=args.comm_ctas or None, device=dev)
         if args.impl == "fused":
             ag = lambda x, w: tp.ag_gemm(x, w)  # noqa: E731
             rs = lambda a, w: tp.gemm_rs(a, w)  # noqa: E731

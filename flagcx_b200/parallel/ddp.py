@@ -170,10 +170,11 @@ class DataParallelTrainer:
         return loss
 
     def kernels_per_step(self) -> int:
-        """Launches of this framework's own kernels in one step: 2 fused
-        LayerNorm forward + 2x2 backward and bias-GELU forward + 3 backward per
-        layer, the final LayerNorm, the loss kernel, AdamW, and one all-reduce
-        kernel per bucket (chunked by the staging size)."""
+        """Launches of this framework's own kernels in one step: per layer 2
+        fused LayerNorm forward, 2 x 3 backward (dx, parameter partials, their
+        reduction), bias-GELU forward + 3 backward (dx, bias partials,
+        reduction); the final LayerNorm (1 + 3), the loss kernel, AdamW, and
+        one all-reduce kernel per bucket (chunked by the staging size)."""
         L = len(getattr(self.model, "blocks", []))
-        own = L * (2 + 4 + 1 + 3) + (1 + 2) + 1 + 1
+        own = L * (2 + 6 + 1 + 3) + (1 + 3) + 1 + 1
         return own + len(self.buckets)

@@ -21,10 +21,11 @@ import flagcx_b200
 
 
 class TensorParallelContext:
-    def __init__(self, comm: int, nranks: int, rank: int, max_rows: int, max_k: int, max_n: int, comm_ctas: int = 16,
+    def __init__(self, comm: int, nranks: int, rank: int, max_rows: int, max_k: int, max_n: int, comm_ctas: int | None = None,
                  device=None):
         """``max_rows``: tokens of the full (gathered) sequence; ``max_k``: widest gathered activation;
-        ``max_n``: widest reduce-scattered output."""
+        ``max_n``: widest reduce-scattered output; ``comm_ctas``: CTAs that move data in the all-gather GEMM
+        (default: sized per call so that the transfer takes about half the GEMM's time)."""
         self.nat = flagcx_b200.native()
         self.comm, self.n, self.rank = comm, nranks, rank
         self.comm_ctas = comm_ctas
@@ -51,7 +52,19 @@ class TensorParallelContext:
         self.ag_calls += 1
         rows, k = x_local.shape[0] * self.n, x_local.shape[1]
         gathered = self.gathered[par].view(-1)[: rows * k].view(rows, k)
-        return self.nat.ag_gemm(self.comm, x_local, gathered, self.ag_flags[par], w, epoch, self.comm_ctas, self.err)
+        return self.nat.ag_gemm(self.comm, x_local, gathered, self.ag_flags[par], w, epoch, self._comm_ctas(rows, k, w.shape[0]), self.err)
+
+    def _comm_ctas(self, rows: int, k: int, n_out: int) -> int:
+        """One data-moving CTA sustains about 40 GB/s over NVLink and 16 saturate the link; use as few as hide the
+        transfer of the remote rows behind the GEMM (estimated at 1.4 PFLOP/s)."""
+        if self.comm_ctas is not None:
+            return self.comm_ctas
+        if self.n == 1:
+            return 1
+        remote_bytes = (self.n - 1) * (rows // self.n) * k * 2
+        gemm_s = 2.0 * rows * k * n_out / 1.4e15
+        want = remote_bytes / (0.5 * gemm_s) / 40e9
+        return int(min(20, max(2, -(-want // 1))))
 
     def gemm_rs(self, a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         """``reduce_scatter(a @ w.T)`` over rows; a [rows, K], w [N, K] -> [rows/n, N]."""

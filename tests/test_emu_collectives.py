@@ -192,6 +192,51 @@ def test_reducescatter_allgather(lib, n, count):
         emu.close()
 
 
+@pytest.mark.parametrize("n", [2, 3, 8])
+def test_pipelined_sub_chunks(lib, n, monkeypatch):
+    """With a tiny sub-chunk size every large-message kind runs many pipeline iterations (push of chunk i
+    overlapping the reduction / copy-out of chunks i-1 and i-2), in place and out of place."""
+    monkeypatch.setenv("FLAGCX_PIPE_BYTES", "65536")
+    emu = Emu(lib, n, stage=16 << 20)
+    try:
+        count = 150001  # per-rank piece: odd, not a multiple of the unit, ~10-40 sub-chunks
+        for dtype in (torch.float32, torch.bfloat16):
+            xs = _rand(n, count * n, dtype, seed=11)
+            ref = _reduce_ref(xs, 0)
+            for kind, ctas in (("ar_twoshot", 5), ("ar_twoshot", 8)):
+                ys = [torch.empty_like(x) for x in xs]
+                emu.coll("allreduce", kind, ctas, xs, ys, count * n, dtype)
+                for y in ys:
+                    torch.testing.assert_close(y.float(), ref, atol=_tol(dtype) * n, rtol=_tol(dtype))
+            zs = [x.clone() for x in xs]  # in place
+            emu.coll("allreduce", "ar_twoshot", 6, zs, zs, count * n, dtype)
+            for z in zs:
+                torch.testing.assert_close(z.float(), ref, atol=_tol(dtype) * n, rtol=_tol(dtype))
+            ys = [torch.empty(count, dtype=dtype, device="cuda") for _ in range(n)]
+            emu.coll("reducescatter", "rs", 7, xs, ys, count, dtype)
+            for r, y in enumerate(ys):
+                torch.testing.assert_close(y.float(), ref[r * count:(r + 1) * count], atol=_tol(dtype) * n, rtol=_tol(dtype))
+            gs = [torch.empty(count * n, dtype=dtype, device="cuda") for _ in range(n)]
+            emu.coll("allgather", "ag", 5, ys, gs, count, dtype)
+            for g in gs:
+                assert torch.equal(g, torch.cat(ys))
+            outs = [torch.empty(count * n, dtype=dtype, device="cuda") for _ in range(n)]
+            emu.coll("a2a", "a2a", 6, xs, outs, count, dtype)
+            for r in range(n):
+                exp = torch.cat([xs[p][r * count:(r + 1) * count] for p in range(n)])
+                assert torch.equal(outs[r], exp)
+            root = n - 1
+            bs = [torch.empty(count * n, dtype=dtype, device="cuda") for _ in range(n)]
+            emu.coll("bcast", "bcast", 4, xs, bs, count * n, dtype, root=root)
+            for b in bs:
+                assert torch.equal(b, xs[root])
+            rd = [torch.empty(count * n, dtype=dtype, device="cuda") for _ in range(n)]
+            emu.coll("reduce", "reduce", 5, xs, rd, count * n, dtype, root=root)
+            torch.testing.assert_close(rd[root].float(), ref, atol=_tol(dtype) * n, rtol=_tol(dtype))
+    finally:
+        emu.close()
+
+
 @pytest.mark.parametrize("n", [2, 5, 8])
 def test_rooted_ops(lib, n):
     emu = Emu(lib, n)

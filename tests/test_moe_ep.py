@@ -51,11 +51,11 @@ def test_silu_mul(nat):
     nat.silu_mul(gu, h, rows)
     torch.cuda.synchronize()
     ref = torch.nn.functional.silu(gu[:, :512].float()) * gu[:, 512:].float()
-    assert (h[:257].float() - ref[:257]).abs().max() < 3e-2
+    assert ((h[:257].float() - ref[:257]).abs() / (ref[:257].abs() + 1.0)).max() < 2e-2
     assert bool((h[257:] == 0).all())
     nat.silu_mul(gu, h)
     torch.cuda.synchronize()
-    assert (h.float() - ref).abs().max() < 3e-2
+    assert ((h.float() - ref).abs() / (ref.abs() + 1.0)).max() < 2e-2
 
 
 def test_fused_layer_on_one_rank(nat, comm1):

@@ -22,7 +22,7 @@ def _worker(lib, uid, rank, world):
     nat = flagcx_b200.native()
     comm = lib.flagcxCommInitRank(world, uid, rank)
     rows, K, N = 128 * 4 * world, 1024, 1536
-    tp = TensorParallelContext(comm.value, world, rank, max_rows=rows, max_k=K, max_n=N, comm_ctas=8)
+    tp = TensorParallelContext(comm.value, world, rank, max_rows=rows, max_k=K, max_n=N)
     g = torch.Generator(device="cpu").manual_seed(7)
     w = (torch.randn(N, K, generator=g) * 0.5).bfloat16().cuda()
     w2 = (torch.randn(K, N, generator=g) * 0.5).bfloat16().cuda()
