@@ -13,11 +13,12 @@
 // The reference has no GEMM; its users would pair flagcx collectives with a
 // vendor scaled matmul.
 //
-// One CTA per SM, 256 threads, persistent over 128x128 tiles:
-//   warp 0    TMA producer (A and B slices of 128x128 bytes, 128-byte swizzle, 6 stages, no multicast)
-//   warp 1    MMA issuer (4 x K32 instructions per slice)
-//   warp 2    TMEM allocation
-//   warps 4-7 promotion + epilogue (one output row per thread, 128 fp32 accumulators in registers)
+// One CTA per SM, 384 threads, persistent over 128x128 tiles:
+//   warp 0     TMA producer (A and B slices of 128x128 bytes, 128-byte swizzle, 6 stages, no multicast)
+//   warp 1     MMA issuer (4 x K32 instructions per slice)
+//   warp 2     TMEM allocation
+//   warps 4-11 promotion + epilogue: warp w reads TMEM lanes 32*(w%4).. (one output row per thread) and the
+//              column half (w-4)/4 of the tile, 64 fp32 accumulators per thread, two TMEM loads in flight
 // Every wait is bounded; a wait that gives up sets the error flag and the kernel drains and returns.
 #include <algorithm>
 #include <cstdlib>
@@ -36,9 +37,10 @@ using namespace fcxmma;
 
 constexpr int BM = 128, BN = 128, BK = 128, STAGES = 6, ACC_BUFS = 4;
 constexpr int A_BYTES = BM * BK, B_BYTES = BN * BK, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int EPI_BYTES = 4 * 32 * 128;
+constexpr int EPI_WARPS = 8;
+constexpr int EPI_BYTES = EPI_WARPS * 32 * 128;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 256;
-constexpr int THREADS = 256;
+constexpr int THREADS = 384;
 
 struct Params {
   int M, N, K;
@@ -74,7 +76,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemmFp8Kernel(const __grid_constan
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbarInit(&fullBar[s], 1); mbarInit(&emptyBar[s], 1); }
-    for (int b = 0; b < ACC_BUFS; b++) { mbarInit(&tmemFull[b], 1); mbarInit(&tmemEmpty[b], 4); }
+    for (int b = 0; b < ACC_BUFS; b++) { mbarInit(&tmemFull[b], 1); mbarInit(&tmemEmpty[b], EPI_WARPS); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
@@ -128,7 +130,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemmFp8Kernel(const __grid_constan
       }
     }
   } else if (warp >= 4) {
-    const int q = warp & 3;
+    const int q = warp & 3, half = (warp - 4) >> 2;  // TMEM lane quarter (fixed by warp index % 4) and column half
+    constexpr int COLS = BN / 2;
     int buf = 0;
     uint32_t accPhase = 0;
     bool live = true;
@@ -138,62 +141,76 @@ __global__ void __launch_bounds__(THREADS, 1) gemmFp8Kernel(const __grid_constan
       const int row = mb * BM + q * 32 + lane;
       const float *saRow = p.sa + min(row, p.M - 1);
       const float *sbRow = p.sb + (size_t)nb * nK;
-      float acc[BN];
+      float acc[COLS];
 #pragma unroll
-      for (int j = 0; j < BN; j++) acc[j] = 0.f;
-      float scaleNext = saRow[0] * sbRow[0];
-      for (int kb = 0; kb < nK; kb++) {
-        const float scale = scaleNext;
-        if (kb + 1 < nK) scaleNext = saRow[(size_t)(kb + 1) * p.M] * sbRow[kb + 1];  // in flight while this slice is folded in
-        if (live) live = __all_sync(0xffffffffu, mbarWait(&tmemFull[buf], accPhase, err));
-        if (live) {
-          fenceAfter();
+      for (int j = 0; j < COLS; j++) acc[j] = 0.f;
+      // The scales of the next eight slices are always in flight (a global load takes several slice times).
+      constexpr int AHEAD = 8;
+      float ringA[AHEAD], ringB[AHEAD];
 #pragma unroll
-          for (int h = 0; h < BN / 32; h++) {
-            uint32_t r[32];
-            tmemLd32(tmemBase + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + 32 * h), r);
-            tmemLdWait();
+      for (int j = 0; j < AHEAD; j++) {
+        ringA[j] = j < nK ? saRow[(size_t)j * p.M] : 0.f;
+        ringB[j] = j < nK ? sbRow[j] : 0.f;
+      }
+      for (int kb0 = 0; kb0 < nK; kb0 += AHEAD) {
 #pragma unroll
-            for (int j = 0; j < 32; j++) acc[32 * h + j] = fmaf(scale, __uint_as_float(r[j]), acc[32 * h + j]);
+        for (int j = 0; j < AHEAD; j++) {
+          const int kb = kb0 + j;
+          if (kb < nK) {
+            const float scale = ringA[j] * ringB[j];
+            if (kb + AHEAD < nK) {
+              ringA[j] = saRow[(size_t)(kb + AHEAD) * p.M];
+              ringB[j] = sbRow[kb + AHEAD];
+            }
+            if (live) live = __all_sync(0xffffffffu, mbarWait(&tmemFull[buf], accPhase, err));
+            if (live) {
+              fenceAfter();
+              uint32_t r0[32], r1[32];
+              const uint32_t taddr = tmemBase + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + half * COLS);
+              tmemLd32(taddr, r0);
+              tmemLd32(taddr + 32, r1);
+              tmemLdWait();
+              fenceBefore();
+              __syncwarp();
+              if (lane == 0) mbarArrive(&tmemEmpty[buf]);  // the values are in registers: the accumulator may be overwritten
+#pragma unroll
+              for (int i = 0; i < 32; i++) acc[i] = fmaf(scale, __uint_as_float(r0[i]), acc[i]);
+#pragma unroll
+              for (int i = 0; i < 32; i++) acc[32 + i] = fmaf(scale, __uint_as_float(r1[i]), acc[32 + i]);
+            }
+            if (++buf == ACC_BUFS) { buf = 0; accPhase ^= 1; }
           }
-          fenceBefore();
-          __syncwarp();
-          if (lane == 0) mbarArrive(&tmemEmpty[buf]);
         }
-        if (++buf == ACC_BUFS) { buf = 0; accPhase ^= 1; }
       }
       if (!live) continue;
       // one row per lane -> transposed through shared memory so that 8 lanes store one 128-byte line of a row
       const int row0 = mb * BM + q * 32;
-      uint4 *stg = (uint4 *)(epiStage + (size_t)q * 32 * 128);
+      uint4 *stg = (uint4 *)(epiStage + (size_t)(warp - 4) * 32 * 128);
 #pragma unroll
-      for (int c0 = 0; c0 < BN; c0 += 64) {
+      for (int v = 0; v < 8; v++) {
+        uint4 o;
+        o.x = pack2(acc[8 * v + 0], acc[8 * v + 1]);
+        o.y = pack2(acc[8 * v + 2], acc[8 * v + 3]);
+        o.z = pack2(acc[8 * v + 4], acc[8 * v + 5]);
+        o.w = pack2(acc[8 * v + 6], acc[8 * v + 7]);
+        stg[lane * 8 + (v ^ (lane & 7))] = o;
+      }
+      __syncwarp();
+      const int col = nb * BN + half * COLS + (lane & 7) * 8;
 #pragma unroll
-        for (int v = 0; v < 8; v++) {
-          uint4 o;
-          o.x = pack2(acc[c0 + 8 * v + 0], acc[c0 + 8 * v + 1]);
-          o.y = pack2(acc[c0 + 8 * v + 2], acc[c0 + 8 * v + 3]);
-          o.z = pack2(acc[c0 + 8 * v + 4], acc[c0 + 8 * v + 5]);
-          o.w = pack2(acc[c0 + 8 * v + 6], acc[c0 + 8 * v + 7]);
-          stg[lane * 8 + (v ^ (lane & 7))] = o;
-        }
-        __syncwarp();
-        const int col = nb * BN + c0 + (lane & 7) * 8;
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-          const int rr = i * 4 + (lane >> 3);
-          uint4 o = stg[rr * 8 + ((lane & 7) ^ (rr & 7))];
-          if (row0 + rr < p.M) {
-            __nv_bfloat16 *d = p.c + (size_t)(row0 + rr) * p.ldc + col;
-            if (col + 8 <= p.N) *(uint4 *)d = o;
-            else {
-              const __nv_bfloat16 *e = (const __nv_bfloat16 *)&o;
-              for (int j = 0; j < 8 && col + j < p.N; j++) d[j] = e[j];
-            }
+      for (int i = 0; i < 8; i++) {
+        const int rr = i * 4 + (lane >> 3);
+        uint4 o = stg[rr * 8 + ((lane & 7) ^ (rr & 7))];
+        if (row0 + rr < p.M) {
+          __nv_bfloat16 *d = p.c + (size_t)(row0 + rr) * p.ldc + col;
+          if (col + 8 <= p.N) *(uint4 *)d = o;
+          else {
+            const __nv_bfloat16 *e = (const __nv_bfloat16 *)&o;
+            for (int j = 0; j < 8 && col + j < p.N; j++) d[j] = e[j];
           }
         }
-        __syncwarp();
       }
+      __syncwarp();
     }
   }
 

@@ -386,14 +386,16 @@ int tileGroup(int nN) {
   return g >= 0 ? g : (nN >= 24 ? 16 : 8);  // wide outputs: taller bands keep more of B in L2 per wave
 }
 
-// Columns per tile for a grid of `ctas`: 128 when the shorter last wave outweighs the smaller tile's overhead.
-int pickBn(int M, int N, int ctas) {
-  const int nM = (M + BM - 1) / BM;
-  const long t256 = (long)nM * ((N + 255) / 256), t128 = (long)nM * ((N + 127) / 128);
-  const double c256 = (double)((t256 + ctas - 1) / ctas), c128 = (double)((t128 + ctas - 1) / ctas) * 0.5 * 1.1;
-  const char *e = getenv("FLAGCX_GEMM_BN");
-  if (e) return atoi(e) == 128 ? 128 : 256;
-  return c128 < c256 ? 128 : 256;
+// Columns per tile.  128-column tiles cost almost as much as 256-column ones (the A tile is re-read for half the
+// math, and shared-memory bandwidth is what bounds the MMA), so they do not pay even when they fill the last
+// wave better; FLAGCX_GEMM_BN=128 selects them for experiments.
+int pickBn(int, int, int) {
+  static int bn = 0;
+  if (!bn) {
+    const char *e = getenv("FLAGCX_GEMM_BN");
+    bn = e && atoi(e) == 128 ? 128 : 256;
+  }
+  return bn;
 }
 
 int smCount() {

@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(THREADS, 1) moeDispatchKernel(const FcxDevComm
       const int pos = baseOf[e] + p.slot[i];
       if (pos >= p.cap) continue;
       const int t = i / p.K, k = i % p.K;
-      const uint4 *src = (const uint4 *)(p.x + (size_t)t * p.H);
+      const uint4 *src = (const uint4 *)((const __nv_bfloat16 *)p.x + (size_t)t * p.H);
       uint4 *dst = (uint4 *)(dc.heap[e] + p.recvOff + (size_t)pos * p.H * 2);
       int v = lane;
       for (; v + 96 < vecs; v += 128) {

@@ -97,8 +97,13 @@ def main():
     t = torch.tensor([e0.elapsed_time(e1) / args.iters], dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
+    agree = None
     if args.impl in ("fused", "unfused"):
         ep.check()
+        # the two paths of this library must agree element by element (a mean over random data would hide a misrouted row)
+        other = ep.unfused_forward(x, topk_idx, topk_w, w1, w2) if args.impl == "fused" else ep.forward(x, topk_idx, topk_w, w1, w2)
+        torch.cuda.synchronize()
+        agree = float(((out.float() - other.float()).abs().max() / other.float().abs().max()).item())
     # rows this rank's expert processed, and bytes this rank had to send to other ranks (there and back)
     rows = torch.tensor([float((topk_idx == r).sum().item()) for r in range(world)], dtype=torch.float64)
     remote = float(rows.sum() - rows[rank]) * H * 2
@@ -113,7 +118,7 @@ def main():
     if rank == 0:
         print(json.dumps({"bench": "ep_moe_layer", "impl": args.impl, "n_gpus": world, "tokens_per_rank": T, "hidden": H, "ffn": F,
                           "topk": K, "ms": round(ms, 3), "tokens_per_s": round(world * T / ms * 1e3, 1), "roofline_ms": round(roof_ms, 3),
-                          "fraction_of_roofline": round(roof_ms / ms, 3), "checksum": float(out.float().abs().mean().item()),
+                          "fraction_of_roofline": round(roof_ms / ms, 3), "checksum": float(out.float().abs().mean().item()), "max_rel_diff_vs_other_path": agree,
                           "peak": "of measured" if peaks.exists() else "of fallback"}))
     dist.destroy_process_group()
 

@@ -60,7 +60,7 @@ class ExpertParallelContext:
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.dispatch_ctas = dispatch_ctas
         balanced = tokens * topk  # n ranks x T x K choices over n experts
-        cap = min(nranks * tokens, int(balanced * capacity_factor))
+        cap = min(nranks * tokens * topk, int(balanced * capacity_factor)) if nranks > 1 else balanced
         self.cap = (cap + 127) // 128 * 128
         ht = self.nat.heap_tensor
         i32, i64, bf = torch.int32, torch.int64, torch.bfloat16

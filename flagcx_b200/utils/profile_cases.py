@@ -8,7 +8,7 @@ CUDA-event time with the achieved fraction of the measured HBM copy rate
 (MEASURED_PEAKS.json, else 6.65 TB/s).  Cases: adamw, cross_entropy,
 layernorm_fwd, layernorm_bwd, bias_gelu, emu_allreduce (8 emulated ranks,
 two-shot kernel, one cooperative launch on this GPU), emu_allgather, gemm
-(tcgen05 GEMM, against the measured cuBLAS rate), moe_dispatch and moe_layer
+(tcgen05 GEMM, against the measured cuBLAS rate), gemm_fp8 (block-scaled e4m3 GEMM), moe_dispatch and moe_layer
 (expert-parallel kernels on a one-rank communicator)."""
 from __future__ import annotations
 
@@ -108,6 +108,18 @@ def main():
         st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
         ms = timed(lambda: lib.call("flagcxEmuCollective", emu, op, kind, 16, s, r, count, 7, 7, ctypes.c_float(1.0), 0, 0, None, st))
         lib.call("flagcxEmuDestroy", emu)
+    elif args.case == "gemm_fp8":
+        M, N, K = 8192, 4096, 4096
+        a = (torch.randn(M, K, device="cuda") * 0.1).bfloat16()
+        b = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+        q, sa = nat.quant_fp8_act(a)
+        qw, sb = nat.quant_fp8_weight(b)
+        err = torch.zeros(1, dtype=torch.int32, device="cuda")
+        ms = timed(lambda: nat.gemm_fp8_nt(q, sa, qw, sb, err))
+        tf = 2.0 * M * N * K / (ms * 1e-3) / 1e12
+        print(json.dumps({"case": "gemm_fp8", "shape": [M, N, K], "ms": round(ms, 4), "tflops": round(tf, 1),
+                          "fraction_of_nominal_fp8_peak": round(tf / 4500.0, 3), "err": int(err.item())}))
+        return
     elif args.case == "gemm":
         # tensor-core bound: reported against the measured cuBLAS bf16 rate instead of the copy rate
         M, N, K = 8192, 4096, 4096
