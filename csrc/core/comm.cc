@@ -116,7 +116,7 @@ flagcxResult_t commCreate(flagcxComm **out, int nranks, const BootstrapHandle &h
         return flagcxInvalidUsage;
       }
     }
-    size_t stage = (size_t)((double)envInt("STAGE_BYTES", 128ll << 20) * heapScale);
+    size_t stage = (size_t)((double)envInt("STAGE_BYTES", 512ll << 20) * heapScale);
     stage = std::max<size_t>(stage, 1u << 20) & ~(size_t)4095;
     size_t chunk = (size_t)envInt("P2P_CHUNK_BYTES", 16ll << 20) & ~(size_t)4095;
     size_t user = (size_t)((double)envInt("HEAP_USER_BYTES", 512ll << 20) * heapScale);
@@ -141,7 +141,7 @@ flagcxResult_t commCreate(flagcxComm **out, int nranks, const BootstrapHandle &h
     d.mcHeap = c->heap.mcBase;
     d.heapBytes = c->heap.bytes;
     d.stageBytes = stage;
-    d.pipeBytes = (unsigned int)std::min<int64_t>(envInt("PIPE_BYTES", 8ll << 20), 1ll << 30);
+    d.pipeBytes = (unsigned int)std::min<int64_t>(envInt("PIPE_BYTES", 16ll << 20), 1ll << 30);
     d.p2pOff = p2pOff;
     d.p2pChunkBytes = chunk;
     d.userOff = userOff;

@@ -52,7 +52,7 @@ flagcxResult_t flagcxEmuCreate(flagcxEmu_t *out, int nranks, size_t stageBytes) 
     d.mcHeap = nullptr;
     d.heapBytes = e->heapBytes;
     d.stageBytes = e->stageBytes;
-    d.pipeBytes = (unsigned int)std::min<int64_t>(envInt("PIPE_BYTES", 8ll << 20), 1ll << 30);
+    d.pipeBytes = (unsigned int)std::min<int64_t>(envInt("PIPE_BYTES", 16ll << 20), 1ll << 30);
     d.p2pOff = p2pOff;
     d.p2pChunkBytes = e->chunk;
     d.userOff = e->heapBytes;

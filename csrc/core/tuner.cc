@@ -42,7 +42,7 @@ double localUs(double bytes, double nctas) { return bytes / std::min(kHbmRate, s
 // A kind with `depth` phases that moves linkBytes over NVLink and localBytes inside the GPU, cut into
 // sub-chunks of pipeBytes / (n-1) per piece.
 double pipelinedUs(double linkBytes, double localBytes, double pieceBytes, int depth, bool mm, int c, const TunerCaps &caps) {
-  const double n = caps.nranks, sub = std::max(16384.0, (double)(caps.pipeBytes ? caps.pipeBytes : (8u << 20)) / std::max(1.0, n - 1));
+  const double n = caps.nranks, sub = std::max(16384.0, (double)(caps.pipeBytes ? caps.pipeBytes : (16u << 20)) / std::max(1.0, n - 1));
   const double chunks = std::max(1.0, std::ceil(pieceBytes / sub));
   auto link = [&](double ctas) { return mm ? mmUs(linkBytes, ctas) : pushUs(linkBytes, ctas); };
   if (chunks <= 1.0) return kLaunchUs + (depth - 1) * kBarrierUs + link(c) + localUs(localBytes, c);

@@ -38,7 +38,7 @@ struct TunerCaps {
   bool multicast = false;
   size_t stageBytes = 0;
   int maxCtas = 64;
-  size_t pipeBytes = 0;  // bytes a rank sends per pipeline sub-chunk (0: 8 MiB)
+  size_t pipeBytes = 0;  // bytes a rank sends per pipeline sub-chunk (0: 16 MiB)
 };
 
 // Estimated duration in microseconds of one launch (cost-model prior).

@@ -112,29 +112,66 @@ __device__ __forceinline__ void copyFromSlot(char *user, const char *slot, size_
 // Large messages are cut into sub-chunks so that the phases of a collective overlap: while sub-chunk i is
 // pushed over NVLink, sub-chunk i-1 is reduced or copied out of local memory (and i-2 copied out, for the
 // three-phase kinds).  One cross-GPU CTA barrier per iteration orders phase k of a sub-chunk before phase
-// k+1 of the same sub-chunk.  Odd CTAs run the phases of an iteration in reverse order, so that at any time
-// about half of the CTAs are on the link and the others on local memory.  Sixteen CTAs saturate a
-// direction of NVLink; the rest of the grid hides the local traffic and the barrier latency behind it.
+// k+1 of the same sub-chunk.  Sixteen CTAs saturate a direction of NVLink; the rest of the grid hides the
+// local traffic behind it.
 __device__ __forceinline__ size_t subLen(size_t total, size_t sub, int c, size_t *lo) {
   *lo = (size_t)c * sub;
   return *lo < total ? min(sub, total - *lo) : 0;
 }
-__device__ __forceinline__ size_t pipeBytesOf(const FcxDevComm &dc) { return dc.pipeBytes ? (size_t)dc.pipeBytes : ((size_t)8 << 20); }
+__device__ __forceinline__ size_t pipeBytesOf(const FcxDevComm &dc) { return dc.pipeBytes ? (size_t)dc.pipeBytes : ((size_t)16 << 20); }
+
+// The barrier between iterations is split: a CTA posts "iteration i done" to its peers at the end of the
+// iteration and only checks the peers' post after it has issued the next sub-chunk's pushes, so the link
+// never idles while flags travel, and the release that precedes a post finds the pushes long acknowledged
+// (the local phases run in between).
+__device__ __forceinline__ void postPeers(const FcxDevComm &dc, int cta, uint64_t value, bool selfToo = false) {
+  __syncthreads();
+  const int t = threadIdx.x;
+  if (t < dc.nranks && (t != dc.rank || selfToo)) stRelease(flagSlot(dc, t, cta, dc.rank), value);
+}
+__device__ __forceinline__ bool waitPeers(const FcxDevComm &dc, int cta, uint64_t value, uint64_t seq) {
+  bool ok = true;
+  const int t = threadIdx.x;
+  if (t < dc.nranks && t != dc.rank) ok = waitGe(dc, flagSlot(dc, dc.rank, cta, t), value, t, FCX_WAIT_BARRIER, cta, seq);
+  return __syncthreads_and(ok);
+}
+
+// ---- role split -----------------------------------------------------------------------------------------
+// With two or more CTAs the grid is split into "link" CTAs, which only stream sub-chunks to the peers (each
+// one a contiguous share, back to back, never waiting for anybody), and "local" CTAs, which copy, reduce and
+// copy out inside this GPU as the sub-chunks arrive.  A link CTA raises its own flag on every peer after
+// each sub-chunk; a consumer waits for the flags of all link CTAs of the ranks it expects data from.  The
+// link therefore stays busy from the first to the last byte while local memory traffic runs beside it.
+__device__ __forceinline__ int linkCtasOf(int nctas) { return nctas < 2 ? 0 : (nctas < 8 ? 1 : min(32, nctas / 4)); }
+
+// Contiguous share of [0, len) for worker x of L, in multiples of `unit` bytes.
+__device__ __forceinline__ size_t shareOf(size_t len, int x, int L, size_t unit, size_t *lo) {
+  const size_t units = (len + unit - 1) / unit, per = (units + L - 1) / L;
+  *lo = min(len, (size_t)x * per * unit);
+  return min(len - *lo, per * unit);
+}
+
+// All threads of the CTA.  Wait until CTAs [first, first+count) of every rank in `srcMask` have posted `value`.
+__device__ __forceinline__ bool waitChunk(const FcxDevComm &dc, int cta, int first, int count, unsigned srcMask, uint64_t value,
+                                          uint64_t seq) {
+  bool ok = true;
+  const int n = dc.nranks;
+  for (int t = threadIdx.x; t < count * n && ok; t += blockDim.x) {
+    const int x = first + t / n, p = t % n;
+    if ((srcMask >> p) & 1u) ok = waitGe(dc, flagSlot(dc, dc.rank, x, p), value, p, FCX_WAIT_BARRIER, cta, seq);
+  }
+  return __syncthreads_and(ok);
+}
 
 template <int DEPTH, class FA, class FB, class FC>
 __device__ __forceinline__ bool pipelined(const FcxDevComm &dc, int cta, uint64_t seq, int chunks, FA stageA, FB stageB, FC stageC) {
   const int iters = chunks + DEPTH - 1;
   for (int i = 0; i < iters; i++) {
-    if (cta & 1) {
-      if (DEPTH == 3 && i >= 2 && i - 2 < chunks) stageC(i - 2);
-      if (i >= 1 && i - 1 < chunks) stageB(i - 1);
-      if (i < chunks) stageA(i);
-    } else {
-      if (i < chunks) stageA(i);
-      if (i >= 1 && i - 1 < chunks) stageB(i - 1);
-      if (DEPTH == 3 && i >= 2 && i - 2 < chunks) stageC(i - 2);
-    }
-    if (i + 1 < iters && !ctaBarrier(dc, cta, barrierValue(seq, 1 + (unsigned)i), seq)) return false;
+    if (i < chunks) stageA(i);                                              // needs nothing from the peers
+    if (i >= 1 && !waitPeers(dc, cta, barrierValue(seq, (unsigned)i), seq)) return false;  // peers finished iteration i-1
+    if (i >= 1 && i - 1 < chunks) stageB(i - 1);
+    if (DEPTH == 3 && i >= 2 && i - 2 < chunks) stageC(i - 2);
+    if (i + 1 < iters) postPeers(dc, cta, barrierValue(seq, 1 + (unsigned)i));
   }
   return true;
 }
@@ -371,18 +408,20 @@ __device__ void fcxCollBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta,
         size_t ne = elemsOf(p), lo = *loU * G;
         return lo >= ne ? 0 : min(cu * G, ne - lo);
       };
-      // phase 1: slice p of my vector goes to rank p
-      auto push = [&](int c) {
+      // phase 1: slice p of my vector goes to rank p (units [uLo, uLo+uCnt) of sub-chunk c, relative to the sub-chunk)
+      auto pushW = [&](int c, size_t tid0, size_t stride, int x, int L) {
         for (int k = 1; k < n; k++) {
           int p = (me + k) % n;
           size_t loU, ne = rangeOf(p, c, &loU);
-          if (ne)
-            copyToSlot(stagePtr(dc, p, seq) + (size_t)me * slotA + loU * INB, send + ((size_t)p * sliceElems + loU * G) * ESI, ne * ESI,
-                       INB, gtid, gstride);
+          if (!ne) continue;
+          size_t slo, slen = shareOf(ne * ESI, x, L, INB, &slo);  // bytes of this worker's share
+          if (slen)
+            copyToSlot(stagePtr(dc, p, seq) + (size_t)me * slotA + loU * INB + slo,
+                       send + ((size_t)p * sliceElems + loU * G) * ESI + slo, slen, INB, tid0, stride);
         }
       };
       // phase 2: combine my slice, hand the result to whoever needs it
-      auto combine = [&](int c) {
+      auto combineW = [&](int c, size_t tid0, size_t stride) {
         size_t loU, ne = rangeOf(me, c, &loU);
         if (!ne) return;
         char *dstSlots[FCX_MAX_RANKS];
@@ -400,19 +439,50 @@ __device__ void fcxCollBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta,
         }
         const char *own = send + ((size_t)me * sliceElems + loU * G) * ESI;
         reduceUnits<TIn, TOut, G>(dc, a, own, aligned16(own), stagePtr(dc, me, seq) + loU * INB, slotA, ne, dstUser,
-                                  dstUser && aligned16(dstUser), dstSlots, nd, gtid, gstride);
+                                  dstUser && aligned16(dstUser), dstSlots, nd, tid0, stride);
       };
       // phase 3: collect the other ranks' finished slices
-      auto collect = [&](int c) {
+      auto collectW = [&](int c, size_t tid0, size_t stride) {
         if (toRootOnly && me != a.root) return;
         for (int k = 1; k < n; k++) {
           int p = (me + k) % n;
           size_t loU, ne = rangeOf(p, c, &loU);
           if (ne)
             copyFromSlot(recv + ((size_t)p * sliceElems + loU * G) * ESO,
-                         stagePtr(dc, me, seq) + (size_t)n * slotA + (size_t)p * slotB + loU * OUTB, ne * ESO, OUTB, gtid, gstride);
+                         stagePtr(dc, me, seq) + (size_t)n * slotA + (size_t)p * slotB + loU * OUTB, ne * ESO, OUTB, tid0, stride);
         }
       };
+      const int L = linkCtasOf(nctas);
+      if (L > 0) {
+        const unsigned all = ((1u << n) - 1u) & ~(1u << me);
+        if (cta < L) {
+          for (int c = 0; c < chunks; c++) {
+            pushW(c, threadIdx.x, blockDim.x, cta, L);
+            postPeers(dc, cta, barrierValue(seq, 1 + (unsigned)c));
+          }
+        } else {
+          const int NL = nctas - L;
+          const size_t tid0 = (size_t)(cta - L) * blockDim.x + threadIdx.x, stride = (size_t)NL * blockDim.x;
+          // results travel to: everybody (all-reduce) or the root (reduce)
+          const bool collects = !toRootOnly || me == a.root;
+          bool ok = true;
+          for (int c = 0; c < chunks && ok; c++) {
+            ok = waitChunk(dc, cta, 0, L, all, barrierValue(seq, 1 + (unsigned)c), seq);
+            if (!ok) break;
+            combineW(c, tid0, stride);
+            postPeers(dc, cta, barrierValue(seq, 1 + (unsigned)c));
+            if (c >= 1 && collects) {
+              ok = waitChunk(dc, cta, L, NL, all, barrierValue(seq, (unsigned)c), seq);
+              if (ok) collectW(c - 1, tid0, stride);
+            }
+          }
+          if (ok && collects && waitChunk(dc, cta, L, NL, all, barrierValue(seq, (unsigned)chunks), seq)) collectW(chunks - 1, tid0, stride);
+        }
+        break;
+      }
+      auto push = [&](int c) { pushW(c, gtid, gstride, 0, 1); };
+      auto combine = [&](int c) { combineW(c, gtid, gstride); };
+      auto collect = [&](int c) { collectW(c, gtid, gstride); };
       pipelined<3>(dc, cta, seq, chunks, push, combine, collect);
       break;
     }
@@ -520,23 +590,43 @@ __device__ void fcxCollBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta,
         size_t lo = *loU * G;
         return lo >= a.count ? 0 : min(cu * G, a.count - lo);
       };
-      auto push = [&](int c) {
+      auto pushW = [&](int c, size_t tid0, size_t stride, int x, int L) {
         size_t loU, ne = rangeOf(c, &loU);
         if (!ne) return;
+        size_t slo, slen = shareOf(ne * ESI, x, L, INB, &slo);
+        if (!slen) return;
         for (int k = 1; k < n; k++) {
           int p = (me + k) % n;
-          copyToSlot(stagePtr(dc, p, seq) + (size_t)me * slot + loU * INB, send + ((size_t)p * a.sendStride + loU * G) * ESI, ne * ESI, INB,
-                     gtid, gstride);
+          copyToSlot(stagePtr(dc, p, seq) + (size_t)me * slot + loU * INB + slo, send + ((size_t)p * a.sendStride + loU * G) * ESI + slo, slen,
+                     INB, tid0, stride);
         }
       };
-      auto combine = [&](int c) {
+      auto combineW = [&](int c, size_t tid0, size_t stride) {
         size_t loU, ne = rangeOf(c, &loU);
         if (!ne) return;
         const char *own = send + ((size_t)me * a.sendStride + loU * G) * ESI;
         char *out = recv + loU * G * ESO;
         reduceUnits<TIn, TOut, G>(dc, a, own, aligned16(own), stagePtr(dc, me, seq) + loU * INB, slot, ne, out, aligned16(out), nullptr, 0,
-                                  gtid, gstride);
+                                  tid0, stride);
       };
+      const int L = linkCtasOf(nctas);
+      if (L > 0) {
+        if (cta < L) {
+          for (int c = 0; c < chunks; c++) {
+            pushW(c, threadIdx.x, blockDim.x, cta, L);
+            postPeers(dc, cta, barrierValue(seq, 1 + (unsigned)c));
+          }
+        } else {
+          const size_t tid0 = (size_t)(cta - L) * blockDim.x + threadIdx.x, stride = (size_t)(nctas - L) * blockDim.x;
+          for (int c = 0; c < chunks; c++) {
+            if (!waitChunk(dc, cta, 0, L, ((1u << n) - 1u) & ~(1u << me), barrierValue(seq, 1 + (unsigned)c), seq)) break;
+            combineW(c, tid0, stride);
+          }
+        }
+        break;
+      }
+      auto push = [&](int c) { pushW(c, gtid, gstride, 0, 1); };
+      auto combine = [&](int c) { combineW(c, gtid, gstride); };
       pipelined<2>(dc, cta, seq, chunks, push, combine, combine);
       break;
     }
@@ -588,7 +678,7 @@ __device__ void fcxMoveBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta,
         break;
       case FCX_K_BCAST:
         if (me == a.root) {
-          if (dc.mcHeap != nullptr && a.useMc) { mcSrc = send; mcDst = dc.mcHeap + stageOff; }
+          if (dc.mcHeap != nullptr && a.useMc && n > 2) { mcSrc = send; mcDst = dc.mcHeap + stageOff; }  // two ranks: a plain store does the same
           else
             for (int p = 0; p < n; p++)
               if (p != me) { outSrc[p] = send; outDst[p] = stagePtr(dc, p, seq); }
@@ -634,38 +724,79 @@ __device__ void fcxMoveBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta,
     }
     const size_t sub = max((size_t)16384, (pipeBytesOf(dc) / (size_t)max(1, n - 1)) & ~(size_t)15);
     const int chunks = (int)max((size_t)1, (bytes + sub - 1) / sub);
-    auto push = [&](int c) {
-      size_t lo, len = subLen(bytes, sub, c, &lo);
+    // remote part of sub-chunk c: bytes [off, off+len) of every outgoing piece, worked on by threads (tid0, stride)
+    auto pushRange = [&](size_t off, size_t len, size_t tid0, size_t stride) {
       if (!len) return;
       if (mcDst) {
         const bool al = aligned16(mcSrc);
         const size_t nunits = (len + 15) / 16;
-        for (size_t u = gtid; u < nunits; u += gstride) {
+        for (size_t u = tid0; u < nunits; u += stride) {
           int nv = (int)min((size_t)16, len - u * 16);
           uint4 v;
-          if (al && nv == 16) v = ld16(mcSrc + lo + u * 16);
+          if (al && nv == 16) v = ld16(mcSrc + off + u * 16);
           else {
             union { uint4 q; char c[16]; } w;
             w.q = make_uint4(0, 0, 0, 0);
-            for (int i = 0; i < nv; i++) w.c[i] = mcSrc[lo + u * 16 + i];
+            for (int i = 0; i < nv; i++) w.c[i] = mcSrc[off + u * 16 + i];
             v = w.q;
           }
-          mmStore(mcDst + lo + u * 16, v);
+          mmStore(mcDst + off + u * 16, v);
         }
       }
       for (int k = 1; k < n; k++) {
         int p = (me + k) % n;
-        if (outSrc[p]) copyToSlot(outDst[p] + lo, outSrc[p] + lo, len, 16, gtid, gstride);
+        if (outSrc[p]) copyToSlot(outDst[p] + off, outSrc[p] + off, len, 16, tid0, stride);
       }
-      if (selfSrc && selfSrc != selfDst) copyUnits(selfDst + lo, selfSrc + lo, len, 16, gtid, gstride);
     };
-    auto pull = [&](int c) {
-      size_t lo, len = subLen(bytes, sub, c, &lo);
+    auto selfRange = [&](size_t off, size_t len, size_t tid0, size_t stride) {
+      if (len && selfSrc && selfSrc != selfDst) copyUnits(selfDst + off, selfSrc + off, len, 16, tid0, stride);
+    };
+    auto pullRange = [&](size_t off, size_t len, size_t tid0, size_t stride) {
       if (!len) return;
       for (int k = 1; k < n; k++) {
         int p = (me + k) % n;
-        if (inSrc[p]) copyFromSlot(inDst[p] + lo, inSrc[p] + lo, len, 16, gtid, gstride);
+        if (inSrc[p]) copyFromSlot(inDst[p] + off, inSrc[p] + off, len, 16, tid0, stride);
       }
+    };
+    const int L = linkCtasOf(nctas);
+    if (L > 0) {
+      unsigned inMask = 0;
+      bool sends = mcDst != nullptr;
+      for (int p = 0; p < n; p++) {
+        if (inSrc[p]) inMask |= 1u << p;
+        if (outSrc[p]) sends = true;
+      }
+      // all-to-all in place: a piece may only be overwritten once this rank's own link CTAs have sent it
+      const bool aliased = a.kind == FCX_K_A2A && send == recv;
+      if (aliased && inMask) inMask |= 1u << me;
+      if (cta < L) {
+        for (int c = 0; c < chunks; c++) {
+          size_t lo, len = subLen(bytes, sub, c, &lo), slo, slen = shareOf(len, cta, L, 16, &slo);
+          if (sends) pushRange(lo + slo, slen, threadIdx.x, blockDim.x);
+          postPeers(dc, cta, barrierValue(seq, 1 + (unsigned)c), aliased);
+        }
+      } else {
+        const size_t tid0 = (size_t)(cta - L) * blockDim.x + threadIdx.x, stride = (size_t)(nctas - L) * blockDim.x;
+        for (int c = 0; c < chunks; c++) {
+          size_t lo, len = subLen(bytes, sub, c, &lo);
+          selfRange(lo, len, tid0, stride);
+          if (inMask) {
+            if (!waitChunk(dc, cta, 0, L, inMask, barrierValue(seq, 1 + (unsigned)c), seq)) break;
+            pullRange(lo, len, tid0, stride);
+          }
+        }
+      }
+      epilogue(dc, seq, nctas);
+      return;
+    }
+    auto push = [&](int c) {
+      size_t lo, len = subLen(bytes, sub, c, &lo);
+      pushRange(lo, len, gtid, gstride);
+      selfRange(lo, len, gtid, gstride);
+    };
+    auto pull = [&](int c) {
+      size_t lo, len = subLen(bytes, sub, c, &lo);
+      pullRange(lo, len, gtid, gstride);
     };
     pipelined<2>(dc, cta, seq, chunks, push, pull, pull);
     epilogue(dc, seq, nctas);

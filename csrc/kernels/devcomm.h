@@ -73,7 +73,7 @@ struct FcxDevComm {
   char *mcHeap;                  // multicast alias of the heaps, or null
   size_t heapBytes;
   size_t stageBytes;             // bytes of one staging half
-  unsigned int pipeBytes;        // bytes a rank sends per pipeline sub-chunk of a large collective (0: 8 MiB)
+  unsigned int pipeBytes;        // bytes a rank sends per pipeline sub-chunk of a large collective (0: 16 MiB)
   size_t p2pOff, p2pChunkBytes;  // per-peer send staging: [peer][2][p2pChunkBytes]
   size_t userOff;                // start of the flagcxMemAlloc area
   FcxDevError *err;              // host-mapped

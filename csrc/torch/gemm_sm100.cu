@@ -65,18 +65,19 @@ __device__ __forceinline__ uint32_t instrDesc(int bn) {
 // the blocks this rank owns come last.
 __device__ __forceinline__ void tileCoord(const FcxGemmParams &p, int nM, int t, int *mb, int *nb) {
   const int nN = (p.N + p.bn - 1) / p.bn;
+  int g;
   if (p.group > 0) {
     // Row blocks in bands of `group`; inside a band the row block changes fastest, so the CTAs of one wave
     // share a few A row blocks and a few B column blocks and both stay in L2.
     const int perBand = p.group * nN, band = t / perBand, first = band * p.group;
     const int rowsHere = min(p.group, nM - first), within = t - band * perBand;
-    *mb = first + within % rowsHere;
+    g = first + within % rowsHere;
     *nb = within / rowsHere;
-    return;
+  } else {
+    g = t / nN;
+    *nb = t % nN;
   }
-  int g = t / nN;
-  *nb = t % nN;
-  *mb = (g + p.rotate) % nM;
+  *mb = (g + p.rotate) % nM;  // AG: the local rows first; RS: the rows this rank owns last
 }
 
 template <int MODE>
@@ -466,9 +467,10 @@ extern "C" cudaError_t fcxAgGemmBf16(const FcxDevComm *dc, const void *aLocal, c
   if (!makeMap(&ma, gathered, M, K, K, BM) || !makeMap(&mb, b, N, K, ldb, bn) || !makeMap(&mal, aLocal, M / n, K, K, BM))
     return cudaErrorNotSupported;
   FcxGemmParams p{};
-  p.M = M; p.N = N; p.K = K; p.c = c; p.ldc = ldc; p.errFlag = errFlag; p.bn = bn;
+  p.M = M; p.N = N; p.K = K; p.c = c; p.ldc = ldc; p.errFlag = errFlag; p.bn = bn; p.group = tileGroup((N + bn - 1) / bn);
   p.rowsPerRank = M / n;
   p.rotate = dc->rank * (p.rowsPerRank / BM);
+  p.group = std::max(1, std::min(p.group, p.rowsPerRank / BM));  // a band never mixes rows of two ranks: they arrive at different times
   p.aLocal = aLocal; p.gatherOff = gatherOff; p.flagOff = flagOff; p.epoch = epoch;
   int tiles = (M / BM) * ((N + bn - 1) / bn);
   p.gemmCtas = std::max(1, std::min(tiles, smCount() - commCtas));
@@ -483,6 +485,7 @@ extern "C" cudaError_t fcxGemmRsBf16(const FcxDevComm *dc, const void *a, const 
   if (!makeMap(&ma, a, M, K, lda, BM) || !makeMap(&mb, b, N, K, ldb, BN)) return cudaErrorNotSupported;
   FcxGemmParams p{};
   p.M = M; p.N = N; p.K = K; p.c = out; p.ldc = ldc; p.errFlag = errFlag; p.bn = BN;  // counters are laid out per 256 columns
+  p.group = tileGroup((N + BN - 1) / BN);
   p.rowsPerRank = M / n;
   p.rotate = ((dc->rank + 1) % n) * (p.rowsPerRank / BM);
   p.stageOff = stageOff; p.flagOff = flagOff; p.epoch = epoch;
