@@ -187,7 +187,11 @@ flagcxResult_t launchCollective(flagcxComm *c, const PendingOp &o) {
     a.send = send;
     a.recv = recv;
     // like the reference (flagcx/flagcx.cc:1613-1616) the variable all-to-all is not searched online
-    Plan p = c->tuner->peek(o.op, std::max<size_t>(maxPair, 16), o.dt, o.red, false);
+    // The ranks see different counts, so nothing derived from them may shape the launch: every rank must
+    // run the same number of CTAs (they pair up across GPUs).
+    (void)maxPair;
+    static const int a2avCtas = (int)std::max<int64_t>(1, std::min<int64_t>(envInt("A2AV_CTAS", 32), FCX_MAX_CTAS));
+    Plan p{FCX_K_A2AV, a2avCtas};
     return launchOne(c, a, p, o.stream, false);
   }
 

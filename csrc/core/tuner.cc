@@ -32,7 +32,7 @@ namespace {
 // directions at once; a CTA copies about 60 GB/s inside its own memory.  Large messages run as a software
 // pipeline over sub-chunks in which about half of the CTAs are on the link and half on local memory.
 constexpr double kLaunchUs = 2.2, kBarrierUs = 1.8, kLLUs = 1.6, kPipeBarrierUs = 0.4;
-constexpr double kLinkRate = 680e3, kCtaPushRate = 40e3, kCtaMmRate = 30e3;
+constexpr double kLinkRate = 680e3, kCtaPushRate = 40e3, kCtaMmRate = 3.5e3;  // multimem: 64-128 CTAs reached 430-490 GB/s on four GPUs
 constexpr double kHbmRate = 5500e3, kCtaLocalRate = 60e3;
 
 double pushUs(double bytes, double nctas) { return bytes / std::min(kLinkRate, std::max(1.0, nctas) * kCtaPushRate); }

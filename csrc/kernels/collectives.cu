@@ -758,8 +758,15 @@ __device__ void fcxMoveBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta,
         if (inSrc[p]) copyFromSlot(inDst[p] + off, inSrc[p] + off, len, 16, tid0, stride);
       }
     };
-    const int L = linkCtasOf(nctas);
-    if (L > 0) {
+    // Link CTAs of this rank and of the ranks it receives from.  Rooted kinds are lopsided: the sending side
+    // puts almost the whole grid on the link and the receiving side has no link work at all.
+    int L = linkCtasOf(nctas), Lsrc = L;
+    if (nctas >= 2) {
+      const int most = nctas - max(1, nctas / 8);
+      if (a.kind == FCX_K_BCAST || a.kind == FCX_K_SCATTER) { Lsrc = most; L = me == a.root ? most : 0; }
+      if (a.kind == FCX_K_GATHER) { Lsrc = nctas; L = me == a.root ? 0 : nctas; }
+    }
+    if (nctas >= 2) {
       unsigned inMask = 0;
       bool sends = mcDst != nullptr;
       for (int p = 0; p < n; p++) {
@@ -781,7 +788,7 @@ __device__ void fcxMoveBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta,
           size_t lo, len = subLen(bytes, sub, c, &lo);
           selfRange(lo, len, tid0, stride);
           if (inMask) {
-            if (!waitChunk(dc, cta, 0, L, inMask, barrierValue(seq, 1 + (unsigned)c), seq)) break;
+            if (!waitChunk(dc, cta, 0, Lsrc, inMask, barrierValue(seq, 1 + (unsigned)c), seq)) break;
             pullRange(lo, len, tid0, stride);
           }
         }
