@@ -96,3 +96,75 @@ class TensorParallelContext:
         out = torch.empty(a.shape[0] // self.n, w.shape[0], dtype=a.dtype, device=a.device)
         self.nat.comm_reduce_scatter(self.comm, part, out, 0)
         return out
+
+
+class _ColumnParallel(torch.autograd.Function):
+    """y = all_gather(x_local) @ w.T with sequence-parallel input (rows sharded) and column-sharded weight.
+
+    forward  : one fused all-gather -> GEMM kernel
+    backward : dx_local = reduce_scatter(dy @ w)   one fused GEMM -> reduce-scatter kernel
+               dw       = dy.T @ all_gather(x)     library GEMM on the rows gathered by the forward kernel
+    """
+
+    @staticmethod
+    def forward(ctx, x_local, w, tp):
+        par = tp.ag_calls & 1
+        y = tp.ag_gemm(x_local, w)
+        rows, k = x_local.shape[0] * tp.n, x_local.shape[1]
+        # the forward kernel left every rank's rows in the workspace (the local block is only read in place)
+        gathered = tp.gathered[par].view(-1)[: rows * k].view(rows, k)
+        full = gathered.clone()
+        r0 = tp.rank * x_local.shape[0]
+        full[r0:r0 + x_local.shape[0]] = x_local
+        ctx.save_for_backward(full, w)
+        ctx.tp = tp
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        full, w = ctx.saved_tensors
+        tp = ctx.tp
+        dy = dy.contiguous()
+        dx_local = tp.gemm_rs(dy, w.t().contiguous())  # [rows, N] @ [N, K] -> rows/n x K
+        dw = dy.t() @ full
+        return dx_local, dw, None
+
+
+class _RowParallel(torch.autograd.Function):
+    """z_local = reduce_scatter(a @ w.T) with row-sharded weight (K sharded) and sequence-parallel output.
+
+    forward  : one fused GEMM -> reduce-scatter kernel
+    backward : da = all_gather(dz_local) @ w       one fused all-gather -> GEMM kernel
+               dw = all_gather(dz_local).T @ a     library GEMM on the rows gathered by that kernel
+    """
+
+    @staticmethod
+    def forward(ctx, a, w, tp):
+        ctx.save_for_backward(a, w)
+        ctx.tp = tp
+        return tp.gemm_rs(a, w)
+
+    @staticmethod
+    def backward(ctx, dz_local):
+        a, w = ctx.saved_tensors
+        tp = ctx.tp
+        dz_local = dz_local.contiguous()
+        par = tp.ag_calls & 1
+        da = tp.ag_gemm(dz_local, w.t().contiguous())  # [rows, N] @ [N, K_local]
+        rows, ncols = dz_local.shape[0] * tp.n, dz_local.shape[1]
+        gathered = tp.gathered[par].view(-1)[: rows * ncols].view(rows, ncols)
+        full = gathered.clone()
+        r0 = tp.rank * dz_local.shape[0]
+        full[r0:r0 + dz_local.shape[0]] = dz_local
+        dw = full.t() @ a
+        return da, dw, None
+
+
+def column_parallel_linear(x_local: torch.Tensor, w: torch.Tensor, tp: TensorParallelContext) -> torch.Tensor:
+    """Differentiable ``all_gather(x_local) @ w.T`` on the fused kernels (entry of a tensor-parallel block)."""
+    return _ColumnParallel.apply(x_local, w, tp)
+
+
+def row_parallel_linear(a: torch.Tensor, w: torch.Tensor, tp: TensorParallelContext) -> torch.Tensor:
+    """Differentiable ``reduce_scatter(a @ w.T)`` on the fused kernels (exit of a tensor-parallel block)."""
+    return _RowParallel.apply(a, w, tp)

@@ -80,3 +80,27 @@ def test_fused_forms_on_one_rank(nat, comm1):
         ref = _ref(x, w)
         _close(y, ref, 512)
         _close(z, ref, 512)
+
+
+def test_tensor_parallel_linears_forward_and_backward(nat, comm1):
+    """Autograd wrappers of the fused kernels against plain PyTorch autograd (one rank: gather and scatter are identities)."""
+    from flagcx_b200.parallel.tp import TensorParallelContext, column_parallel_linear, row_parallel_linear
+    lib, comm = comm1
+    tp = TensorParallelContext(comm.value, 1, 0, max_rows=512, max_k=1024, max_n=1024)
+    torch.manual_seed(5)
+    x = (torch.randn(512, 256, device="cuda") * 0.5).bfloat16().requires_grad_()
+    w1 = (torch.randn(1024, 256, device="cuda") * 0.05).bfloat16().requires_grad_()
+    w2 = (torch.randn(256, 1024, device="cuda") * 0.05).bfloat16().requires_grad_()
+    h = column_parallel_linear(x, w1, tp)
+    z = row_parallel_linear(torch.nn.functional.gelu(h), w2, tp)
+    z.float().square().mean().backward()
+    torch.cuda.synchronize()
+    tp.check()
+    got = [t.grad.float().clone() for t in (x, w1, w2)]
+    xr, w1r, w2r = (t.detach().float().requires_grad_() for t in (x, w1, w2))
+    hr = (xr @ w1r.t()).bfloat16().float()
+    zr = torch.nn.functional.gelu(hr) @ w2r.t()
+    zr.square().mean().backward()
+    _close(z.detach(), zr.detach(), 1024)
+    for g, r in zip(got, (xr.grad, w1r.grad, w2r.grad)):
+        assert (g - r).abs().max() / (r.abs().max() + 1e-12) < 5e-2
