@@ -34,7 +34,7 @@ from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent
 
-BASELINE_PUBLISHED = None  # the reference publishes no training throughput
+BASELINE_PUBLISHED = None  # the reference publishes no training throughput for any model
 
 
 def parse():
