@@ -10,6 +10,7 @@
 //              into one kernel launch and collectives are issued in order;
 //   hybrid   - more than one cluster: the C2C planner (c2c/planner.cc);
 //   direct   - a kernel of collectives.cu, variant picked by the tuner.
+#include <nvtx3/nvToolsExt.h>
 #include "comm.h"
 #include "hostcoll.h"
 #include "hosttypes.h"
@@ -343,9 +344,28 @@ static flagcxResult_t validate(flagcxComm_t c, const PendingOp &o) {
   return flagcxSuccess;
 }
 
+// FLAGCX_NVTX=1: one NVTX range per API call ("flagcx allreduce 1048576 B"), visible in Nsight Systems timelines.
+namespace {
+const char *const kOpLabel[] = {"send", "recv", "broadcast", "gather", "scatter", "reduce", "allreduce", "allgather",
+                                "reducescatter", "alltoall", "alltoallv", "barrier"};
+struct NvtxRange {
+  bool on;
+  NvtxRange(int op, size_t bytes) {
+    static const bool enabled = envInt("NVTX", 0) != 0;
+    on = enabled;
+    if (!on) return;
+    char label[96];
+    snprintf(label, sizeof label, "flagcx %s %zu B", op >= 0 && op < 12 ? kOpLabel[op] : "op", bytes);
+    nvtxRangePushA(label);
+  }
+  ~NvtxRange() { if (on) nvtxRangePop(); }
+};
+}  // namespace
+
 static flagcxResult_t submit(flagcxComm_t c, PendingOp &&o) {
   FCX_CHECK(validate(c, o));
   size_t bytes = o.count * dtypeSize(o.dt);
+  NvtxRange nvtx((int)o.op, bytes);
   if (o.op != flagcxCommNoOp) count(c, o.op, bytes);
   FCX_TRACE(SUB_CALL, "op %d count %zu dtype %d red %d root %d", (int)o.op, o.count, (int)o.dt, (int)o.red, o.root);
   if (tGroupDepth > 0) {

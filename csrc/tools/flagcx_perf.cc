@@ -17,6 +17,7 @@
 // Sizes follow the reference: the size is the whole buffer; all-gather, reduce-scatter, all-to-all, gather and scatter
 // move size/ranks per rank.  Reported: device time (CUDA events around the -n calls), MAX over ranks, and the
 // reference-style host-timed mean over ranks; bus-bandwidth factors as in the reference's tests.
+#include <algorithm>
 #include <cuda_runtime.h>
 #include <dlfcn.h>
 #include <sys/wait.h>
@@ -108,7 +109,7 @@ size_t parseSize(const char *s) {
 
 struct Opts {
   std::string op = "allreduce", lib, dtype = "float", json;
-  int ranks = 0, warm = 5, iters = 20, print = 0, root = 0, reg = 0, check = 0;
+  int ranks = 0, warm = 5, iters = 20, print = 0, root = 0, reg = 0, check = 0, splitMask = 0;
   size_t minB = 8, maxB = 128u << 20;
   double factor = 2;
 };
@@ -142,20 +143,26 @@ float bf16ToF(uint16_t v) { uint32_t u = (uint32_t)v << 16; float f; memcpy(&f, 
 int worker(const Opts &o, int rank, int n, int idRead, int idWrite[], int outFd) {
   Api api;
   if (!loadApi(o.lib.c_str(), &api)) return 3;
-  cudaSetDevice(rank);
+  cudaSetDevice(rank);  // before the split: one GPU per world rank
   cudaFree(0);
   flagcxHandlerGroup_t hg;
   CK(api.HandleInit(&hg));
+  // -s mask: the ranks with the same (rank & mask) form one communicator, like the reference's harness
+  // (test/perf/tools.cc:16-20); world rank stays the device index.
+  const int worldRank = rank, worldSize = n, color = worldRank & o.splitMask;
+  std::vector<int> members;
+  for (int r = 0; r < worldSize; r++)
+    if ((r & o.splitMask) == color) members.push_back(r);
+  n = (int)members.size();
+  rank = (int)(std::find(members.begin(), members.end(), worldRank) - members.begin());
   flagcxUniqueId id;
   if (rank == 0) {
-    flagcxUniqueId_t p = &id;
     // the reference allocates the id itself and overwrites the pointer
     flagcxUniqueId_t q = nullptr;
     CK(api.GetUniqueId(&q));
     memcpy(&id, q, sizeof id);
-    (void)p;
     for (int r = 1; r < n; r++)
-      if (write(idWrite[r], &id, sizeof id) != (ssize_t)sizeof id) return 4;
+      if (write(idWrite[members[r]], &id, sizeof id) != (ssize_t)sizeof id) return 4;
   } else if (read(idRead, &id, sizeof id) != (ssize_t)sizeof id) {
     return 4;
   }
@@ -313,6 +320,7 @@ int main(int argc, char **argv) {
     else if (k == "-p") o.print = atoi(v);
     else if (k == "-r") o.root = atoi(v);
     else if (k == "-R") o.reg = atoi(v);
+    else if (k == "-s") o.splitMask = (int)strtol(v, nullptr, 0);
     else if (k == "-L") o.lib = v;
     else if (k == "-d") o.dtype = v;
     else if (k == "-c") o.check = atoi(v);
@@ -371,10 +379,12 @@ int main(int argc, char **argv) {
   int lastOp = -1;
   for (size_t i = 0; i < all[0].size(); i++) {
     const std::string &opn = ops[all[0][i].op];
-    const double f = busFactor(opn, n);
+    int groupSize = 0;
+    for (int r = 0; r < n; r++) groupSize += ((r & o.splitMask) == 0);
+    const double f = busFactor(opn, groupSize);
     if (all[0][i].op != lastOp) {
       lastOp = all[0][i].op;
-      printf("# %s, %d ranks, %s, library %s\n", opn.c_str(), n, o.dtype.c_str(), o.lib.c_str());
+      printf("# %s, %d ranks%s, %s, library %s\n", opn.c_str(), groupSize, o.splitMask ? " per communicator" : "", o.dtype.c_str(), o.lib.c_str());
       printf("# %12s %12s %12s %12s %14s %6s\n", "bytes", "time_us", "algbw_GB/s", "busbw_GB/s", "host_mean_us", "wrong");
     }
     double dev = 0, host = 0;

@@ -33,6 +33,18 @@ NVCCFLAGS = ARCH + ["-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC", "--
                     "-Xptxas", "-v"]
 
 
+# FLAGCX_SANITIZE=address|thread builds a second copy of libflagcx.so with the host code instrumented
+# (build/san/<kind>/libflagcx.so); the CPU tests then run against it with the sanitizer runtime preloaded.
+SANITIZE = os.environ.get("FLAGCX_SANITIZE", "")
+if SANITIZE:
+    OBJDIR = ROOT / "build" / f"obj_{SANITIZE}"
+    LIBDIR_NATIVE = ROOT / "build" / "san" / SANITIZE
+    CXXFLAGS = CXXFLAGS + [f"-fsanitize={SANITIZE}", "-fno-omit-frame-pointer"]
+    NVCCFLAGS = NVCCFLAGS + ["-Xcompiler", f"-fsanitize={SANITIZE}", "-Xcompiler", "-fno-omit-frame-pointer"]
+else:
+    LIBDIR_NATIVE = LIBDIR
+
+
 def _run(cmd, log=None):
     proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if log is not None:
@@ -79,16 +91,19 @@ def native_sources():
 
 
 def build_native(force=False, verbose=False) -> Path:
-    """Build flagcx_b200/lib/libflagcx.so."""
-    LIBDIR.mkdir(parents=True, exist_ok=True)
+    """Build flagcx_b200/lib/libflagcx.so (or the sanitizer copy when FLAGCX_SANITIZE is set)."""
+    LIBDIR_NATIVE.mkdir(parents=True, exist_ok=True)
+    OBJDIR.mkdir(parents=True, exist_ok=True)
     srcs = native_sources()
     with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
         objs = list(ex.map(lambda s: _compile(s, force=force), srcs))
-    out = LIBDIR / "libflagcx.so"
+    out = LIBDIR_NATIVE / "libflagcx.so"
     newest = max(o.stat().st_mtime for o in objs)
     if force or not out.exists() or out.stat().st_mtime < newest:
+        # the sanitizer runtime is preloaded by the process, so its symbols stay undefined at link time
+        san = ["-Xcompiler", f"-fsanitize={SANITIZE}"] if SANITIZE else ["-Xlinker", "-z", "-Xlinker", "defs"]
         cmd = [NVCC, "-shared", "-o", str(out)] + [str(o) for o in objs] + ARCH + [
-            "-cudart", "static", "-Xlinker", "--no-as-needed", "-lpthread", "-ldl", "-lrt", "-Xlinker", "-z", "-Xlinker", "defs"]
+            "-cudart", "static", "-Xlinker", "--no-as-needed", "-lpthread", "-ldl", "-lrt"] + san
         _run(cmd)
     if verbose:
         print(f"built {out}")
