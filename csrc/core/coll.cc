@@ -139,6 +139,18 @@ static uint64_t heapOffOf(flagcxComm *c, const void *p, size_t bytes) {
   return ~0ull;
 }
 
+// The byte mover a collective stands for when it runs in its LL form.
+static int moveKindOf(flagcxCommOp_t op) {
+  switch (op) {
+    case flagcxCommOpAllGather: return FCX_K_AG;
+    case flagcxCommOpBroadcast: return FCX_K_BCAST;
+    case flagcxCommOpGather: return FCX_K_GATHER;
+    case flagcxCommOpScatter: return FCX_K_SCATTER;
+    case flagcxCommOpAlltoAll: return FCX_K_A2A;
+    default: return 0;
+  }
+}
+
 static flagcxResult_t launchOne(flagcxComm *c, FcxCollArgs &a, const Plan &plan, cudaStream_t st, bool timed) {
   a.kind = plan.kind;
   a.seq = ++c->seq;
@@ -147,7 +159,7 @@ static flagcxResult_t launchOne(flagcxComm *c, FcxCollArgs &a, const Plan &plan,
   cudaError_t e = fcxLaunchColl(&c->dev, &a, nctas, st);
   if (timed) c->tuner->endTiming(st);
   c->counters.launches++;
-  if (plan.kind >= 0 && plan.kind < 16) c->counters.kindLaunches[plan.kind]++;
+  if (plan.kind >= 0 && plan.kind < 24) c->counters.kindLaunches[plan.kind]++;
   return cudaToResult(e, "collective kernel launch");
 }
 
@@ -165,6 +177,7 @@ flagcxResult_t launchCollective(flagcxComm *c, const PendingOp &o) {
   a.scale = o.scale;
   a.sendHeapOff = a.recvHeapOff = ~0ull;
   a.useMc = c->dev.mcHeap != nullptr;
+  a.moveOp = moveKindOf(o.op);
   const bool cast = o.outDt != o.dt || o.scale != 1.0f;
   const char *send = (const char *)o.send;
   char *recv = (char *)o.recv;

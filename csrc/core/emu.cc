@@ -117,6 +117,8 @@ flagcxResult_t flagcxEmuCollective(flagcxEmu_t e, flagcxCommOp_t op, const char 
     a.recv = recv ? recv[r] : nullptr;
     a.count = count;
     a.sendHeapOff = a.recvHeapOff = ~0ull;
+    a.moveOp = op == flagcxCommOpAllGather ? FCX_K_AG : op == flagcxCommOpBroadcast ? FCX_K_BCAST : op == flagcxCommOpGather ? FCX_K_GATHER
+               : op == flagcxCommOpScatter ? FCX_K_SCATTER : op == flagcxCommOpAlltoAll ? FCX_K_A2A : 0;
     switch (op) {
       case flagcxCommOpAllGather: case flagcxCommOpGather: a.recvStride = count; break;
       case flagcxCommOpReduceScatter: case flagcxCommOpScatter: a.sendStride = count; break;

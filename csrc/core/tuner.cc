@@ -11,7 +11,7 @@
 namespace fcx {
 
 static const char *kKindNames[FCX_K_NUM] = {"barrier", "ar_ll", "ar_oneshot", "ar_twoshot", "ar_nvls", "rs", "rs_nvls", "ag",
-                                            "ag_nvls", "bcast", "reduce", "gather", "scatter", "a2a", "a2av"};
+                                            "ag_nvls", "bcast", "reduce", "gather", "scatter", "a2a", "a2av", "move_ll", "rs_ll", "reduce_ll"};
 
 const char *kindName(int kind) { return kind >= 0 && kind < FCX_K_NUM ? kKindNames[kind] : "?"; }
 
@@ -71,6 +71,10 @@ double estimateUs(const Plan &p, flagcxCommOp_t, size_t bytesIn, int, const Tune
     case FCX_K_SCATTER: return pipelinedUs((n - 1) * b, 2 * b, b, 2, false, c, caps);
     case FCX_K_A2A: return pipelinedUs((n - 1) * b, 2 * n * b, b, 2, false, c, caps);
     case FCX_K_A2AV: return kLaunchUs + 2 * kBarrierUs + pushUs((n - 1) * b, c) + localUs(2 * n * b, c);
+    // LL forms (b: per-rank piece, whole vector for reduce): every payload byte travels with a flag byte, no barrier
+    case FCX_K_MOVE_LL:
+    case FCX_K_RS_LL: return kLaunchUs + kLLUs + pushUs(2 * (n - 1) * b, c) + localUs(2 * n * b, c);
+    case FCX_K_REDUCE_LL: return kLaunchUs + kLLUs + pushUs(2 * b, c) + localUs(2 * n * b, c);
     default: return 1e9;
   }
 }
@@ -134,18 +138,30 @@ std::vector<Plan> Tuner::candidates(flagcxCommOp_t op, size_t bytes, flagcxDataT
       if (nvls && bytes >= 4096) addCtas(out, FCX_K_AR_NVLS, {8, 16, 32, 64, 128}, units / n + 1, mx);
       break;
     case flagcxCommOpReduceScatter:
+      if (!cast && bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_RS_LL, {1, 2, 4}, units, mx);
       addCtas(out, FCX_K_RS, {2, 8, 16, 32, 64, 128}, units, mx);
       if (nvls && bytes >= 4096) addCtas(out, FCX_K_RS_NVLS, {8, 16, 32, 64, 128}, units, mx);
       break;
     case flagcxCommOpAllGather:
+      if (bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_MOVE_LL, {1, 2, 4}, units, mx);
       addCtas(out, FCX_K_AG, {2, 8, 16, 32, 64, 128}, units, mx);
       if (caps_.multicast && n > 1 && bytes >= 4096) addCtas(out, FCX_K_AG_NVLS, {8, 16, 32, 64, 128}, units, mx);
       break;
-    case flagcxCommOpReduce: addCtas(out, FCX_K_REDUCE, {2, 8, 16, 32, 64, 128}, units / n + 1, mx); break;
-    case flagcxCommOpBroadcast: addCtas(out, FCX_K_BCAST, {1, 4, 16, 32, 64, 128}, units, mx); break;
-    case flagcxCommOpGather: addCtas(out, FCX_K_GATHER, {1, 4, 16, 64, 128}, units, mx); break;
-    case flagcxCommOpScatter: addCtas(out, FCX_K_SCATTER, {1, 4, 16, 64, 128}, units, mx); break;
-    case flagcxCommOpAlltoAll: addCtas(out, FCX_K_A2A, {2, 8, 16, 32, 64, 128}, units, mx); break;
+    case flagcxCommOpReduce:
+      if (!cast && bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_REDUCE_LL, {1, 2, 4}, units, mx);
+      addCtas(out, FCX_K_REDUCE, {2, 8, 16, 32, 64, 128}, units / n + 1, mx); break;
+    case flagcxCommOpBroadcast:
+      if (bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_MOVE_LL, {1, 2, 4}, units, mx);
+      addCtas(out, FCX_K_BCAST, {1, 4, 16, 32, 64, 128}, units, mx); break;
+    case flagcxCommOpGather:
+      if (bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_MOVE_LL, {1, 2, 4}, units, mx);
+      addCtas(out, FCX_K_GATHER, {1, 4, 16, 64, 128}, units, mx); break;
+    case flagcxCommOpScatter:
+      if (bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_MOVE_LL, {1, 2, 4}, units, mx);
+      addCtas(out, FCX_K_SCATTER, {1, 4, 16, 64, 128}, units, mx); break;
+    case flagcxCommOpAlltoAll:
+      if (bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_MOVE_LL, {1, 2, 4}, units, mx);
+      addCtas(out, FCX_K_A2A, {2, 8, 16, 32, 64, 128}, units, mx); break;
     case flagcxCommOpAlltoAllv: addCtas(out, FCX_K_A2AV, {2, 8, 16, 32, 64, 128}, units, mx); break;
     default: out.push_back({FCX_K_BARRIER, 1}); break;
   }

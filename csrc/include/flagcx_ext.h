@@ -36,7 +36,7 @@ typedef struct {
   uint64_t bytes[flagcxNumCommOps];
   uint64_t launches;      /* kernels launched by the library on behalf of this communicator */
   uint64_t timeouts;      /* device waits that ended by deadline */
-  uint64_t kindLaunches[16];
+  uint64_t kindLaunches[24];
 } flagcxCommCounters;
 flagcxResult_t flagcxCommGetCounters(flagcxComm_t comm, flagcxCommCounters *out);
 

@@ -192,15 +192,20 @@ __device__ __forceinline__ uint4 llLoad(const char *line) {
   return v;
 }
 
+// mode 0: all-reduce (everybody sends its whole vector to everybody and reduces);
+// mode 1: reduce-scatter (piece p goes to rank p, every rank reduces the pieces it received and its own);
+// mode 2: reduce (everybody sends its whole vector to the root, which reduces).
 template <typename T>
-__device__ void arLL(const FcxDevComm &dc, const FcxCollArgs &a, uint64_t seq, int cta, int nctas) {
+__device__ void arLL(const FcxDevComm &dc, const FcxCollArgs &a, uint64_t seq, int cta, int nctas, int mode = 0) {
   using Acc = typename Elem<T>::Acc;
   constexpr int G = 16 / (int)sizeof(T);
   const int n = dc.nranks, me = dc.rank;
   const uint32_t tag = (uint32_t)seq;
   const size_t gtid = (size_t)cta * blockDim.x + threadIdx.x, gstride = (size_t)nctas * blockDim.x;
   const size_t nunits = (a.count + G - 1) / G;
-  const char *send = (const char *)a.send;
+  const size_t pieceBytes = mode == 1 ? a.sendStride * sizeof(T) : 0;  // distance between the pieces of a reduce-scatter
+  const char *send = (const char *)a.send + (size_t)me * pieceBytes;    // what this rank contributes to its own result
+  const bool reduces = mode != 2 || me == a.root;
   const bool alS = aligned16(send), alR = aligned16(a.recv);
   const size_t llOff = FCX_OFF_LL + (size_t)(seq & 1) * FCX_MAX_RANKS * FCX_LL_SLOT_BYTES;
   bool ok = true;
@@ -208,14 +213,23 @@ __device__ void arLL(const FcxDevComm &dc, const FcxCollArgs &a, uint64_t seq, i
     int nv = (int)min((size_t)G, a.count - u * G);
     Acc mine[G];
     loadUnit<T, G>(send + u * 16, alS, nv, mine);
-    uint4 raw;
-    packUnit<T, G>(mine, &raw);
     for (int k = 1; k < n; k++) {
       int p = (me + k) % n;
+      if (mode == 2 && p != a.root) continue;
+      uint4 raw;
+      if (mode == 1) {
+        const char *src = (const char *)a.send + (size_t)p * pieceBytes + u * 16;
+        Acc theirs[G];
+        loadUnit<T, G>(src, aligned16(src), nv, theirs);
+        packUnit<T, G>(theirs, &raw);
+      } else {
+        packUnit<T, G>(mine, &raw);
+      }
       char *line = dc.heap[p] + llOff + (size_t)me * FCX_LL_SLOT_BYTES + u * 32;
       llStore(line, raw.x, raw.y, tag);
       llStore(line + 16, raw.z, raw.w, tag);
     }
+    if (!reduces) continue;
     Acc acc[G];
     bool first = true;
     for (int p = 0; p < n; p++) {
@@ -372,6 +386,14 @@ __device__ void fcxCollBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta,
 
     case FCX_K_AR_LL: {
       if constexpr (ESI == ESO) arLL<TIn>(dc, a, seq, cta, nctas);
+      break;
+    }
+    case FCX_K_RS_LL: {
+      if constexpr (ESI == ESO) arLL<TIn>(dc, a, seq, cta, nctas, 1);
+      break;
+    }
+    case FCX_K_REDUCE_LL: {
+      if constexpr (ESI == ESO) arLL<TIn>(dc, a, seq, cta, nctas, 2);
       break;
     }
 
@@ -638,6 +660,58 @@ __device__ void fcxCollBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta,
   epilogue(dc, seq, nctas);
 }
 
+// ---------------------------------------------------------------- LL byte mover
+//
+// Small fixed-size exchanges without any barrier: every 8 payload bytes travel in one 16-byte line
+// {lo, tag, hi, tag} whose halves are written atomically, so a reader that sees the tag in both halves
+// has the payload.  The tag is the collective's sequence number; the slots are parity double-buffered
+// like the staging area.  One line slot per source rank on every receiver (FCX_LL_SLOT_BYTES each).
+__device__ __forceinline__ void ld8(const char *p, size_t valid, uint32_t *lo, uint32_t *hi) {
+  if (valid >= 8 && ((uintptr_t)p & 7u) == 0) {
+    uint2 v = *(const uint2 *)p;
+    *lo = v.x;
+    *hi = v.y;
+  } else {
+    union { uint2 v; char c[8]; } w;
+    w.v = make_uint2(0, 0);
+    for (size_t i = 0; i < valid && i < 8; i++) w.c[i] = p[i];
+    *lo = w.v.x;
+    *hi = w.v.y;
+  }
+}
+__device__ __forceinline__ void st8(char *p, size_t valid, uint32_t lo, uint32_t hi) {
+  if (valid >= 8 && ((uintptr_t)p & 7u) == 0) {
+    *(uint2 *)p = make_uint2(lo, hi);
+  } else {
+    union { uint2 v; char c[8]; } w;
+    w.v = make_uint2(lo, hi);
+    for (size_t i = 0; i < valid && i < 8; i++) p[i] = w.c[i];
+  }
+}
+// Bounded wait for one line carrying `tag`; false = gave up.
+__device__ __forceinline__ bool llWaitLine(const FcxDevComm &dc, const char *line, uint32_t tag, int peer, int cta, uint64_t seq,
+                                           uint4 *out) {
+  uint4 v = llLoad(line);
+  if (v.y == tag && v.w == tag) { *out = v; return true; }
+  const uint64_t t0 = globalTimerNs();
+  unsigned spins = 0;
+  for (;;) {
+    v = llLoad(line);
+    if (v.y == tag && v.w == tag) { *out = v; return true; }
+    if ((++spins & 63u) == 0u) {
+      if (*(volatile unsigned int *)&localOf(dc)->abortSeen) return false;
+      if (globalTimerNs() - t0 > dc.timeoutNs) {
+        giveUp(dc, FCX_ERR_TIMEOUT, peer, FCX_WAIT_LL, cta, tag, v.y, seq);
+        return false;
+      }
+      if ((spins & 1023u) == 0u && *dc.abortWord) {
+        giveUp(dc, FCX_ERR_ABORT, peer, FCX_WAIT_LL, cta, tag, v.y, seq);
+        return false;
+      }
+    }
+  }
+}
+
 // Byte-moving collectives need no element type.
 __device__ void fcxMoveBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta, int nctas) {
   const int n = dc.nranks, me = dc.rank;
@@ -651,6 +725,7 @@ __device__ void fcxMoveBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta,
   const size_t slot = (bytes + 15) / 16 * 16;
 
   if (a.kind != FCX_K_A2AV) {
+    const int mk = a.kind == FCX_K_MOVE_LL ? a.moveOp : a.kind;  // the LL form moves the same pieces
     // Every fixed-size byte mover is one exchange: piece out[p] goes into a slot of rank p's staging area,
     // piece in[p] arrives in a slot of this rank's staging area and is copied to its place, and the piece a
     // rank keeps for itself is copied locally.  With the multicast alias one store reaches every rank.
@@ -663,16 +738,16 @@ __device__ void fcxMoveBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta,
     char *selfDst = nullptr, *mcDst = nullptr;
     const size_t stageOff = FCX_OFF_STAGE + (size_t)(seq & 1) * dc.stageBytes;
     char *myStage = stagePtr(dc, me, seq);
-    switch (a.kind) {
+    switch (mk) {
       case FCX_K_AG:
       case FCX_K_AG_NVLS:
         for (int p = 0; p < n; p++)
           if (p != me) {
-            if (a.kind == FCX_K_AG) { outSrc[p] = send; outDst[p] = stagePtr(dc, p, seq) + (size_t)me * slot; }
+            if (mk == FCX_K_AG) { outSrc[p] = send; outDst[p] = stagePtr(dc, p, seq) + (size_t)me * slot; }
             inSrc[p] = myStage + (size_t)p * slot;
             inDst[p] = recv + (size_t)p * a.recvStride * es;
           }
-        if (a.kind == FCX_K_AG_NVLS) { mcSrc = send; mcDst = dc.mcHeap + stageOff + (size_t)me * slot; }
+        if (mk == FCX_K_AG_NVLS) { mcSrc = send; mcDst = dc.mcHeap + stageOff + (size_t)me * slot; }
         selfSrc = send;
         selfDst = recv + (size_t)me * a.recvStride * es;
         break;
@@ -721,6 +796,36 @@ __device__ void fcxMoveBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta,
         selfDst = recv + (size_t)me * a.recvStride * es;
         break;
       default: break;
+    }
+    if (a.kind == FCX_K_MOVE_LL) {
+      const uint32_t tag = (uint32_t)seq;
+      const size_t llOff = FCX_OFF_LL + (size_t)(seq & 1) * FCX_MAX_RANKS * FCX_LL_SLOT_BYTES;
+      const size_t nwords = (bytes + 7) / 8;
+      for (size_t w = gtid; w < nwords; w += gstride) {
+        const size_t valid = min((size_t)8, bytes - w * 8);
+        for (int k = 1; k < n; k++) {
+          int p = (me + k) % n;
+          if (!outSrc[p] && !(mcSrc && mk == FCX_K_BCAST)) continue;
+          const char *src = outSrc[p] ? outSrc[p] : mcSrc;  // a multicast broadcast falls back to unicast lines here
+          uint32_t lo, hi;
+          ld8(src + w * 8, valid, &lo, &hi);
+          llStore(dc.heap[p] + llOff + (size_t)me * FCX_LL_SLOT_BYTES + w * 16, lo, hi, tag);
+        }
+      }
+      if (selfSrc && selfSrc != selfDst) copyUnits(selfDst, selfSrc, bytes, 16, gtid, gstride);
+      bool ok = true;
+      for (size_t w = gtid; w < nwords && ok; w += gstride) {
+        const size_t valid = min((size_t)8, bytes - w * 8);
+        for (int k = 1; k < n && ok; k++) {
+          int p = (me + k) % n;
+          if (!inSrc[p]) continue;
+          uint4 v;
+          ok = llWaitLine(dc, dc.heap[me] + llOff + (size_t)p * FCX_LL_SLOT_BYTES + w * 16, tag, p, cta, seq, &v);
+          if (ok) st8(inDst[p] + w * 8, valid, v.x, v.z);
+        }
+      }
+      epilogue(dc, seq, nctas);
+      return;
     }
     const size_t sub = max((size_t)16384, (pipeBytesOf(dc) / (size_t)max(1, n - 1)) & ~(size_t)15);
     const int chunks = (int)max((size_t)1, (bytes + sub - 1) / sub);
@@ -1058,8 +1163,11 @@ cudaError_t launchTypedEmu(const FcxDevComm *dcs, const FcxCollArgs *as, int nra
 
 }  // namespace
 
+// kinds that move bytes without looking at the element type
+static bool isMoveKind(int k) { return k >= FCX_K_AG && k != FCX_K_REDUCE && k != FCX_K_RS_LL && k != FCX_K_REDUCE_LL; }
+
 extern "C" cudaError_t fcxLaunchColl(const FcxDevComm *dc, const FcxCollArgs *a, int nctas, cudaStream_t s) {
-  if (a->kind >= FCX_K_AG && a->kind != FCX_K_REDUCE) {
+  if (isMoveKind(a->kind)) {
     fcxMoveKernel<<<nctas, FCX_THREADS, 0, s>>>(*dc, *a);
     return cudaGetLastError();
   }
@@ -1092,7 +1200,7 @@ extern "C" cudaError_t fcxLaunchWaitTest(const FcxDevComm *dc, uint64_t want, cu
 extern "C" cudaError_t fcxLaunchCollEmu(const FcxDevComm *dcs, const FcxCollArgs *as, const FcxCollArgs *hostArgs0,
                                         int nranks, int nctas, cudaStream_t s) {
   const FcxCollArgs *a = hostArgs0;
-  if (a->kind >= FCX_K_AG && a->kind != FCX_K_REDUCE) {
+  if (isMoveKind(a->kind)) {
     void *params[] = {(void *)&dcs, (void *)&as, (void *)&nctas};
     return cudaLaunchCooperativeKernel((const void *)fcxMoveEmuKernel, dim3(nranks * nctas), dim3(FCX_THREADS), params, 0, s);
   }

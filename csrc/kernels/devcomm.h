@@ -99,6 +99,9 @@ enum FcxKind : int {
   FCX_K_SCATTER,
   FCX_K_A2A,
   FCX_K_A2AV,
+  FCX_K_MOVE_LL,      // small all-gather / broadcast / gather / scatter / all-to-all: flags travel inside the data lines
+  FCX_K_RS_LL,        // small reduce-scatter, same idea
+  FCX_K_REDUCE_LL,    // small reduce to the root, same idea
   FCX_K_NUM
 };
 
@@ -107,6 +110,7 @@ struct FcxCollArgs {
   int dtype, redop, root;
   int elemSize;          // bytes per element (the byte-moving kinds only look at this)
   int useMc;             // broadcast: root stores through the multicast alias
+  int moveOp;            // FCX_K_MOVE_LL: which byte mover it stands for (FCX_K_AG, _BCAST, _GATHER, _SCATTER, _A2A)
   int outDtype;          // all-reduce with fused cast: element type of recv (== dtype when unused)
   float scale;           // multiplied into the result before the final rounding (1 = off)
   uint64_t seq;          // unused by the kernels (they count in device memory); kept for logs

@@ -208,7 +208,7 @@ static py::dict commCounters(uint64_t comm) {
   d["launches"] = cc.launches;
   py::list calls, kinds;
   for (int i = 0; i < flagcxNumCommOps; i++) calls.append(cc.calls[i]);
-  for (int i = 0; i < 16; i++) kinds.append(cc.kindLaunches[i]);
+  for (int i = 0; i < 24; i++) kinds.append(cc.kindLaunches[i]);
   d["calls"] = calls;
   d["kind_launches"] = kinds;
   return d;

@@ -83,7 +83,7 @@ flagcxHandlerGroup_t = ctypes.POINTER(flagcxHandlerGroup)
 
 class flagcxCommCounters(ctypes.Structure):
     _fields_ = [("calls", ctypes.c_uint64 * 12), ("bytes", ctypes.c_uint64 * 12), ("launches", ctypes.c_uint64),
-                ("timeouts", ctypes.c_uint64), ("kindLaunches", ctypes.c_uint64 * 16)]
+                ("timeouts", ctypes.c_uint64), ("kindLaunches", ctypes.c_uint64 * 24)]
 
 
 class flagcxDataTypeEnum:

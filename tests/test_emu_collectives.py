@@ -193,6 +193,49 @@ def test_reducescatter_allgather(lib, n, count):
 
 
 @pytest.mark.parametrize("n", [2, 3, 8])
+@pytest.mark.parametrize("nctas", [1, 3])
+def test_ll_forms_of_small_collectives(lib, n, nctas):
+    """The barrier-free forms used for small messages: flags travel inside the data lines."""
+    emu = Emu(lib, n)
+    try:
+        for dtype, count in ((torch.float32, 1), (torch.float32, 1000), (torch.bfloat16, 4093), (torch.int8, 13), (torch.uint8, 8190)):
+            xs = _rand(n, count * n, dtype, seed=21)
+            pieces = [x[:count].clone() for x in xs]
+            gs = [torch.zeros(count * n, dtype=dtype, device="cuda") for _ in range(n)]
+            emu.coll("allgather", "move_ll", nctas, pieces, gs, count, dtype)
+            for g in gs:
+                assert torch.equal(g, torch.cat(pieces))
+            outs = [torch.zeros(count * n, dtype=dtype, device="cuda") for _ in range(n)]
+            emu.coll("a2a", "move_ll", nctas, xs, outs, count, dtype)
+            for r in range(n):
+                assert torch.equal(outs[r], torch.cat([xs[p][r * count:(r + 1) * count] for p in range(n)]))
+            for root in (0, n - 1):
+                bs = [torch.zeros(count, dtype=dtype, device="cuda") for _ in range(n)]
+                emu.coll("bcast", "move_ll", nctas, pieces, bs, count, dtype, root=root)
+                for b in bs:
+                    assert torch.equal(b, pieces[root])
+                gg = [torch.zeros(count * n, dtype=dtype, device="cuda") for _ in range(n)]
+                emu.coll("gather", "move_ll", nctas, pieces, gg, count, dtype, root=root)
+                assert torch.equal(gg[root], torch.cat(pieces))
+                ss = [torch.zeros(count, dtype=dtype, device="cuda") for _ in range(n)]
+                emu.coll("scatter", "move_ll", nctas, xs, ss, count, dtype, root=root)
+                for r in range(n):
+                    assert torch.equal(ss[r], xs[root][r * count:(r + 1) * count])
+            if dtype in (torch.float32, torch.bfloat16):
+                ref = _reduce_ref(xs, 0)
+                ys = [torch.zeros(count, dtype=dtype, device="cuda") for _ in range(n)]
+                emu.coll("reducescatter", "rs_ll", nctas, xs, ys, count, dtype)
+                for r, y in enumerate(ys):
+                    torch.testing.assert_close(y.float(), ref[r * count:(r + 1) * count], atol=_tol(dtype) * n, rtol=_tol(dtype))
+                root = n // 2
+                rd = [torch.zeros(count, dtype=dtype, device="cuda") for _ in range(n)]
+                emu.coll("reduce", "reduce_ll", nctas, pieces, rd, count, dtype, root=root)
+                torch.testing.assert_close(rd[root].float(), _reduce_ref(pieces, 0), atol=_tol(dtype) * n, rtol=_tol(dtype))
+    finally:
+        emu.close()
+
+
+@pytest.mark.parametrize("n", [2, 3, 8])
 def test_pipelined_sub_chunks(lib, n, monkeypatch):
     """With a tiny sub-chunk size every large-message kind runs many pipeline iterations (push of chunk i
     overlapping the reduction / copy-out of chunks i-1 and i-2), in place and out of place."""
