@@ -205,11 +205,9 @@ flagcxResult_t flagcxHandleFree(flagcxHandlerGroup_t handler);
  * flagcxCommRegister makes an arbitrary device buffer peer-visible; all
  * ranks must register their buffers in the same order (the call exchanges
  * export handles over the bootstrap network). */
-flagcxResult_t flagcxMemAlloc(void **ptr, size_t size,
-                              flagcxComm_t comm FLAGCX_DEFAULT(NULL));
+flagcxResult_t flagcxMemAlloc(void **ptr, size_t size, flagcxComm_t comm FLAGCX_DEFAULT(NULL));
 flagcxResult_t flagcxMemFree(void *ptr, flagcxComm_t comm FLAGCX_DEFAULT(NULL));
-flagcxResult_t flagcxCommRegister(const flagcxComm_t comm, void *buff,
-                                  size_t size, void **handle);
+flagcxResult_t flagcxCommRegister(const flagcxComm_t comm, void *buff, size_t size, void **handle);
 flagcxResult_t flagcxCommDeregister(const flagcxComm_t comm, void *handle);
 
 /* ---- communicator life cycle ------------------------------------------ */
@@ -218,8 +216,7 @@ flagcxResult_t flagcxGetVersion(int *version);
 /* Rank 0 calls this once and ships the 256 bytes to the other ranks by any
  * out-of-band means.  *uniqueId may be NULL, in which case it is allocated. */
 flagcxResult_t flagcxGetUniqueId(flagcxUniqueId_t *uniqueId);
-flagcxResult_t flagcxCommInitRank(flagcxComm_t *comm, int nranks,
-                                  flagcxUniqueId_t commId, int rank);
+flagcxResult_t flagcxCommInitRank(flagcxComm_t *comm, int nranks, flagcxUniqueId_t commId, int rank);
 flagcxResult_t flagcxCommFinalize(flagcxComm_t comm);
 flagcxResult_t flagcxCommDestroy(flagcxComm_t comm);
 flagcxResult_t flagcxCommAbort(flagcxComm_t comm);
@@ -227,8 +224,7 @@ flagcxResult_t flagcxCommResume(flagcxComm_t comm);
 flagcxResult_t flagcxCommSuspend(flagcxComm_t comm);
 const char *flagcxGetErrorString(flagcxResult_t result);
 const char *flagcxGetLastError(flagcxComm_t comm);
-flagcxResult_t flagcxCommGetAsyncError(flagcxComm_t comm,
-                                       flagcxResult_t *asyncError);
+flagcxResult_t flagcxCommGetAsyncError(flagcxComm_t comm, flagcxResult_t *asyncError);
 flagcxResult_t flagcxCommCount(const flagcxComm_t comm, int *count);
 flagcxResult_t flagcxCommGetDeviceNumber(const flagcxComm_t comm, int *device);
 flagcxResult_t flagcxCommUserRank(const flagcxComm_t comm, int *rank);
@@ -242,45 +238,28 @@ flagcxResult_t flagcxCommFifoBuffer(const flagcxComm_t comm, void **buffer);
  * sendbuff == recvbuff; all-gather with sendbuff == recvbuff + rank*count;
  * reduce-scatter with recvbuff == sendbuff + rank*recvcount. */
 flagcxResult_t flagcxBarrier(flagcxComm_t comm, flagcxStream_t stream);
-flagcxResult_t flagcxReduce(const void *sendbuff, void *recvbuff, size_t count,
-                            flagcxDataType_t datatype, flagcxRedOp_t op,
-                            int root, flagcxComm_t comm, flagcxStream_t stream);
-flagcxResult_t flagcxGather(const void *sendbuff, void *recvbuff, size_t count,
-                            flagcxDataType_t datatype, int root,
+flagcxResult_t flagcxReduce(const void *sendbuff, void *recvbuff, size_t count, flagcxDataType_t datatype, flagcxRedOp_t op, int root,
                             flagcxComm_t comm, flagcxStream_t stream);
-flagcxResult_t flagcxScatter(const void *sendbuff, void *recvbuff, size_t count,
-                             flagcxDataType_t datatype, int root,
-                             flagcxComm_t comm, flagcxStream_t stream);
-flagcxResult_t flagcxBroadcast(const void *sendbuff, void *recvbuff,
-                               size_t count, flagcxDataType_t datatype,
-                               int root, flagcxComm_t comm,
+flagcxResult_t flagcxGather(const void *sendbuff, void *recvbuff, size_t count, flagcxDataType_t datatype, int root, flagcxComm_t comm,
+                            flagcxStream_t stream);
+flagcxResult_t flagcxScatter(const void *sendbuff, void *recvbuff, size_t count, flagcxDataType_t datatype, int root, flagcxComm_t comm,
+                             flagcxStream_t stream);
+flagcxResult_t flagcxBroadcast(const void *sendbuff, void *recvbuff, size_t count, flagcxDataType_t datatype, int root, flagcxComm_t comm,
                                flagcxStream_t stream);
-flagcxResult_t flagcxAllReduce(const void *sendbuff, void *recvbuff,
-                               size_t count, flagcxDataType_t datatype,
-                               flagcxRedOp_t op, flagcxComm_t comm,
-                               flagcxStream_t stream);
-flagcxResult_t flagcxReduceScatter(const void *sendbuff, void *recvbuff,
-                                   size_t recvcount, flagcxDataType_t datatype,
-                                   flagcxRedOp_t op, flagcxComm_t comm,
-                                   flagcxStream_t stream);
-flagcxResult_t flagcxAllGather(const void *sendbuff, void *recvbuff,
-                               size_t sendcount, flagcxDataType_t datatype,
+flagcxResult_t flagcxAllReduce(const void *sendbuff, void *recvbuff, size_t count, flagcxDataType_t datatype, flagcxRedOp_t op,
                                flagcxComm_t comm, flagcxStream_t stream);
-flagcxResult_t flagcxAlltoAll(const void *sendbuff, void *recvbuff,
-                              size_t count, flagcxDataType_t datatype,
-                              flagcxComm_t comm, flagcxStream_t stream);
-/* counts and displacements are host arrays of nranks elements, in elements */
-flagcxResult_t flagcxAlltoAllv(const void *sendbuff, size_t *sendcounts,
-                               size_t *sdispls, void *recvbuff,
-                               size_t *recvcounts, size_t *rdispls,
-                               flagcxDataType_t datatype, flagcxComm_t comm,
+flagcxResult_t flagcxReduceScatter(const void *sendbuff, void *recvbuff, size_t recvcount, flagcxDataType_t datatype, flagcxRedOp_t op,
+                                   flagcxComm_t comm, flagcxStream_t stream);
+flagcxResult_t flagcxAllGather(const void *sendbuff, void *recvbuff, size_t sendcount, flagcxDataType_t datatype, flagcxComm_t comm,
                                flagcxStream_t stream);
-flagcxResult_t flagcxSend(const void *sendbuff, size_t count,
-                          flagcxDataType_t datatype, int peer,
-                          flagcxComm_t comm, flagcxStream_t stream);
-flagcxResult_t flagcxRecv(void *recvbuff, size_t count,
-                          flagcxDataType_t datatype, int peer,
-                          flagcxComm_t comm, flagcxStream_t stream);
+flagcxResult_t flagcxAlltoAll(const void *sendbuff, void *recvbuff, size_t count, flagcxDataType_t datatype, flagcxComm_t comm,
+                              flagcxStream_t stream);
+/* counts and displacements are host arrays of nranks elements, in elements */
+flagcxResult_t flagcxAlltoAllv(const void *sendbuff, size_t *sendcounts, size_t *sdispls, void *recvbuff, size_t *recvcounts,
+                               size_t *rdispls, flagcxDataType_t datatype, flagcxComm_t comm, flagcxStream_t stream);
+flagcxResult_t flagcxSend(const void *sendbuff, size_t count, flagcxDataType_t datatype, int peer, flagcxComm_t comm,
+                          flagcxStream_t stream);
+flagcxResult_t flagcxRecv(void *recvbuff, size_t count, flagcxDataType_t datatype, int peer, flagcxComm_t comm, flagcxStream_t stream);
 /* Calls between GroupStart and GroupEnd are collected and issued as one
  * fused launch at the outermost GroupEnd. */
 flagcxResult_t flagcxGroupStart(flagcxComm_t comm);
