@@ -142,7 +142,7 @@ def main():
         from flagcx_b200.wrapper import FLAGCXLibrary
         lib = FLAGCXLibrary()
         comm = lib.flagcxCommInitRank(1, lib.flagcxGetUniqueId(), 0)
-        T, H, F, K = 16384, 4096, 2048, 2
+        T, H, F, K = 8192, 4096, 2048, 2
         ep = ExpertParallelContext(comm.value, 1, 0, T, H, F, K)
         x = torch.randn(T, H, device="cuda").bfloat16()
         idx = torch.zeros(T, K, dtype=torch.int32, device="cuda")
