@@ -66,6 +66,10 @@ flagcxResult_t flagcxTunerPin(flagcxComm_t comm, const char *kind, int nctas);
 flagcxResult_t flagcxTunerQuery(flagcxComm_t comm, flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red,
                                 char *kindOut, size_t kindOutBytes, int *nctas, double *estimateUs);
 
+/* The plan the cost-model prior picks for a machine of `nranks` GPUs; needs neither a communicator nor a GPU. */
+flagcxResult_t flagcxTunerPriorPlan(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, int nranks, int multicast, char *kindOut,
+                                    size_t kindOutBytes, int *nctas, double *estimateUs);
+
 /* Failure handling.  Device waits are bounded by this many milliseconds
  * (default FLAGCX_KERNEL_TIMEOUT_MS or 30000). */
 flagcxResult_t flagcxCommSetTimeoutMs(flagcxComm_t comm, int ms);

@@ -213,6 +213,8 @@ _SIGNATURES = {
     "flagcxTunerSave": (_R, [flagcxComm_t, ctypes.c_char_p]),
     "flagcxTunerLoad": (_R, [flagcxComm_t, ctypes.c_char_p]),
     "flagcxTunerPin": (_R, [flagcxComm_t, ctypes.c_char_p, ctypes.c_int]),
+    "flagcxTunerPriorPlan": (_R, [ctypes.c_int, _sz, flagcxDataType_t, ctypes.c_int, ctypes.c_int, ctypes.c_char_p, _sz,
+                                  ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_double)]),
     "flagcxTunerQuery": (_R, [flagcxComm_t, ctypes.c_int, _sz, flagcxDataType_t, flagcxRedOp_t, ctypes.c_char_p, _sz,
                               ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_double)]),
     "flagcxEmuCreate": (_R, [ctypes.POINTER(_vp), ctypes.c_int, _sz]),
@@ -430,6 +432,13 @@ class FLAGCXLibrary:
         buf = ctypes.create_string_buffer(64)
         nctas, us = ctypes.c_int(), ctypes.c_double()
         self.call("flagcxTunerQuery", comm, op, nbytes, dtype, red, buf, 64, ctypes.byref(nctas), ctypes.byref(us))
+        return buf.value.decode(), nctas.value, us.value
+
+    def tuner_prior_plan(self, op: int, nbytes: int, dtype: int, nranks: int, multicast: bool = True):
+        """(kind, CTAs, estimated microseconds) the cost model picks for `nranks` GPUs; works without a GPU."""
+        buf = ctypes.create_string_buffer(64)
+        nctas, us = ctypes.c_int(), ctypes.c_double()
+        self.call("flagcxTunerPriorPlan", op, nbytes, dtype, nranks, int(multicast), buf, 64, ctypes.byref(nctas), ctypes.byref(us))
         return buf.value.decode(), nctas.value, us.value
 
     def tuner_pin(self, comm, kind: Optional[str], nctas: int = 16):

@@ -1,0 +1,41 @@
+"""The tuner's cost-model prior, queried without a GPU: small messages take the barrier-free LL forms, nothing is ever
+planned beyond what a kind can hold, large messages get the whole grid, and estimates grow with the message."""
+import pytest
+
+from flagcx_b200.wrapper import FLAGCXLibrary
+
+OPS = {"bcast": 2, "gather": 3, "scatter": 4, "reduce": 5, "allreduce": 6, "allgather": 7, "reducescatter": 8, "a2a": 9}
+LL_KINDS = {"ar_ll", "move_ll", "rs_ll", "reduce_ll"}
+FP32 = 7
+
+
+@pytest.fixture(scope="module")
+def lib(native_lib):
+    return FLAGCXLibrary(native_lib)
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+@pytest.mark.parametrize("mc", [False, True])
+def test_prior_plans_are_sane(lib, n, mc):
+    for name, op in OPS.items():
+        last = 0.0
+        for nbytes in (8, 64, 1024, 32768, 32772, 1 << 20, 16 << 20, 256 << 20, 1 << 30):
+            kind, ctas, us = lib.tuner_prior_plan(op, nbytes, FP32, n, mc)
+            assert 1 <= ctas <= 128, (name, nbytes, kind, ctas)
+            assert us > 0
+            if nbytes <= 64:
+                assert kind in LL_KINDS, (name, nbytes, kind)
+            if nbytes > 32768:
+                assert kind not in LL_KINDS, (name, nbytes, kind)  # an LL slot holds 32 KiB of payload
+            if not mc:
+                assert "nvls" not in kind
+            if nbytes >= (256 << 20):
+                assert ctas >= 64, (name, nbytes, kind, ctas)
+            assert us >= last * 0.9, (name, nbytes, us, last)  # a change of kind may dip a little
+            last = us
+
+
+def test_prior_rejects_bad_world():
+    lib = FLAGCXLibrary()
+    with pytest.raises(Exception):
+        lib.tuner_prior_plan(6, 1024, FP32, 9, True)
