@@ -264,6 +264,7 @@ struct MsgHeader {
 
 // Root service: collect one check-in per rank, then send the full table.
 void rootThread(int listenFd, uint64_t magic) {
+  nameThisThread("flagcx-root");
   int64_t dl = nowMs() + envInt("BOOTSTRAP_TIMEOUT_MS", 600000);
   std::vector<int> fds;
   std::vector<SockAddr> table;

@@ -79,6 +79,10 @@ flagcxResult_t commCreate(flagcxComm **out, int nranks, const BootstrapHandle &h
   bool haveGpu = cudaGetDeviceCount(&ndev) == cudaSuccess && ndev > 0;
   cudaGetLastError();
   bool forceHost = envInt("USE_HOST_COMM", 0) != 0;
+  // Variables of the reference that select between its own transports and the vendor library have nothing to
+  // select here (every path is this library's own): they are accepted and reported, never an error.
+  for (const char *name : {"USE_HETERO_COMM", "RUNTIME_PROXY", "FORCE_NET_SOCKET", "USENET", "DMABUF_ENABLE", "C2C_SEARCH_GRANULARITY"})
+    if (!envStr(name, "").empty()) FCX_INFO(SUB_ENV, "FLAGCX_%s=%s accepted; it changes nothing inside one NVSwitch domain", name, envStr(name, "").c_str());
   if (flags & FLAGCX_INIT_HOST_ONLY) haveGpu = false;  // buffers of this communicator are host memory
   c->hostOnly = !haveGpu;
   c->hostFallback = haveGpu && forceHost;
@@ -168,7 +172,14 @@ flagcxResult_t commCreate(flagcxComm **out, int nranks, const BootstrapHandle &h
   caps.pipeBytes = c->dev.pipeBytes;
   caps.maxCtas = (int)std::min<int64_t>(envInt("MAX_CTAS", 128), FCX_MAX_CTAS);
   c->tuner.reset(new Tuner(&c->bs, caps));
-  *out = c.release();
+  flagcxComm *raw = c.release();
+  *out = raw;
+  // FLAGCX_KERNEL_PROXY=1 (reference: flagcx/core/proxy.cc:1074-1182): start the thread that serves the
+  // device->host request queue with the communicator instead of at the first flagcxCommFifoBuffer call.
+  if (envInt("KERNEL_PROXY", 0) != 0 && !raw->hostOnly && raw->heap.bytes) {
+    void *queue = nullptr;
+    flagcxCommFifoBuffer(raw, &queue);
+  }
   return flagcxSuccess;
 }
 
@@ -200,6 +211,7 @@ flagcxResult_t commFree(flagcxComm *c) {
     if (c->segsDev) cudaFree(c->segsDev);
     cudaGetLastError();
   }
+  FCX_INFO(SUB_INIT, "communicator %p (rank %d of %d) destroyed", (void *)c, c->rank, c->nranks);
   c->bs.close();
   c->destroyed = true;
   delete c;

@@ -27,6 +27,7 @@ class FifoService {
 };
 
 static void serve(flagcxComm *c, FifoService *f) {
+  nameThisThread("flagcx-fifo");
   cudaSetDevice(f->cudaDev);
   volatile uint64_t *buf = f->host;
   flagcxStream fs{f->stream};

@@ -4,6 +4,8 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <pthread.h>
+#include <cstdlib>
 #include <string>
 #include <sys/syscall.h>
 #include <sys/time.h>
@@ -144,6 +146,13 @@ void logMsg(LogLevel lvl, uint32_t subsys, const char *file, int line, const cha
   va_end(ap);
   if (lvl == LOG_WARN) {
     snprintf(tLastError, sizeof tLastError, "%s", body);
+    // FLAGCX_WARN_ENABLE_DEBUG_INFO=1: after the first warning, log INFO of every subsystem
+    // (reference: flagcx/service/debug.cc:157)
+    static const bool escalate = getEnv("FLAGCX_WARN_ENABLE_DEBUG_INFO") && atoi(getEnv("FLAGCX_WARN_ENABLE_DEBUG_INFO")) != 0;
+    if (escalate && gLevel < LOG_INFO) {
+      gLevel = LOG_INFO;
+      gMask = ~0u;
+    }
   }
   if (gLevel < lvl) return;
   if (lvl != LOG_WARN && !(subsys & gMask)) return;
@@ -162,6 +171,13 @@ void logMsg(LogLevel lvl, uint32_t subsys, const char *file, int line, const cha
     fprintf(gOut, "%s:%d:%ld [%d] FLAGCX INFO %s\n", gHost, getpid(), tid, gDev, body);
   }
   fflush(gOut);
+}
+
+// FLAGCX_SET_THREAD_NAME=1: helper threads carry a name ("flagcx-root", "flagcx-fifo") visible in ps/top/gdb
+// (reference: flagcx/service/debug.cc:231).
+void nameThisThread(const char *name) {
+  static const bool on = getEnv("FLAGCX_SET_THREAD_NAME") && atoi(getEnv("FLAGCX_SET_THREAD_NAME")) != 0;
+  if (on) pthread_setname_np(pthread_self(), name);
 }
 
 }  // namespace fcx

@@ -37,6 +37,7 @@ const char *getEnv(const char *name);
 int64_t envInt(const char *name, int64_t dflt);          // "FLAGCX_" prefix is added
 std::string envStr(const char *name, const char *dflt);  // "FLAGCX_" prefix is added
 void setLogRank(int rank, int dev);
+void nameThisThread(const char *name);  // honours FLAGCX_SET_THREAD_NAME
 
 }  // namespace fcx
 

@@ -33,6 +33,25 @@ static const char *pathType(const TopoRank &a, int self, int other) {
 
 flagcxResult_t topoProbeAndDump(flagcxComm *c) {
   std::string dump = envStr("TOPO_DUMP_FILE", "");
+  std::string given = envStr("TOPO_FILE", "");
+  if (!given.empty()) {
+    // A topology supplied by the user replaces the probe (reference: FLAGCX_TOPO_FILE).  Inside one NVSwitch
+    // domain nothing is derived from it; it is checked against the communicator and reported.
+    if (c->rank == 0) {
+      FILE *f = fopen(given.c_str(), "r");
+      if (!f) { FCX_WARN("cannot read topology file %s", given.c_str()); return flagcxSystemError; }
+      char line[512];
+      int ranks = -1;
+      while (fgets(line, sizeof line, f)) {
+        const char *at = strstr(line, "ranks=\"");
+        if (strstr(line, "<system") && at) { ranks = atoi(at + 7); break; }
+      }
+      fclose(f);
+      if (ranks != c->nranks) FCX_WARN("topology file %s describes %d ranks, the communicator has %d", given.c_str(), ranks, c->nranks);
+      else FCX_INFO(SUB_GRAPH, "topology taken from %s (%d ranks)", given.c_str(), ranks);
+    }
+    return flagcxSuccess;
+  }
   bool detect = envStr("ENABLE_TOPO_DETECT", "") == "TRUE" || !dump.empty();
   if (!detect || c->hostOnly) return flagcxSuccess;
   const int n = c->nranks;
