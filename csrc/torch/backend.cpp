@@ -204,6 +204,7 @@ class FlagcxBackend : public c10d::Backend {
   c10::intrusive_ptr<c10d::Work> run(c10d::OpType type, const at::Device &dev, std::vector<at::Tensor> touched,
                                      std::vector<at::Tensor> outputs, F &&fn) {
     flagcxComm_t c = comm(dev);
+    seq_++;
     auto work = c10::make_intrusive<FlagcxWork>(type, getRank(), c, dev.is_cuda(), dev.is_cuda() ? dev.index() : 0, timeout_);
     work->setOutputs(std::move(outputs));
     if (!dev.is_cuda()) {
@@ -553,6 +554,77 @@ class FlagcxBackend : public c10d::Backend {
   }
   uint64_t ensureComm(const at::Device &dev) { return (uint64_t)(uintptr_t)comm(dev); }
 
+  // ---- group health and bookkeeping (the reference plugin has none of these)
+
+  // Collectives issued so far on this group; equal on every rank of a healthy group.
+  void setSequenceNumberForGroup() override {}
+  uint64_t getSequenceNumberForGroup() override { return seq_; }
+
+  // A barrier over the store that names the ranks which did not arrive before the time-out.
+  void monitoredBarrier(const c10d::BarrierOptions &opts, bool waitAllRanks = false) override {
+    const auto limit = opts.timeout.count() > 0 ? opts.timeout : (timeout_.count() > 0 ? timeout_ : std::chrono::milliseconds(300000));
+    const std::string base = "flagcx/monitored_barrier/" + std::to_string(monitored_++) + "/";
+    store_->set(base + std::to_string(getRank()), std::vector<uint8_t>{1});
+    if (getRank() != 0) {
+      // rank 0 publishes the verdict; everybody else waits for it
+      try {
+        store_->wait({base + "done"}, limit + std::chrono::milliseconds(1000));
+      } catch (const std::exception &) {
+        TORCH_CHECK(false, "flagcx: monitoredBarrier: rank ", getRank(), " did not hear from rank 0 within ", limit.count(), " ms");
+      }
+      auto v = store_->get(base + "done");
+      TORCH_CHECK(!v.empty() && v[0] == 1, "flagcx: monitoredBarrier failed: some ranks did not arrive (see rank 0)");
+      return;
+    }
+    std::vector<int> missing;
+    const auto t0 = std::chrono::steady_clock::now();
+    for (int r = 1; r < getSize(); r++) {
+      auto left = limit - std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0);
+      if (left.count() < 1) left = std::chrono::milliseconds(1);
+      try {
+        store_->wait({base + std::to_string(r)}, left);
+      } catch (const std::exception &) {
+        missing.push_back(r);
+        if (!waitAllRanks) break;
+      }
+    }
+    store_->set(base + "done", std::vector<uint8_t>{(uint8_t)(missing.empty() ? 1 : 0)});
+    if (!missing.empty()) {
+      std::string who;
+      for (int r : missing) who += (who.empty() ? "" : ", ") + std::to_string(r);
+      TORCH_CHECK(false, "flagcx: monitoredBarrier: rank(s) ", who, " did not arrive within ", limit.count(), " ms");
+    }
+  }
+
+  // Block the host until everything this backend enqueued has run.
+  void waitForPendingWorks() override {
+    if (stream_) stream_->synchronize();
+  }
+
+  // What the library's bounded device waits and the host path have recorded.
+  c10d::ErrorType getError() override {
+    for (auto &kv : comms_) {
+      if (!kv.second) continue;
+      flagcxResult_t async = flagcxSuccess;
+      flagcxCommGetAsyncError(kv.second, &async);
+      if (async == flagcxRemoteError) return c10d::ErrorType::REMOTE_ERROR;
+      if (async != flagcxSuccess && async != flagcxInProgress) return c10d::ErrorType::COMM_ERROR;
+    }
+    return c10d::ErrorType::SUCCESS;
+  }
+
+  // Tensors in the communicator's symmetric heap: collectives on them need no staging copy on the NVLS path and
+  // the fused kernels can address them on every peer.
+  bool supportsTensorAlloc(c10::DeviceIndex) override { return true; }
+  at::Tensor allocateTensor(long size, at::TensorOptions options = {}) override {
+    TORCH_CHECK(options.device().is_cuda(), "flagcx: allocateTensor needs a CUDA device in its options");
+    flagcxComm_t c = comm(options.device());
+    const size_t bytes = std::max<size_t>((size_t)size * c10::elementSize(c10::typeMetaToScalarType(options.dtype())), 16);
+    void *p = nullptr;
+    FCX_TORCH_CHECK(flagcxMemAlloc(&p, bytes, c));
+    return at::from_blob(p, {size}, [c](void *q) { flagcxMemFree(q, c); }, options);
+  }
+
   void abort() override {
     for (auto &kv : comms_)
       if (kv.second) { flagcxCommAbort(kv.second); kv.second = nullptr; }
@@ -576,6 +648,7 @@ class FlagcxBackend : public c10d::Backend {
   std::chrono::milliseconds timeout_;
   std::map<std::string, flagcxComm_t> comms_;
   int commCounter_ = 0;
+  uint64_t seq_ = 0, monitored_ = 0;
   std::unique_ptr<c10::cuda::CUDAStream> stream_;
   flagcxStreamLayout wrapped_{};
   bool coalescing_ = false, syncedInGroup_ = false;

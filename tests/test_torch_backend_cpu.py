@@ -80,6 +80,25 @@ def _worker(rank, world, port, q):
         w.wait()
         out["async"] = w.is_completed()
         dist.barrier()
+        # group health: everybody arrives at a monitored barrier; then the last rank stays away from a second one
+        # and rank 0 names it
+        import datetime
+        pg = dist.distributed_c10d._get_default_group()
+        backend = pg._get_backend(torch.device("cpu"))
+        # (torch.distributed.monitored_barrier itself only admits gloo; the backend method is reachable directly)
+        backend.monitored_barrier(datetime.timedelta(seconds=20), False)
+        out["monitored_ok"] = True
+        if rank == world - 1:
+            out["monitored_names_missing"] = True
+        else:
+            try:
+                backend.monitored_barrier(datetime.timedelta(milliseconds=600), False)
+                out["monitored_names_missing"] = False
+            except RuntimeError as e:
+                out["monitored_names_missing"] = (f"rank(s) {world - 1}" in str(e)) if rank == 0 else ("did not" in str(e))
+        seqs = [None] * world
+        dist.all_gather_object(seqs, int(backend._get_sequence_number_for_group()))
+        out["sequence_numbers_agree"] = len(set(seqs)) == 1 and seqs[0] > 10
         obj = [None] * world
         dist.all_gather_object(obj, {"rank": rank})
         out["object"] = [o["rank"] for o in obj] == list(range(world))
