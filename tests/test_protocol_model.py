@@ -99,3 +99,62 @@ def _explore(n, L, NL, chunks, depth):
 def test_flag_protocol_has_no_early_read_and_no_deadlock(n, L, NL, chunks, depth):
     states, terminal = _explore(n, L, NL, chunks, depth)
     assert states > 10 and terminal >= 1
+
+
+def _explore_unified(n, chunks, depth):
+    """The NVLS kinds keep one role per CTA and the unit-ownership rule: CTA x of every rank runs
+    A(i); wait(peers finished iteration i-1); B(i-1); [C(i-2)]; post(i+1).  One CTA index suffices for the model."""
+    iters = chunks + depth - 1
+    progs = {}
+    for r in range(n):
+        steps = []
+        for i in range(iters):
+            if i < chunks:
+                steps.append(("A", i))
+            if i >= 1:
+                steps.append(("wait", i))
+                if i - 1 < chunks:
+                    steps.append(("B", i - 1))
+            if depth == 3 and i >= 2 and i - 2 < chunks:
+                steps.append(("C", i - 2))
+            if i + 1 < iters:
+                steps.append(("post", i + 1))
+        progs[r] = steps
+    start = (tuple(0 for _ in range(n)), tuple(0 for _ in range(n)), frozenset(), frozenset())
+    seen, stack, terminal = {start}, [start], 0
+    while stack:
+        pcs, posted, doneA, doneB = stack.pop()
+        moved = False
+        for r in range(n):
+            if pcs[r] >= len(progs[r]):
+                continue
+            op, arg = progs[r][pcs[r]]
+            np_, nA, nB = posted, doneA, doneB
+            if op == "A":
+                nA = doneA | {(r, arg)}
+            elif op == "post":
+                assert posted[r] < arg
+                np_ = posted[:r] + (arg,) + posted[r + 1:]
+            elif op == "wait":
+                if not all(posted[p] >= arg for p in range(n) if p != r):
+                    continue
+            elif op == "B":
+                assert all((p, arg) in doneA for p in range(n)), f"rank {r} reduced sub-chunk {arg} before every rank staged it"
+                nB = doneB | {(r, arg)}
+            elif op == "C":
+                assert all((p, arg) in doneB for p in range(n)), f"rank {r} copied out sub-chunk {arg} before every rank finished it"
+            moved = True
+            st = (pcs[:r] + (pcs[r] + 1,) + pcs[r + 1:], np_, nA, nB)
+            if st not in seen:
+                seen.add(st)
+                stack.append(st)
+        if not moved:
+            assert all(pcs[r] >= len(progs[r]) for r in range(n)), f"deadlock at {pcs}"
+            terminal += 1
+    return len(seen), terminal
+
+
+@pytest.mark.parametrize("n,chunks,depth", [(2, 1, 2), (2, 4, 2), (3, 3, 2), (2, 1, 3), (2, 4, 3), (3, 3, 3)])
+def test_split_phase_pipeline_of_the_switch_kinds(n, chunks, depth):
+    states, terminal = _explore_unified(n, chunks, depth)
+    assert states > 3 and terminal >= 1
