@@ -8,6 +8,11 @@ PyTorch GPT-2-medium.  Nothing of this framework is imported here.
 The model is the textbook module (nn.LayerNorm, nn.Linear, tanh-GELU,
 scaled_dot_product_attention, F.cross_entropy), bf16 parameters, fp32 master
 weights updated by torch.optim.AdamW(fused=True).
+
+``build_stock_ddp`` is the same model and loop on whatever process group is
+already initialised; ``bench.py --impl ours-c10d`` uses it over this
+framework's c10d backend, which isolates the communication library from the
+model-side kernel fusion when the two arms are compared.
 """
 from __future__ import annotations
 
@@ -67,15 +72,8 @@ class _GPT2(nn.Module):
         return F.cross_entropy(logits.view(B * T, -1).float(), tgt.view(-1))
 
 
-def build_reference(args, rank, world, local_rank, device):
-    # the plugin's _C extension was linked against a build-tree path; load the library by hand first
-    ctypes.CDLL(str(REF / "libflagcx.so"), mode=ctypes.RTLD_GLOBAL)
-    sys.path.insert(0, str(REF))
-    for k in [k for k in sys.modules if k == "flagcx" or k.startswith("flagcx.")]:
-        del sys.modules[k]
-    import flagcx as ref_flagcx  # noqa: F401  (the reference plugin registers backend "flagcx")
-    assert str(REF) in getattr(ref_flagcx, "__file__", ""), "the reference plugin must come from baseline/_ref"
-    dist.init_process_group("cpu:gloo,cuda:flagcx", rank=rank, world_size=world)
+def build_stock_ddp(args, local_rank, device):
+    """Plain PyTorch GPT-2 under stock DistributedDataParallel on whatever backend the process group has."""
     if args.model == "medium":
         model = _GPT2()
         name = "gpt2-medium"
@@ -84,12 +82,12 @@ def build_reference(args, rank, world, local_rank, device):
         name = "gpt2-tiny"
     model = model.to(device=device, dtype=torch.bfloat16)
     ddp = nn.parallel.DistributedDataParallel(model, device_ids=[local_rank], bucket_cap_mb=args.bucket_mb,
-                                              gradient_as_bucket_view=True)
+                                              gradient_as_bucket_view=True) if dist.is_initialized() else model
     params = [p for p in model.parameters()]
     master = [p.detach().float().clone().requires_grad_(True) for p in params]
     opt = torch.optim.AdamW(master, lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, fused=True)
 
-    class Ref:
+    class Runner:
         vocab = model.wte.weight.shape[0]
 
         def step(self, tok, tgt):
@@ -105,10 +103,28 @@ def build_reference(args, rank, world, local_rank, device):
                 torch._foreach_copy_([m.grad for m in master], [p.grad for p in params])
                 opt.step()
                 torch._foreach_copy_(params, master)
-            ddp.zero_grad(set_to_none=False)
+            model.zero_grad(set_to_none=False)
             return loss.detach()
 
         def launches_per_step(self):
             return 0
-    Ref.name = name
-    return Ref()
+
+        def checksum(self):
+            """Three numbers that are equal on every rank exactly when the ranks hold the same weights."""
+            with torch.no_grad():
+                return torch.stack([params[0].float().sum(), params[len(params) // 2].float().sum(),
+                                    params[-1].float().sum()]).double().cpu()
+    Runner.name = name
+    return Runner()
+
+
+def build_reference(args, rank, world, local_rank, device):
+    # the plugin's _C extension was linked against a build-tree path; load the library by hand first
+    ctypes.CDLL(str(REF / "libflagcx.so"), mode=ctypes.RTLD_GLOBAL)
+    sys.path.insert(0, str(REF))
+    for k in [k for k in sys.modules if k == "flagcx" or k.startswith("flagcx.")]:
+        del sys.modules[k]
+    import flagcx as ref_flagcx  # noqa: F401  (the reference plugin registers backend "flagcx")
+    assert str(REF) in getattr(ref_flagcx, "__file__", ""), "the reference plugin must come from baseline/_ref"
+    dist.init_process_group("cpu:gloo,cuda:flagcx", rank=rank, world_size=world)
+    return build_stock_ddp(args, local_rank, device)

@@ -14,6 +14,14 @@ library's NVLink all-reduce kernels, the step captured in a CUDA graph.
 ``--impl reference`` runs the unmodified reference (its PyTorch plugin from
 ``baseline/_ref`` over its libflagcx.so) under stock ``DistributedDataParallel``
 with a plain PyTorch model: none of this framework's code is on that path.
+``--impl ours-c10d`` runs that same plain model and stock
+``DistributedDataParallel`` over THIS framework's c10d backend: against the
+reference arm it isolates the communication library from the model kernels.
+
+After the timed regions every arm compares a checksum of its weights across
+the ranks (over gloo, so neither backend under test carries it) and reports
+``weights_in_sync``; ``first_loss`` / ``final_loss`` are the losses of the
+first warm-up step and of the last timed step on rank 0.
 
 Rank 0 prints one JSON line.  ``value`` is device-timed (CUDA events, max over
 ranks) with inputs already on the device; ``e2e`` times the public
@@ -42,7 +50,7 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--impl", choices=["ours", "reference", "ours-c10d"], default="ours")
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--seq", type=int, default=1024)
     ap.add_argument("--model", choices=["medium", "tiny"], default="medium")
@@ -144,6 +152,11 @@ def main():
     if args.impl == "reference":
         from baseline.reference_arm import build_reference
         runner = build_reference(args, rank, world, local_rank, device)
+    elif args.impl == "ours-c10d":
+        import flagcx  # registers this framework's backend  # noqa: F401
+        from baseline.reference_arm import build_stock_ddp
+        dist.init_process_group("cpu:gloo,cuda:flagcx", rank=rank, world_size=world)
+        runner = build_stock_ddp(args, local_rank, device)
     else:
         import flagcx  # registers the backend  # noqa: F401
         from flagcx_b200.models.gpt2 import GPT2, GPT2Config
@@ -164,6 +177,11 @@ def main():
 
             def launches_per_step(self):
                 return trainer.kernels_per_step()
+
+            def checksum(self):
+                fp = trainer.flat_params
+                k = fp.numel() // 3
+                return torch.stack([fp[:k].float().sum(), fp[k:2 * k].float().sum(), fp[2 * k:].float().sum()]).double().cpu()
         runner = Ours()
 
     B, T = args.micro_batch, args.seq if args.model == "medium" else min(args.seq, 64)
@@ -176,12 +194,15 @@ def main():
 
     def barrier():
         if world > 1:
-            dist.barrier(device_ids=[local_rank]) if args.impl == "ours" else dist.barrier()
+            dist.barrier(device_ids=[local_rank]) if args.impl != "reference" else dist.barrier()
         torch.cuda.synchronize()
 
     # ---- warm-up (includes graph capture for our arm)
+    first_loss = None
     for i in range(max(args.warmup, 3)):
-        runner.step(dev_tok[i % nbuf], dev_tgt[i % nbuf])
+        l0 = runner.step(dev_tok[i % nbuf], dev_tgt[i % nbuf])
+        if first_loss is None:
+            first_loss = float(l0.item())
     torch.cuda.synchronize()
 
     # ---- device-timed region: inputs on the device
@@ -210,10 +231,17 @@ def main():
         wall_ms = (time.perf_counter() - t0) * 1e3
     clk = clocks.summary()
 
+    in_sync = True
     if world > 1:
         t = torch.tensor([dev_ms, e2e_ms, wall_ms], dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)  # CPU tensor: gloo in both arms
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)  # CPU tensor: gloo in every arm
         dev_ms, e2e_ms, wall_ms = t.tolist()
+        # do the ranks hold the same weights?  (checksums travel over gloo)
+        cs = runner.checksum()
+        hi, lo = cs.clone(), cs.clone()
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        in_sync = bool(torch.equal(hi, lo))
 
     tokens = args.steps * B * T * world
     value = tokens / (dev_ms / 1e3)
@@ -234,13 +262,15 @@ def main():
         "impl": args.impl,
         "config": {"model": runner.name, "global_batch": B * world, "seq_len": T, "parallelism": f"dp{world}",
                    "micro_batch": B, "bucket_mb": args.bucket_mb, "master_weights": "fp32",
-                   "l2_policy": "working set per step (weights 0.7 GB + activations) far exceeds the 126 MB L2",
-                   "cuda_graph": (args.impl == "ours" and not args.no_graph)},
+                   "l2_policy": "working set per step (weights 0.7 GB + activations) far exceeds the 126 MB L2"},
+        "cuda_graph": (args.impl == "ours" and not args.no_graph),
         "clocks": clk,
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * T * 8,
                 "d2h_bytes_per_step": 4, "ms_per_step": round(max(e2e_ms, wall_ms) / args.steps, 3)},
         "gpu_launches": int(runner.launches_per_step() * args.steps) if args.impl == "ours" else 0,
+        "first_loss": round(first_loss, 4) if first_loss is not None else None,
         "final_loss": round(last, 4),
+        "weights_in_sync": in_sync,
     }
     if rank == 0:
         print(json.dumps(out))

@@ -423,6 +423,7 @@ flagcxResult_t runHomo(flagcxComm *c, const C2cHomoFunc &h, const PendingOp &o, 
   char *recv = bufs[h.recvType == 1 ? 1 : 2] ? bufs[h.recvType == 1 ? 1 : 2] + h.recvOffset * es : nullptr;
   flagcxStream fs{st};
   int root = h.rootRank >= 0 ? h.rootRank : o.root;
+  InternalCallScope internal;  // stage buffers are cut out of the user's buffers and may overlap
   switch (h.commOp) {
     case flagcxCommOpReduce: return flagcxReduce(send, recv, h.count, o.dt, o.red, root, sub, &fs);
     case flagcxCommOpAllReduce: return flagcxAllReduce(send, recv, h.count, o.dt, o.red, sub, &fs);
@@ -588,7 +589,17 @@ flagcxResult_t c2cExecute(flagcxComm *c, const PendingOp &o, bool *handled) {
 
 using namespace fcx;
 
+static flagcxResult_t commSplitImpl(flagcxComm_t comm, int color, int key, size_t stageBytes, size_t userBytes, flagcxComm_t *newcomm);
+
 extern "C" flagcxResult_t flagcxCommSplit(flagcxComm_t comm, int color, int key, flagcxComm_t *newcomm) {
+  return commSplitImpl(comm, color, key, 0, 0, newcomm);
+}
+extern "C" flagcxResult_t flagcxCommSplitSized(flagcxComm_t comm, int color, int key, size_t stageBytes, size_t userBytes,
+                                               flagcxComm_t *newcomm) {
+  return commSplitImpl(comm, color, key, stageBytes, userBytes, newcomm);
+}
+
+static flagcxResult_t commSplitImpl(flagcxComm_t comm, int color, int key, size_t stageBytes, size_t userBytes, flagcxComm_t *newcomm) {
   if (!validComm(comm) || !newcomm) return flagcxInvalidArgument;
   *newcomm = nullptr;
   const int n = comm->nranks, me = comm->rank;
@@ -617,10 +628,11 @@ extern "C" flagcxResult_t flagcxCommSplit(flagcxComm_t comm, int color, int key,
   const char *savedSplit = getenv("FLAGCX_CLUSTER_SPLIT_LIST");
   std::string saved = savedSplit ? savedSplit : "";
   if (savedSplit) unsetenv("FLAGCX_CLUSTER_SPLIT_LIST");  // a sub-communicator is one cluster
-  flagcxResult_t r = commCreate(&child, (int)members.size(), h, newRank, envInt("SUBCOMM_HEAP_SCALE_PCT", 25) / 100.0, flags);
+  flagcxResult_t r = commCreate(&child, (int)members.size(), h, newRank, envInt("SUBCOMM_HEAP_SCALE_PCT", 25) / 100.0, flags, stageBytes, userBytes);
   if (savedSplit) setenv("FLAGCX_CLUSTER_SPLIT_LIST", saved.c_str(), 1);
   FCX_CHECK(r);
   child->hostFallback = comm->hostFallback;
+  child->parent = comm;
   comm->children.push_back(child);
   *newcomm = child;
   return flagcxSuccess;

@@ -28,6 +28,9 @@ flagcxResult_t c2cExecute(flagcxComm *c, const PendingOp &op, bool *handled);  /
 static thread_local int tGroupDepth = 0;
 static thread_local std::vector<flagcxComm *> tGroupComms;
 int groupDepth() { return tGroupDepth; }
+static thread_local int tInternalDepth = 0;
+InternalCallScope::InternalCallScope() { tInternalDepth++; }
+InternalCallScope::~InternalCallScope() { tInternalDepth--; }
 
 static cudaStream_t streamOf(flagcxStream_t s) { return s ? s->base : (cudaStream_t)0; }
 
@@ -139,6 +142,25 @@ static uint64_t heapOffOf(flagcxComm *c, const void *p, size_t bytes) {
   return ~0ull;
 }
 
+// Where `bytes` at `p` live as the peers see them: the symmetric heap, a registered segment, or nowhere.
+static void resolveSeg(flagcxComm *c, const void *p, size_t bytes, int *seg, uint64_t *off) {
+  *seg = FCX_SEG_NONE;
+  *off = ~0ull;
+  if (!p) return;
+  uint64_t h = heapOffOf(c, p, bytes);
+  if (h != ~0ull) { *seg = FCX_SEG_HEAP; *off = h; return; }
+  for (int i = 1; i < (int)c->segs.size(); i++) {
+    const Segment &sg = c->segs[i];
+    if (sg.used && (const char *)p >= sg.localBase && (const char *)p + bytes <= sg.localBase + sg.bytes) {
+      *seg = i;
+      *off = (const char *)p - sg.localBase;
+      return;
+    }
+  }
+}
+
+static bool isZcKind(int k) { return k == FCX_K_AR_ZC || k == FCX_K_RS_ZC || k == FCX_K_REDUCE_ZC || k == FCX_K_MOVE_ZC; }
+
 // The byte mover a collective stands for when it runs in its LL form.
 static int moveKindOf(flagcxCommOp_t op) {
   switch (op) {
@@ -188,6 +210,57 @@ flagcxResult_t launchCollective(flagcxComm *c, const PendingOp &o) {
     return launchOne(c, a, p, o.stream, false);
   }
 
+  // A stream that is being captured must not see the online search (it synchronises on events).
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(o.stream, &capturing) != cudaSuccess) { cudaGetLastError(); capturing = cudaStreamCaptureStatusNone; }
+  const bool maySearch = capturing == cudaStreamCaptureStatusNone;
+
+  // Zero-copy route: the buffer that every rank hands to this collective is peer-visible (the ranks must
+  // agree on that; a rank that finds a peer's buffer missing records a bad-argument error, it never guesses).
+  static const bool zcEnabled = envInt("ZERO_COPY", 1) != 0;
+  static const int zcMc = (envInt("ZC_MC", 1) != 0 ? 1 : 0) | (envInt("ZC_AG_MC", 1) != 0 ? 2 : 0);
+  a.sendSeg = a.recvSeg = FCX_SEG_NONE;
+  bool zc = false;
+  if (zcEnabled && n > 1) {
+    int sseg, rseg;
+    uint64_t soff, roff;
+    size_t sspan = 0, rspan = 0;
+    bool needS = false, needR = false;
+    switch (o.op) {
+      case flagcxCommOpAllReduce: needS = needR = true; sspan = o.count * es; rspan = o.count * eso; break;
+      case flagcxCommOpReduceScatter: needS = true; sspan = (size_t)n * o.count * es; break;
+      case flagcxCommOpReduce: needS = true; sspan = o.count * es; break;
+      case flagcxCommOpGather: needS = true; sspan = o.count * es; break;
+      case flagcxCommOpAllGather: needR = true; rspan = (size_t)n * o.count * es; break;
+      case flagcxCommOpBroadcast: case flagcxCommOpScatter: needR = true; rspan = o.count * es; break;
+      case flagcxCommOpAlltoAll: needR = send != recv; rspan = (size_t)n * o.count * es; break;
+      case flagcxCommOpAlltoAllv: {
+        needS = send != recv;
+        const size_t *t = o.tables.data();
+        for (int i = 0; i < n; i++) sspan = std::max(sspan, (t[i] + t[n + i]) * es);
+        break;
+      }
+      default: break;
+    }
+    resolveSeg(c, needS ? send : nullptr, sspan, &sseg, &soff);
+    resolveSeg(c, needR ? recv : nullptr, rspan, &rseg, &roff);
+    zc = (needS || needR) && (!needS || sseg != FCX_SEG_NONE) && (!needR || rseg != FCX_SEG_NONE);
+    if (zc) {
+      a.sendSeg = needS ? sseg : FCX_SEG_NONE;
+      a.sendHeapOff = needS ? soff : ~0ull;
+      a.recvSeg = needR ? rseg : FCX_SEG_NONE;
+      a.recvHeapOff = needR ? roff : ~0ull;
+      a.useMc = c->dev.mcHeap != nullptr ? zcMc : 0;
+    }
+  }
+  auto launchZc = [&](const Plan &p, bool timed) {
+    a.send = send;
+    a.recv = recv;
+    a.count = o.count;
+    a.sendStride = a.recvStride = o.count;
+    return launchOne(c, a, p, o.stream, timed);
+  };
+
   if (o.op == flagcxCommOpAlltoAllv) {
     const size_t *t = o.tables.data();
     size_t maxPair = 0;
@@ -200,6 +273,12 @@ flagcxResult_t launchCollective(flagcxComm *c, const PendingOp &o) {
     }
     a.send = send;
     a.recv = recv;
+    if (zc) {
+      a.moveOp = FCX_K_A2AV;
+      static const int zcCtas = (int)std::max<int64_t>(1, std::min<int64_t>(envInt("A2AV_CTAS", 32), FCX_MAX_CTAS));
+      Plan p{FCX_K_MOVE_ZC, c->tuner->ctaBudget() > 0 ? std::min(zcCtas, c->tuner->ctaBudget()) : zcCtas};
+      return launchOne(c, a, p, o.stream, false);
+    }
     // like the reference (flagcx/flagcx.cc:1613-1616) the variable all-to-all is not searched online
     // The ranks see different counts, so nothing derived from them may shape the launch: every rank must
     // run the same number of CTAs (they pair up across GPUs).
@@ -219,12 +298,28 @@ flagcxResult_t launchCollective(flagcxComm *c, const PendingOp &o) {
     default: cap = (stage / n - 64) / es; break;  // per-rank piece
   }
   cap &= ~(size_t)63;
+  if (zc) {
+    // no staging, hence no size limit: the whole message is one launch when the tuner picks a zero-copy kind
+    bool timed = false;
+    Plan p = c->tuner->choose(o.op, std::max<size_t>(o.count * es, 1), o.dt, o.red, cast, &timed, true, maySearch);
+    if (isZcKind(p.kind)) return launchZc(p, timed);
+    a.sendSeg = a.recvSeg = FCX_SEG_NONE;
+    a.sendHeapOff = a.recvHeapOff = ~0ull;
+    a.useMc = c->dev.mcHeap != nullptr;
+    if (o.count <= cap) {  // a staged kind won the search or is pinned: the message fits one launch
+      a.count = o.count;
+      a.send = send;
+      a.recv = recv;
+      a.sendStride = a.recvStride = o.count;
+      return launchOne(c, a, p, o.stream, timed);
+    }
+  }
   size_t done = 0;
   do {
     size_t cnt = std::min(cap, o.count - done);
     size_t bytes = cnt * es;
     bool timed = false;
-    Plan p = c->tuner->choose(o.op, std::max<size_t>(bytes, 1), o.dt, o.red, cast, &timed);
+    Plan p = c->tuner->choose(o.op, std::max<size_t>(bytes, 1), o.dt, o.red, cast, &timed, false, maySearch);
     a.count = cnt;
     switch (o.op) {
       case flagcxCommOpAllReduce:
@@ -353,6 +448,35 @@ static flagcxResult_t validate(flagcxComm_t c, const PendingOp &o) {
     bool needRecv = o.op != flagcxCommOpSend && !(o.op == flagcxCommOpGather && c->rank != o.root) &&
                     !(o.op == flagcxCommOpReduce && c->rank != o.root);
     if ((needSend && !o.send) || (needRecv && !o.recv)) { FCX_WARN("null buffer"); return flagcxInvalidArgument; }
+    // element alignment: the kernels load and store whole elements
+    const size_t es = dtypeSize(o.dt), eso = dtypeSize(o.outDt), n = (size_t)c->nranks;
+    if ((needSend && ((uintptr_t)o.send % es)) || (needRecv && ((uintptr_t)o.recv % eso))) {
+      FCX_WARN("buffer not aligned to its element size (%zu / %zu bytes)", es, eso);
+      return flagcxInvalidArgument;
+    }
+    if (o.op == flagcxCommOpAlltoAllv) return flagcxSuccess;  // extents come from the tables
+    // count x size x ranks must fit size_t
+    const size_t widest = std::max(es, eso);
+    if (o.count > (~(size_t)0) / widest / n) { FCX_WARN("count %zu overflows the byte size of the buffer", o.count); return flagcxInvalidArgument; }
+    // send and receive ranges: identical or the documented in-place position, otherwise disjoint
+    size_t sb = o.count * es, rb = o.count * eso;
+    const char *inPlaceSend = (const char *)o.recv;  // where send may sit inside recv
+    switch (o.op) {
+      case flagcxCommOpAllGather: case flagcxCommOpGather: rb = n * o.count * es; inPlaceSend = (const char *)o.recv + (size_t)c->rank * sb; break;
+      case flagcxCommOpReduceScatter: case flagcxCommOpScatter: sb = n * o.count * es; break;
+      case flagcxCommOpAlltoAll: sb = rb = n * o.count * es; break;
+      default: break;
+    }
+    if (needSend && needRecv && tInternalDepth == 0) {
+      const char *s0 = (const char *)o.send, *r0 = (const char *)o.recv;
+      bool inPlace = s0 == inPlaceSend;
+      if (o.op == flagcxCommOpReduceScatter || o.op == flagcxCommOpScatter) inPlace = r0 == s0 + (size_t)c->rank * rb;
+      const bool overlap = s0 < r0 + rb && r0 < s0 + sb;
+      if (overlap && !inPlace) {
+        FCX_WARN("send and receive buffers overlap without being the in-place form of the operation");
+        return flagcxInvalidArgument;
+      }
+    }
   }
   return flagcxSuccess;
 }
@@ -577,10 +701,21 @@ flagcxResult_t flagcxTunerPin(flagcxComm_t comm, const char *kind, int nctas) {
   return flagcxSuccess;
 }
 
+flagcxResult_t flagcxCommSetCtaBudget(flagcxComm_t comm, int maxCtas) {
+  if (!validComm(comm) || maxCtas < 0) return flagcxInvalidArgument;
+  if (comm->tuner) comm->tuner->setCtaBudget(maxCtas);
+  return flagcxSuccess;
+}
+
 flagcxResult_t flagcxTunerQuery(flagcxComm_t comm, flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red,
                                 char *kindOut, size_t kindOutBytes, int *nctas, double *estimate) {
+  return flagcxTunerQueryEx(comm, op, bytes, dt, red, 0, kindOut, kindOutBytes, nctas, estimate);
+}
+
+flagcxResult_t flagcxTunerQueryEx(flagcxComm_t comm, flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red,
+                                  int zeroCopy, char *kindOut, size_t kindOutBytes, int *nctas, double *estimate) {
   if (!validComm(comm)) return flagcxInvalidArgument;
-  Plan p = comm->tuner->peek(op, bytes, dt, red, false);
+  Plan p = comm->tuner->peek(op, bytes, dt, red, false, zeroCopy != 0);
   if (kindOut && kindOutBytes) snprintf(kindOut, kindOutBytes, "%s", kindName(p.kind));
   if (nctas) *nctas = p.nctas;
   if (estimate) *estimate = comm->tuner->estimate(p, op, bytes, dt);

@@ -4,13 +4,24 @@
 #include "hosttypes.h"
 #include "log.h"
 
+#include <algorithm>
 #include <cstring>
+#include <set>
 #include <cuda_runtime.h>
 #include <unistd.h>
 
 namespace fcx {
 
-bool validComm(flagcxComm_t c) { return c && c->magic == 0xF1A6C0DE && !c->destroyed; }
+// Live communicators, and destroyed ones that still lend heap memory out.  validComm never dereferences a
+// pointer that is in neither set, so a stale handle is refused instead of read.
+static std::mutex gCommMu;
+static std::set<flagcxComm *> gLive, gLent;
+
+bool validComm(flagcxComm_t c) {
+  if (!c) return false;
+  std::lock_guard<std::mutex> lk(gCommMu);
+  return gLive.count(c) != 0 && c->magic == 0xF1A6C0DE && !c->destroyed;
+}
 
 flagcxResult_t cudaToResult(cudaError_t e, const char *what) {
   if (e == cudaSuccess) return flagcxSuccess;
@@ -67,7 +78,8 @@ static void detectClusters(flagcxComm *c) {
   c->myCluster = c->clusterOf[c->rank];
 }
 
-flagcxResult_t commCreate(flagcxComm **out, int nranks, const BootstrapHandle &h, int rank, double heapScale, unsigned flags) {
+flagcxResult_t commCreate(flagcxComm **out, int nranks, const BootstrapHandle &h, int rank, double heapScale, unsigned flags,
+                          size_t stageOverride, size_t userOverride) {
   if (nranks < 1 || rank < 0 || rank >= nranks) return flagcxInvalidArgument;
   std::unique_ptr<flagcxComm> c(new flagcxComm);
   c->rank = rank;
@@ -121,9 +133,11 @@ flagcxResult_t commCreate(flagcxComm **out, int nranks, const BootstrapHandle &h
       }
     }
     size_t stage = (size_t)((double)envInt("STAGE_BYTES", 512ll << 20) * heapScale);
+    if (stageOverride) stage = stageOverride;
     stage = std::max<size_t>(stage, 1u << 20) & ~(size_t)4095;
     size_t chunk = (size_t)envInt("P2P_CHUNK_BYTES", 16ll << 20) & ~(size_t)4095;
     size_t user = (size_t)((double)envInt("HEAP_USER_BYTES", 512ll << 20) * heapScale);
+    if (userOverride) user = (userOverride + 4095) & ~(size_t)4095;
     size_t p2pOff = FCX_OFF_STAGE + 2 * stage;
     size_t userOff = p2pOff + (size_t)FCX_MAX_RANKS * 2 * chunk;
     size_t total = userOff + user;
@@ -174,6 +188,7 @@ flagcxResult_t commCreate(flagcxComm **out, int nranks, const BootstrapHandle &h
   c->tuner.reset(new Tuner(&c->bs, caps));
   flagcxComm *raw = c.release();
   *out = raw;
+  { std::lock_guard<std::mutex> lk(gCommMu); gLive.insert(raw); }
   // FLAGCX_KERNEL_PROXY=1 (reference: flagcx/core/proxy.cc:1074-1182): start the thread that serves the
   // device->host request queue with the communicator instead of at the first flagcxCommFifoBuffer call.
   if (envInt("KERNEL_PROXY", 0) != 0 && !raw->hostOnly && raw->heap.bytes) {
@@ -183,10 +198,33 @@ flagcxResult_t commCreate(flagcxComm **out, int nranks, const BootstrapHandle &h
   return flagcxSuccess;
 }
 
+// Unmap the heap and free what hangs off the communicator.
+static void commRelease(flagcxComm *c) {
+  if (!c->hostOnly && c->heap.bytes) {
+    for (auto &s : c->segs)
+      if (s.used)
+        for (int r = 0; r < c->nranks; r++)
+          if (r != c->rank && s.peer[r]) cudaIpcCloseMemHandle(s.peer[r]);
+    c->heap.destroy();
+    if (c->errHost) cudaFreeHost(c->errHost);
+    if (c->segsDev) cudaFree(c->segsDev);
+    cudaGetLastError();
+  }
+  delete c;
+}
+
 flagcxResult_t commFree(flagcxComm *c) {
   if (!c) return flagcxSuccess;
-  for (flagcxComm *ch : c->children) commFree(ch);
-  c->children.clear();
+  {
+    std::lock_guard<std::mutex> lk(gCommMu);
+    if (!gLive.count(c)) return flagcxSuccess;  // already destroyed (a child freed with its parent, or twice)
+  }
+  while (!c->children.empty()) commFree(c->children.back());  // each child takes itself off the list
+  if (c->parent) {
+    auto &sib = c->parent->children;
+    sib.erase(std::remove(sib.begin(), sib.end(), c), sib.end());
+    c->parent = nullptr;
+  }
   fifoStop(c);
   c2cDestroy(c);
   if (!c->hostOnly && c->heap.bytes) {
@@ -202,19 +240,48 @@ flagcxResult_t commFree(flagcxComm *c) {
     }
     // Peers must stop touching this heap before it is unmapped.
     if (!c->abortFlag.load()) c->bs.barrier();
-    for (auto &s : c->segs)
-      if (s.used)
-        for (int r = 0; r < c->nranks; r++)
-          if (r != c->rank && s.peer[r]) cudaIpcCloseMemHandle(s.peer[r]);
-    c->heap.destroy();
-    if (c->errHost) cudaFreeHost(c->errHost);
-    if (c->segsDev) cudaFree(c->segsDev);
-    cudaGetLastError();
   }
   FCX_INFO(SUB_INIT, "communicator %p (rank %d of %d) destroyed", (void *)c, c->rank, c->nranks);
   c->bs.close();
-  c->destroyed = true;
-  delete c;
+  bool lent;
+  {
+    std::lock_guard<std::mutex> lk(gCommMu);
+    gLive.erase(c);
+    c->destroyed = true;
+    lent = c->heapRefs.load() > 0;
+    if (lent) gLent.insert(c);
+  }
+  if (lent) {
+    FCX_INFO(SUB_ALLOC, "communicator %p: %d heap buffers are still held; the heap stays mapped until they are released", (void *)c,
+             c->heapRefs.load());
+    return flagcxSuccess;
+  }
+  commRelease(c);
+  return flagcxSuccess;
+}
+
+// A holder of heap memory that may outlive the communicator (a tensor) takes a reference when it gets the
+// memory and gives it back with the pointer.
+flagcxResult_t commHeapRetain(flagcxComm *c) {
+  std::lock_guard<std::mutex> lk(gCommMu);
+  if (!gLive.count(c)) return flagcxInvalidArgument;
+  c->heapRefs.fetch_add(1);
+  return flagcxSuccess;
+}
+
+flagcxResult_t commHeapRelease(flagcxComm *c, void *ptr) {
+  bool last = false, live = false;
+  {
+    std::lock_guard<std::mutex> lk(gCommMu);
+    live = gLive.count(c) != 0;
+    if (!live && !gLent.count(c)) return flagcxInvalidArgument;
+    if (c->heapRefs.fetch_sub(1) == 1 && !live) { gLent.erase(c); last = true; }
+  }
+  if (live && ptr) {
+    char *base = c->heap.base[c->rank];
+    if ((char *)ptr >= base && (char *)ptr < base + c->heap.bytes) c->arena.free((char *)ptr - base);
+  }
+  if (last) commRelease(c);
   return flagcxSuccess;
 }
 
@@ -570,6 +637,9 @@ flagcxResult_t flagcxCommDeregister(const flagcxComm_t comm, void *handle) {
 
 // ---- extensions
 
+flagcxResult_t flagcxCommHeapRetain(flagcxComm_t comm) { return commHeapRetain(comm); }
+flagcxResult_t flagcxCommHeapRelease(flagcxComm_t comm, void *ptr) { return commHeapRelease(comm, ptr); }
+
 flagcxResult_t flagcxCommGetCounters(flagcxComm_t comm, flagcxCommCounters *out) {
   if (!validComm(comm) || !out) return flagcxInvalidArgument;
   *out = comm->counters;
@@ -643,6 +713,45 @@ flagcxResult_t flagcxCommClearError(flagcxComm_t comm) {
     // errClaim and abortSeen live at the start of the local block
     FCX_CHECK(cudaToResult(cudaMemset(comm->heap.base[comm->rank] + FCX_OFF_LOCAL, 0, 16), "clear error"));
   }
+  return flagcxSuccess;
+}
+
+// Collective re-synchronisation after a collective gave up on some rank.  The ranks may disagree on how many
+// collectives completed (a rank that left in its prologue did not count the call, one that left later did),
+// and every wait is a ">=" on values built from that count, so carrying on would let the rank that is behind
+// pass barriers on flags left by its peers' newer calls.  All ranks therefore agree on a sequence number
+// above anything used so far, rewrite their counters to it and clear the control words behind host barriers.
+flagcxResult_t flagcxCommRecover(flagcxComm_t comm) {
+  if (!validComm(comm)) return flagcxInvalidArgument;
+  if (comm->hostOnly || !comm->heap.bytes) return flagcxSuccess;
+  FCX_CHECK(cudaToResult(cudaDeviceSynchronize(), "recover"));
+  char *base = comm->heap.base[comm->rank];
+  // FcxLocal: {ctaDone, errClaim, abortSeen, pad, seq, opCount[][]}
+  unsigned long long seq = 0;
+  FCX_CHECK(cudaToResult(cudaMemcpy(&seq, base + FCX_OFF_LOCAL + 16, sizeof seq, cudaMemcpyDeviceToHost), "recover: read seq"));
+  std::vector<unsigned long long> all(comm->nranks, 0);
+  all[comm->rank] = seq;
+  FCX_CHECK(comm->bs.allGather(all.data(), sizeof(unsigned long long)));  // also a barrier: every rank's device is idle
+  unsigned long long next = 0;
+  for (auto v : all) next = std::max(next, v);
+  next += 2;
+  // nobody launches before everybody has reset, and nobody resets while somebody could still be running
+  FCX_CHECK(cudaToResult(cudaMemset(base + FCX_OFF_FLAGS, 0, FCX_OFF_DONE - FCX_OFF_FLAGS), "recover: flags"));
+  std::vector<unsigned long long> done(FCX_MAX_RANKS, next);
+  FCX_CHECK(cudaToResult(cudaMemcpy(base + FCX_OFF_DONE, done.data(), sizeof(unsigned long long) * FCX_MAX_RANKS, cudaMemcpyHostToDevice),
+                         "recover: done words"));
+  FCX_CHECK(cudaToResult(cudaMemset(base + FCX_OFF_MAIL, 0, FCX_OFF_P2P - FCX_OFF_MAIL), "recover: mailboxes"));
+  FCX_CHECK(cudaToResult(cudaMemset(base + FCX_OFF_P2P, 0, FCX_OFF_LOCAL - FCX_OFF_P2P), "recover: p2p control"));
+  FCX_CHECK(cudaToResult(cudaMemset(base + FCX_OFF_LOCAL, 0, FCX_OFF_DEVAPI - FCX_OFF_LOCAL), "recover: local words"));
+  FCX_CHECK(cudaToResult(cudaMemcpy(base + FCX_OFF_LOCAL + 16, &next, sizeof next, cudaMemcpyHostToDevice), "recover: seq"));
+  FCX_CHECK(cudaToResult(cudaMemset(base + FCX_OFF_LL, 0, 2 * (size_t)FCX_MAX_RANKS * FCX_LL_SLOT_BYTES), "recover: LL lines"));
+  memset(comm->sendChunks, 0, sizeof comm->sendChunks);
+  memset(comm->recvChunks, 0, sizeof comm->recvChunks);
+  comm->seq = next;
+  if (comm->errHost) memset(comm->errHost, 0, sizeof(FcxDevError));
+  FCX_CHECK(cudaToResult(cudaDeviceSynchronize(), "recover"));
+  FCX_CHECK(comm->bs.barrier());
+  FCX_INFO(SUB_INIT, "communicator %p re-synchronised at sequence %llu", (void *)comm, next);
   return flagcxSuccess;
 }
 

@@ -91,9 +91,13 @@ struct flagcxComm {
   fcx::C2cState *c2c = nullptr;
   // device->host request queue
   fcx::FifoService *fifo = nullptr;
-  // communicators split off this one, destroyed with it
+  // communicators split off this one, destroyed with it (a child destroyed on its own leaves this list)
   std::vector<flagcxComm *> children;
+  flagcxComm *parent = nullptr;
   bool destroyed = false;
+  // Heap memory handed to owners that may outlive the communicator (tensors): while any is outstanding a
+  // destroyed communicator keeps its heap mapped and is only freed by the last release.
+  std::atomic<int> heapRefs{0};
 };
 
 namespace fcx {
@@ -106,9 +110,20 @@ flagcxResult_t launchCollective(flagcxComm *c, const PendingOp &op);
 flagcxResult_t launchP2pBatch(flagcxComm *c, const std::vector<PendingOp> &ops);
 flagcxResult_t hostCollective(flagcxComm *c, const PendingOp &op);
 int groupDepth();
+// While an object of this type lives on a thread, the overlap rule of the argument check is off for that
+// thread's calls: the hierarchical planner cuts user buffers into stage buffers that may legitimately overlap.
+struct InternalCallScope {
+  InternalCallScope();
+  ~InternalCallScope();
+};
 
 // comm.cc
-flagcxResult_t commCreate(flagcxComm **out, int nranks, const BootstrapHandle &h, int rank, double heapScale, unsigned flags);
+// stageOverride / userOverride: bytes of one staging half and of the flagcxMemAlloc area (0: FLAGCX_STAGE_BYTES /
+// FLAGCX_HEAP_USER_BYTES times heapScale).
+flagcxResult_t commCreate(flagcxComm **out, int nranks, const BootstrapHandle &h, int rank, double heapScale, unsigned flags,
+                          size_t stageOverride = 0, size_t userOverride = 0);
 flagcxResult_t commFree(flagcxComm *c);
+flagcxResult_t commHeapRetain(flagcxComm *c);
+flagcxResult_t commHeapRelease(flagcxComm *c, void *ptr);
 
 }  // namespace fcx

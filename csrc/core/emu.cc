@@ -117,8 +117,16 @@ flagcxResult_t flagcxEmuCollective(flagcxEmu_t e, flagcxCommOp_t op, const char 
     a.recv = recv ? recv[r] : nullptr;
     a.count = count;
     a.sendHeapOff = a.recvHeapOff = ~0ull;
+    a.sendSeg = a.recvSeg = FCX_SEG_NONE;
+    if (k == FCX_K_AR_ZC || k == FCX_K_RS_ZC || k == FCX_K_REDUCE_ZC || k == FCX_K_MOVE_ZC) {
+      // one device holds every emulated rank's buffers, so a buffer's address is valid for all of them
+      a.sendSeg = a.send ? FCX_SEG_ABS : FCX_SEG_NONE;
+      a.sendHeapOff = (uint64_t)(uintptr_t)a.send;
+      a.recvSeg = a.recv ? FCX_SEG_ABS : FCX_SEG_NONE;
+      a.recvHeapOff = (uint64_t)(uintptr_t)a.recv;
+    }
     a.moveOp = op == flagcxCommOpAllGather ? FCX_K_AG : op == flagcxCommOpBroadcast ? FCX_K_BCAST : op == flagcxCommOpGather ? FCX_K_GATHER
-               : op == flagcxCommOpScatter ? FCX_K_SCATTER : op == flagcxCommOpAlltoAll ? FCX_K_A2A : 0;
+               : op == flagcxCommOpScatter ? FCX_K_SCATTER : op == flagcxCommOpAlltoAll ? FCX_K_A2A : op == flagcxCommOpAlltoAllv ? FCX_K_A2AV : 0;
     switch (op) {
       case flagcxCommOpAllGather: case flagcxCommOpGather: a.recvStride = count; break;
       case flagcxCommOpReduceScatter: case flagcxCommOpScatter: a.sendStride = count; break;

@@ -11,7 +11,8 @@
 namespace fcx {
 
 static const char *kKindNames[FCX_K_NUM] = {"barrier", "ar_ll", "ar_oneshot", "ar_twoshot", "ar_nvls", "rs", "rs_nvls", "ag",
-                                            "ag_nvls", "bcast", "reduce", "gather", "scatter", "a2a", "a2av", "move_ll", "rs_ll", "reduce_ll"};
+                                            "ag_nvls", "bcast", "reduce", "gather", "scatter", "a2a", "a2av", "move_ll", "rs_ll", "reduce_ll",
+                                            "ar_zc", "rs_zc", "reduce_zc", "move_zc"};
 
 const char *kindName(int kind) { return kind >= 0 && kind < FCX_K_NUM ? kKindNames[kind] : "?"; }
 
@@ -35,6 +36,11 @@ constexpr double kLaunchUs = 2.2, kBarrierUs = 1.8, kLLUs = 1.6, kPipeBarrierUs 
 constexpr double kLinkRate = 680e3, kCtaPushRate = 40e3, kCtaMmRate = 3.5e3;  // multimem: 64-128 CTAs reached 430-490 GB/s on four GPUs
 constexpr double kHbmRate = 5500e3, kCtaLocalRate = 60e3;
 
+// Zero-copy kinds: a CTA keeps 8 switch reductions of 16 bytes per thread in flight (about 20 GB/s per CTA at
+// the switch's round-trip time), pulls about 30 GB/s from peers with plain loads, and stores through the
+// multicast alias at about the plain push rate.
+constexpr double kCtaZcMmRate = 20e3, kCtaPullRate = 30e3;
+
 double pushUs(double bytes, double nctas) { return bytes / std::min(kLinkRate, std::max(1.0, nctas) * kCtaPushRate); }
 double mmUs(double bytes, double nctas) { return bytes / std::min(kLinkRate, std::max(1.0, nctas) * kCtaMmRate); }
 double localUs(double bytes, double nctas) { return bytes / std::min(kHbmRate, std::max(1.0, nctas) * kCtaLocalRate); }
@@ -51,10 +57,34 @@ double pipelinedUs(double linkBytes, double localBytes, double pieceBytes, int d
 }
 }  // namespace
 
-double estimateUs(const Plan &p, flagcxCommOp_t, size_t bytesIn, int, const TunerCaps &caps) {
+double estimateUs(const Plan &p, flagcxCommOp_t op, size_t bytesIn, int, const TunerCaps &caps) {
   const double b = (double)bytesIn, n = caps.nranks;
   const int c = p.nctas;
+  const bool mc = caps.multicast;
+  const double zcFixed = kLaunchUs + 2 * kBarrierUs;
   switch (p.kind) {
+    // zero-copy kinds: two barriers, one pass; bound by the link or by what `c` CTAs keep in flight
+    case FCX_K_AR_ZC:
+      if (mc) return zcFixed + std::max(b * (1 + 1 / n) / kLinkRate, b / n / (c * kCtaZcMmRate));
+      return zcFixed + std::max(b * (n - 1) / n / kLinkRate, b * (n - 1) / n / (c * kCtaPullRate));
+    case FCX_K_RS_ZC:  // b: per-rank piece
+      if (mc) return zcFixed + std::max(b * (n - 1) / kLinkRate, b / (c * kCtaZcMmRate));
+      return zcFixed + std::max(b * (n - 1) / kLinkRate, b * (n - 1) / (c * kCtaPullRate));
+    case FCX_K_REDUCE_ZC:
+      if (mc) return zcFixed + std::max(b / kLinkRate, b / (c * kCtaZcMmRate));
+      return zcFixed + std::max(b * (n - 1) / kLinkRate, b * (n - 1) / (c * kCtaPullRate));
+    case FCX_K_MOVE_ZC:
+      switch (op) {
+        case flagcxCommOpBroadcast:
+          return zcFixed + (mc ? std::max(b / kLinkRate, b / (c * kCtaPushRate)) : std::max(b * (n - 1) / kLinkRate, b * (n - 1) / (c * kCtaPushRate)));
+        case flagcxCommOpAllGather:
+          return zcFixed + std::max(b * (n - 1) / kLinkRate, (mc ? b : b * (n - 1)) / (c * kCtaPushRate));
+        case flagcxCommOpGather:
+        case flagcxCommOpAlltoAllv:
+          return zcFixed + std::max(b * (n - 1) / kLinkRate, b * (n - 1) / (c * kCtaPullRate));
+        default:
+          return zcFixed + std::max(b * (n - 1) / kLinkRate, b * (n - 1) / (c * kCtaPushRate));
+      }
     case FCX_K_BARRIER: return kLaunchUs + kBarrierUs;
     case FCX_K_AR_LL: return kLaunchUs + kLLUs + pushUs(2 * (n - 1) * b, c) + localUs(2 * n * b, c);
     case FCX_K_AR_ONESHOT: return kLaunchUs + kBarrierUs + pushUs((n - 1) * b, c) + localUs((n + 1) * b, c);
@@ -122,7 +152,7 @@ static void addCtas(std::vector<Plan> &out, int kind, std::initializer_list<int>
   }
 }
 
-std::vector<Plan> Tuner::candidates(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red, bool cast) const {
+std::vector<Plan> Tuner::candidates(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red, bool cast, bool zc) const {
   std::vector<Plan> out;
   const int n = caps_.nranks;
   const size_t units = (bytes + 15) / 16;
@@ -136,37 +166,55 @@ std::vector<Plan> Tuner::candidates(flagcxCommOp_t op, size_t bytes, flagcxDataT
       if ((bytes + 64) * n <= caps_.stageBytes && bytes <= (8u << 20)) addCtas(out, FCX_K_AR_ONESHOT, {2, 8, 16, 32, 64}, units, mx);
       if (bytes > 2048 || out.empty()) addCtas(out, FCX_K_AR_TWOSHOT, {8, 16, 32, 64, 128}, units / n + 1, mx);
       if (nvls && bytes >= 4096) addCtas(out, FCX_K_AR_NVLS, {8, 16, 32, 64, 128}, units / n + 1, mx);
+      if (zc && n > 1) addCtas(out, FCX_K_AR_ZC, {1, 2, 4, 8, 16, 24, 32, 48, 64, 96}, units / n + 1, mx);
       break;
     case flagcxCommOpReduceScatter:
       if (!cast && bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_RS_LL, {1, 2, 4}, units, mx);
       addCtas(out, FCX_K_RS, {2, 8, 16, 32, 64, 128}, units, mx);
       if (nvls && bytes >= 4096) addCtas(out, FCX_K_RS_NVLS, {8, 16, 32, 64, 128}, units, mx);
+      if (zc && n > 1) addCtas(out, FCX_K_RS_ZC, {1, 2, 4, 8, 16, 24, 32, 48, 64, 96}, units, mx);
       break;
     case flagcxCommOpAllGather:
       if (bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_MOVE_LL, {1, 2, 4}, units, mx);
       addCtas(out, FCX_K_AG, {2, 8, 16, 32, 64, 128}, units, mx);
       if (caps_.multicast && n > 1 && bytes >= 4096) addCtas(out, FCX_K_AG_NVLS, {8, 16, 32, 64, 128}, units, mx);
+      if (zc && n > 1) addCtas(out, FCX_K_MOVE_ZC, {1, 2, 4, 8, 16, 24, 32, 48, 64, 96}, units, mx);
       break;
     case flagcxCommOpReduce:
       if (!cast && bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_REDUCE_LL, {1, 2, 4}, units, mx);
-      addCtas(out, FCX_K_REDUCE, {2, 8, 16, 32, 64, 128}, units / n + 1, mx); break;
+      addCtas(out, FCX_K_REDUCE, {2, 8, 16, 32, 64, 128}, units / n + 1, mx);
+      if (zc && n > 1 && nvls) addCtas(out, FCX_K_REDUCE_ZC, {1, 2, 4, 8, 16, 24, 32, 48, 64, 96}, units, mx);
+      break;
     case flagcxCommOpBroadcast:
       if (bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_MOVE_LL, {1, 2, 4}, units, mx);
-      addCtas(out, FCX_K_BCAST, {1, 4, 16, 32, 64, 128}, units, mx); break;
+      addCtas(out, FCX_K_BCAST, {1, 4, 16, 32, 64, 128}, units, mx);
+      if (zc && n > 1) addCtas(out, FCX_K_MOVE_ZC, {1, 2, 4, 8, 16, 24, 32, 48, 64, 96}, units, mx);
+      break;
     case flagcxCommOpGather:
       if (bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_MOVE_LL, {1, 2, 4}, units, mx);
-      addCtas(out, FCX_K_GATHER, {1, 4, 16, 64, 128}, units, mx); break;
+      addCtas(out, FCX_K_GATHER, {1, 4, 16, 64, 128}, units, mx);
+      if (zc && n > 1) addCtas(out, FCX_K_MOVE_ZC, {1, 2, 4, 8, 16, 24, 32, 48, 64, 96}, units, mx);
+      break;
     case flagcxCommOpScatter:
       if (bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_MOVE_LL, {1, 2, 4}, units, mx);
-      addCtas(out, FCX_K_SCATTER, {1, 4, 16, 64, 128}, units, mx); break;
+      addCtas(out, FCX_K_SCATTER, {1, 4, 16, 64, 128}, units, mx);
+      if (zc && n > 1) addCtas(out, FCX_K_MOVE_ZC, {1, 2, 4, 8, 16, 24, 32, 48, 64, 96}, units, mx);
+      break;
     case flagcxCommOpAlltoAll:
       if (bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_MOVE_LL, {1, 2, 4}, units, mx);
-      addCtas(out, FCX_K_A2A, {2, 8, 16, 32, 64, 128}, units, mx); break;
-    case flagcxCommOpAlltoAllv: addCtas(out, FCX_K_A2AV, {2, 8, 16, 32, 64, 128}, units, mx); break;
+      addCtas(out, FCX_K_A2A, {2, 8, 16, 32, 64, 128}, units, mx);
+      if (zc && n > 1) addCtas(out, FCX_K_MOVE_ZC, {1, 2, 4, 8, 16, 24, 32, 48, 64, 96}, units, mx);
+      break;
+    case flagcxCommOpAlltoAllv:
+      addCtas(out, FCX_K_A2AV, {2, 8, 16, 32, 64, 128}, units, mx);
+      if (zc && n > 1) addCtas(out, FCX_K_MOVE_ZC, {8, 16, 32, 64}, units, mx);
+      break;
     default: out.push_back({FCX_K_BARRIER, 1}); break;
   }
   return out;
 }
+
+static int sigOf(flagcxDataType_t dt, flagcxRedOp_t red, bool cast) { return ((int)dt << 8) | ((int)red << 4) | (cast ? 1 : 0); }
 
 void Tuner::decide(const Key &k, Search &s) {
   // Average every candidate's mean time over the ranks, then take the minimum.
@@ -183,22 +231,26 @@ void Tuner::decide(const Key &k, Search &s) {
     if (mean[i] < mean[bestI] * 0.95) bestI = i;
   best_[k] = s.cands[bestI];
   bestUs_[k] = mean[bestI];
+  // the same answer serves calls of other signatures in this bucket as long as their own candidate list holds it
+  Key generic{k.op, k.log2b, k.zc, -1};
+  if (!best_.count(generic)) { best_[generic] = s.cands[bestI]; bestUs_[generic] = mean[bestI]; }
   s.decided = true;
-  FCX_INFO(SUB_TUNING, "tuner: op %d, <=2^%d bytes -> %s with %d CTAs (%.2f us)", k.op, k.log2b, kindName(s.cands[bestI].kind),
-           s.cands[bestI].nctas, mean[bestI]);
+  FCX_INFO(SUB_TUNING, "tuner: op %d, <=2^%d bytes%s -> %s with %d CTAs (%.2f us)", k.op, k.log2b, k.zc ? " (zero-copy)" : "",
+           kindName(s.cands[bestI].kind), s.cands[bestI].nctas, mean[bestI]);
 }
 
-Plan Tuner::choose(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red, bool cast, bool *timed) {
+Plan Tuner::choose(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red, bool cast, bool *timed, bool zc,
+                   bool maySearch) {
   if (timed) *timed = false;
   // FLAGCX_FORCE_CTAS overrides the CTA count of whatever variant is chosen (for experiments)
   static const int forceCtas = (int)envInt("FORCE_CTAS", 0);
   if (forceCtas > 0) {
-    Plan p = peek(op, bytes, dt, red, cast);
+    Plan p = peek(op, bytes, dt, red, cast, zc);
     p.nctas = forceCtas;
     return p;
   }
   // Close the timing of the previous searched call.
-  if (cur_) {
+  if (cur_ && maySearch) {
     cudaEventSynchronize(ev1_);
     float ms = 0;
     if (cudaEventElapsedTime(&ms, ev0_, ev1_) == cudaSuccess) {
@@ -210,67 +262,75 @@ Plan Tuner::choose(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxR
     cur_ = nullptr;
     if (!s->decided && s->calls >= (long)nLoops_ * (long)s->cands.size()) decide(curKey_, *s);
   }
-  // Hot path: the answer for this exact (op, bytes, type, reduction, cast) was computed before.
+  const bool searching = search_ && maySearch;
+  // Hot path: the answer for this exact (op, bytes, type, reduction, cast, zero-copy) was computed before.
   const uint64_t fkey = ((uint64_t)bytes << 16) ^ ((uint64_t)op << 12) ^ ((uint64_t)dt << 8) ^ ((uint64_t)red << 4) ^ (cast ? 1u : 0u) ^
-                        ((uint64_t)bucket(bytes) << 56);
-  if (!search_) {
+                        (zc ? 2u : 0u) ^ ((uint64_t)bucket(bytes) << 56);
+  if (!searching) {
     auto f = fast_.find(fkey);
     if (f != fast_.end()) return f->second;
   }
-  std::vector<Plan> cands = candidates(op, bytes, dt, red, cast);
+  std::vector<Plan> cands = candidates(op, bytes, dt, red, cast, zc);
   auto legal = [&](const Plan &p) {
     for (auto &c : cands)
       if (c.kind == p.kind) return true;
     return false;
   };
-  if (pinned_ && legal(pin_)) return pin_;
-  Key k{(int)op, bucket(bytes)};
-  auto it = best_.find(k);
-  if (it != best_.end() && legal(it->second)) {
-    if (!search_ && !pinned_ && fast_.size() < 4096) fast_[fkey] = it->second;
-    return it->second;
+  auto remember = [&](Plan p) {
+    p = clamp(p);
+    if (!searching && !pinned_ && fast_.size() < 4096) fast_[fkey] = p;
+    return p;
+  };
+  if (pinned_ && legal(pin_)) return clamp(pin_);
+  const Key k{(int)op, bucket(bytes), zc ? 1 : 0, sigOf(dt, red, cast)};
+  for (const Key &kk : {k, Key{k.op, k.log2b, k.zc, -1}}) {
+    auto it = best_.find(kk);
+    if (it != best_.end() && legal(it->second)) return remember(it->second);
   }
   // order by the prior
   std::sort(cands.begin(), cands.end(), [&](const Plan &a, const Plan &b) {
-    return estimateUs(a, op, bytes, (int)dtypeSize(dt), caps_) < estimateUs(b, op, bytes, (int)dtypeSize(dt), caps_);
+    return estimateUs(clamp(a), op, bytes, (int)dtypeSize(dt), caps_) < estimateUs(clamp(b), op, bytes, (int)dtypeSize(dt), caps_);
   });
-  if (!search_ || cands.size() < 2) {
-    if (!search_ && !pinned_ && fast_.size() < 4096) fast_[fkey] = cands[0];
-    return cands[0];
-  }
-  Search &s = searches_[k];
+  if (!searching || cands.size() < 2) return remember(cands[0]);
+  Search &s = searches_[k];  // keyed by the full signature: every candidate in it is legal for this call
   if (s.cands.empty()) {
     s.cands = cands;
     s.sumUs.assign(cands.size(), 0.0);
     s.nSamples.assign(cands.size(), 0);
   }
-  if (s.decided) return best_[k];
+  if (s.decided) {
+    auto it = best_.find(k);
+    return clamp(it != best_.end() && legal(it->second) ? it->second : cands[0]);
+  }
   int idx = (int)(s.calls % (long)s.cands.size());
   s.calls++;
   cur_ = &s;
   curIdx_ = idx;
   curKey_ = k;
   if (timed) *timed = true;
-  return s.cands[idx];
+  return clamp(s.cands[idx]);
 }
 
-Plan Tuner::peek(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red, bool cast) const {
-  std::vector<Plan> cands = candidates(op, bytes, dt, red, cast);
+Plan Tuner::peek(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red, bool cast, bool zc) const {
+  std::vector<Plan> cands = candidates(op, bytes, dt, red, cast, zc);
   auto legal = [&](const Plan &p) {
     for (auto &c : cands)
       if (c.kind == p.kind) return true;
     return false;
   };
-  if (pinned_ && legal(pin_)) return pin_;
-  auto it = best_.find(Key{(int)op, bucket(bytes)});
-  if (it != best_.end() && legal(it->second)) return it->second;
+  if (pinned_ && legal(pin_)) return clamp(pin_);
+  const Key k{(int)op, bucket(bytes), zc ? 1 : 0, sigOf(dt, red, cast)};
+  for (const Key &kk : {k, Key{k.op, k.log2b, k.zc, -1}}) {
+    auto it = best_.find(kk);
+    if (it != best_.end() && legal(it->second)) return clamp(it->second);
+  }
   Plan best = cands[0];
   double bestUs = 1e30;
   for (auto &c : cands) {
-    double us = estimateUs(c, op, bytes, (int)dtypeSize(dt), caps_);
+    double us = estimateUs(clamp(c), op, bytes, (int)dtypeSize(dt), caps_);
     if (us < bestUs) { bestUs = us; best = c; }
   }
-  return best;
+  return clamp(best);
 }
 
 double Tuner::estimate(const Plan &p, flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt) const {
@@ -290,8 +350,10 @@ void Tuner::beginTiming(cudaStream_t st) {
 
 void Tuner::endTiming(cudaStream_t st) { cudaEventRecord(ev1_, st); }
 
+static bool isZcKind(int k) { return k == FCX_K_AR_ZC || k == FCX_K_RS_ZC || k == FCX_K_REDUCE_ZC || k == FCX_K_MOVE_ZC; }
+
 void Tuner::record(flagcxCommOp_t op, size_t bytes, const Plan &p, double us) {
-  Key k{(int)op, bucket(bytes)};
+  Key k{(int)op, bucket(bytes), isZcKind(p.kind) ? 1 : 0, -1};
   auto it = bestUs_.find(k);
   if (it == bestUs_.end() || us < it->second) {
     best_[k] = p;
@@ -314,8 +376,9 @@ flagcxResult_t Tuner::load(const std::string &path) {
       int k = kindFromName(kind);
       if (nr != caps_.nranks || k < 0) continue;
       if ((k == FCX_K_AR_NVLS || k == FCX_K_RS_NVLS || k == FCX_K_AG_NVLS) && !caps_.multicast) continue;
-      best_[{op, l2}] = {k, nctas};
-      bestUs_[{op, l2}] = us;
+      Key key{op, l2, isZcKind(k) ? 1 : 0, -1};
+      best_[key] = {k, nctas};
+      bestUs_[key] = us;
       loaded++;
     }
   }
@@ -329,14 +392,15 @@ flagcxResult_t Tuner::save(const std::string &path) const {
   FILE *f = fopen(path.c_str(), "w");
   if (!f) return flagcxSystemError;
   fprintf(f, "[\n");
-  size_t i = 0;
+  bool first = true;
   for (auto &kv : best_) {
+    if (kv.first.sig != -1) continue;  // the per-signature entries live for the process only
     auto us = bestUs_.find(kv.first);
-    fprintf(f, " {\"op\": %d, \"log2_bytes\": %d, \"nranks\": %d, \"kind\": \"%s\", \"nctas\": %d, \"us\": %.3f}%s\n", kv.first.op,
-            kv.first.log2b, caps_.nranks, kindName(kv.second.kind), kv.second.nctas, us == bestUs_.end() ? 0.0 : us->second,
-            ++i == best_.size() ? "" : ",");
+    fprintf(f, "%s {\"op\": %d, \"log2_bytes\": %d, \"nranks\": %d, \"kind\": \"%s\", \"nctas\": %d, \"us\": %.3f}", first ? "" : ",\n",
+            kv.first.op, kv.first.log2b, caps_.nranks, kindName(kv.second.kind), kv.second.nctas, us == bestUs_.end() ? 0.0 : us->second);
+    first = false;
   }
-  fprintf(f, "]\n");
+  fprintf(f, "\n]\n");
   fclose(f);
   return flagcxSuccess;
 }
@@ -344,7 +408,9 @@ flagcxResult_t Tuner::save(const std::string &path) const {
 std::string Tuner::describe() const {
   std::ostringstream os;
   for (auto &kv : best_)
-    os << "op " << kv.first.op << " <=2^" << kv.first.log2b << " B: " << kindName(kv.second.kind) << " x" << kv.second.nctas << "\n";
+    if (kv.first.sig == -1)
+      os << "op " << kv.first.op << " <=2^" << kv.first.log2b << " B" << (kv.first.zc ? " zc" : "") << ": " << kindName(kv.second.kind) << " x"
+         << kv.second.nctas << "\n";
   return os.str();
 }
 

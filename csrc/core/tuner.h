@@ -53,32 +53,49 @@ class Tuner {
   ~Tuner();
 
   // All variants that can legally run this call.
-  std::vector<Plan> candidates(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red, bool cast) const;
+  // `zc`: every rank's buffers are peer-visible (symmetric heap or registered), so the zero-copy kinds may run.
+  std::vector<Plan> candidates(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red, bool cast,
+                               bool zc = false) const;
 
   // Pick the plan for this call.  When the online search is active and the
   // returned `timed` is true the caller brackets the launch with
   // beginTiming/endTiming.
-  Plan choose(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red, bool cast, bool *timed);
+  // `maySearch` false (a stream that is being captured into a graph, for one) keeps the online search out of
+  // this call: closing a timed call synchronises on an event, which a capture forbids.
+  Plan choose(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red, bool cast, bool *timed, bool zc = false,
+              bool maySearch = true);
   void beginTiming(cudaStream_t s);
   void endTiming(cudaStream_t s);
 
   // Offline interface: record a measured time for a plan, adopt the best.
   void record(flagcxCommOp_t op, size_t bytes, const Plan &p, double us);
+  // Upper bound on the CTAs of any plan handed out (0: none).  A caller that overlaps collectives with
+  // compute kernels sets it so that a collective leaves most SMs to the compute stream.
+  void setCtaBudget(int n) { budget_ = n > 0 ? n : 0; fast_.clear(); }
+  int ctaBudget() const { return budget_; }
   flagcxResult_t load(const std::string &path);
   flagcxResult_t save(const std::string &path) const;
   std::string describe() const;  // one line per decided key
 
   bool searching() const { return search_; }
   // The plan that would run, without advancing the online search.
-  Plan peek(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red, bool cast) const;
+  Plan peek(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red, bool cast, bool zc = false) const;
   double estimate(const Plan &p, flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt) const;
   // Force one variant for every call it can legally serve; nullptr clears.
   void pin(const Plan *p);
 
  private:
+  // Decisions are kept per (op, size bucket, zero-copy or staged).  A decision is only ever applied to a call
+  // whose own candidate list holds its kind; the online search is keyed by the call's full signature `sig`
+  // (element type, reduction, cast) as well, because the candidate list depends on all of them.
   struct Key {
-    int op, log2b;
-    bool operator<(const Key &o) const { return op != o.op ? op < o.op : log2b < o.log2b; }
+    int op, log2b, zc, sig;
+    bool operator<(const Key &o) const {
+      if (op != o.op) return op < o.op;
+      if (log2b != o.log2b) return log2b < o.log2b;
+      if (zc != o.zc) return zc < o.zc;
+      return sig < o.sig;
+    }
   };
   struct Search {
     std::vector<Plan> cands;
@@ -96,6 +113,8 @@ class Tuner {
   int nLoops_ = 5;
   bool pinned_ = false;
   Plan pin_;
+  int budget_ = 0;
+  Plan clamp(Plan p) const { if (budget_ > 0 && p.nctas > budget_) p.nctas = budget_; return p; }
   // decisions of earlier calls, keyed by everything that can change the answer
   std::map<uint64_t, Plan> fast_;
   std::map<Key, Plan> best_;

@@ -30,6 +30,19 @@ flagcxResult_t flagcxCommInitRankEx(flagcxComm_t *comm, int nranks, flagcxUnique
  * Collective over the parent. */
 flagcxResult_t flagcxCommSplit(flagcxComm_t comm, int color, int key, flagcxComm_t *newcomm);
 
+/* The same, with the size of the new communicator's symmetric heap given: bytes of one staging half (two are
+ * kept) and bytes of the flagcxMemAlloc area; 0 keeps the default of a split (a quarter of FLAGCX_STAGE_BYTES /
+ * FLAGCX_HEAP_USER_BYTES).  A trainer that keeps its gradients in the heap sizes its communicator with this. */
+flagcxResult_t flagcxCommSplitSized(flagcxComm_t comm, int color, int key, size_t stageBytes, size_t userBytes,
+                                    flagcxComm_t *newcomm);
+
+/* Heap memory whose owner may outlive the communicator (a framework tensor built on flagcxMemAlloc memory):
+ * Retain before handing the memory out, Release(ptr) instead of flagcxMemFree when the owner dies.  A
+ * communicator destroyed while such memory is outstanding stops serving calls at once but keeps its heap
+ * mapped until the last Release, so the memory never dangles. */
+flagcxResult_t flagcxCommHeapRetain(flagcxComm_t comm);
+flagcxResult_t flagcxCommHeapRelease(flagcxComm_t comm, void *ptr);
+
 /* Per-communicator statistics. */
 typedef struct {
   uint64_t calls[flagcxNumCommOps];
@@ -62,9 +75,17 @@ flagcxResult_t flagcxTunerSave(flagcxComm_t comm, const char *path);
 flagcxResult_t flagcxTunerLoad(flagcxComm_t comm, const char *path);
 /* Force the variant of subsequent calls ("ar_twoshot", 32); kind NULL clears. */
 flagcxResult_t flagcxTunerPin(flagcxComm_t comm, const char *kind, int nctas);
+/* Upper bound on the CTAs any collective of this communicator launches (0 lifts it).  For callers that run
+ * collectives beside compute kernels (gradient buckets during the backward pass): a collective that takes
+ * every SM stalls the kernels it was meant to overlap.  Every rank must set the same value. */
+flagcxResult_t flagcxCommSetCtaBudget(flagcxComm_t comm, int maxCtas);
 /* Writes a NUL-terminated description of the plan that would run. */
 flagcxResult_t flagcxTunerQuery(flagcxComm_t comm, flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red,
                                 char *kindOut, size_t kindOutBytes, int *nctas, double *estimateUs);
+
+/* The same for a call whose buffers are peer-visible on every rank (zeroCopy != 0: symmetric heap or registered). */
+flagcxResult_t flagcxTunerQueryEx(flagcxComm_t comm, flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red,
+                                  int zeroCopy, char *kindOut, size_t kindOutBytes, int *nctas, double *estimateUs);
 
 /* The plan the cost-model prior picks for a machine of `nranks` GPUs; needs neither a communicator nor a GPU. */
 flagcxResult_t flagcxTunerPriorPlan(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, int nranks, int multicast, char *kindOut,
@@ -80,9 +101,15 @@ flagcxResult_t flagcxCommWaitTest(flagcxComm_t comm, flagcxStream_t stream);
 /* Details of the last device-side give-up: code 0 none / 1 time-out / 2 abort. */
 flagcxResult_t flagcxCommGetDeviceError(flagcxComm_t comm, int *code, int *peer, int *where, unsigned long long *expected,
                                         unsigned long long *seen);
-/* Clear a recorded device error so that the communicator can be used again
- * (only meaningful when all ranks do so at the same point). */
+/* Clear a recorded device error.  Local, not collective: enough when the wait that gave up belonged to no
+ * collective (a device-API wait, flagcxCommWaitTest).  After a COLLECTIVE gave up on any rank the ranks may
+ * disagree on how many collectives completed; use flagcxCommRecover then, or destroy the communicator. */
 flagcxResult_t flagcxCommClearError(flagcxComm_t comm);
+/* Collective over all ranks of the communicator (host side, over the bootstrap network): drain the device,
+ * agree on a sequence number above anything used so far, reset flags, counters, mailboxes and point-to-point
+ * state, clear the error.  Afterwards the communicator serves collectives again.  Every rank must call it,
+ * with nothing of this communicator in flight. */
+flagcxResult_t flagcxCommRecover(flagcxComm_t comm);
 
 /* Single-GPU emulation of an n-rank collective (protocol tests without
  * NVLink): runs `nranks` emulated ranks inside one cooperative launch.

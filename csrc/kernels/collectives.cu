@@ -21,6 +21,7 @@
 // (fcxCollEmuKernel), which is how the protocol is tested without NVLink.
 #include "prims.cuh"
 #include "launch.h"
+#include "dispatch.h"
 
 #include <cuda_runtime.h>
 
@@ -30,73 +31,6 @@ __device__ __forceinline__ char *stagePtr(const FcxDevComm &dc, int r, uint64_t 
   return dc.heap[r] + FCX_OFF_STAGE + (size_t)(seq & 1) * dc.stageBytes;
 }
 
-// ---------------------------------------------------------------- plain copies
-
-// Copy `bytes` between two buffers in units of `unitBytes` (a multiple of 16).
-// Unit u always belongs to thread (u mod gstride), whatever the alignment, so
-// the same thread that wrote a unit into a slot is the one that reads it back
-// on the other side of a barrier.  When both pointers are 16-byte aligned the
-// loop keeps four independent 16-byte loads in flight per thread.
-__device__ __forceinline__ void copyUnits(char *dst, const char *src, size_t bytes, int unitBytes, size_t gtid,
-                                          size_t gstride) {
-  const size_t nfull = bytes / unitBytes;
-  const int tail = (int)(bytes - nfull * unitBytes);
-  uintptr_t both = (uintptr_t)dst | (uintptr_t)src;
-  if ((both & 15u) == 0) {
-    size_t u = gtid;
-    if (unitBytes == 16) {
-      // eight independent 16-byte loads in flight per thread, then eight stores
-      for (; u + 7 * gstride < nfull; u += 8 * gstride) {
-        uint4 v[8];
-#pragma unroll
-        for (int i = 0; i < 8; i++) v[i] = ld16(src + (u + i * gstride) * 16);
-#pragma unroll
-        for (int i = 0; i < 8; i++) st16(dst + (u + i * gstride) * 16, v[i]);
-      }
-      for (; u + 3 * gstride < nfull; u += 4 * gstride) {
-        uint4 v0 = ld16(src + u * 16), v1 = ld16(src + (u + gstride) * 16), v2 = ld16(src + (u + 2 * gstride) * 16),
-              v3 = ld16(src + (u + 3 * gstride) * 16);
-        st16(dst + u * 16, v0);
-        st16(dst + (u + gstride) * 16, v1);
-        st16(dst + (u + 2 * gstride) * 16, v2);
-        st16(dst + (u + 3 * gstride) * 16, v3);
-      }
-      for (; u < nfull; u += gstride) st16(dst + u * 16, ld16(src + u * 16));
-    } else {
-      const int lines = unitBytes / 16;
-      for (; u < nfull; u += gstride) {
-        uint4 v[4];
-        const char *s = src + u * unitBytes;
-        char *d = dst + u * unitBytes;
-        for (int l0 = 0; l0 < lines; l0 += 4) {
-#pragma unroll
-          for (int l = 0; l < 4; l++)
-            if (l0 + l < lines) v[l] = ld16(s + (l0 + l) * 16);
-#pragma unroll
-          for (int l = 0; l < 4; l++)
-            if (l0 + l < lines) st16(d + (l0 + l) * 16, v[l]);
-        }
-      }
-    }
-  } else if ((both & 3u) == 0 && (bytes & 3u) == 0) {
-    for (size_t u = gtid; u < nfull; u += gstride) {
-      const uint32_t *s = (const uint32_t *)(src + u * unitBytes);
-      uint32_t *d = (uint32_t *)(dst + u * unitBytes);
-      for (int i = 0; i < unitBytes / 4; i++) d[i] = s[i];
-    }
-  } else {
-    for (size_t u = gtid; u < nfull; u += gstride) {
-      const char *s = src + u * unitBytes;
-      char *d = dst + u * unitBytes;
-      for (int i = 0; i < unitBytes; i++) d[i] = s[i];
-    }
-  }
-  if (tail && (nfull % gstride) == gtid) {
-    const char *s = src + nfull * unitBytes;
-    char *d = dst + nfull * unitBytes;
-    for (int i = 0; i < tail; i++) d[i] = s[i];
-  }
-}
 __device__ __forceinline__ void copyToSlot(char *slot, const char *user, size_t bytes, int unitBytes, size_t gtid,
                                            size_t gstride) {
   copyUnits(slot, user, bytes, unitBytes, gtid, gstride);
@@ -342,24 +276,6 @@ __device__ __forceinline__ void reduceUnits(const FcxDevComm &dc, const FcxCollA
     gather(u, acc);
     emit(u, acc);
   }
-}
-
-// ---------------------------------------------------------------- NVLS helpers
-
-template <typename T>
-__device__ __forceinline__ uint4 mmFinish(uint4 r, int op, int nranks, float scale) {
-  // avg and scale need arithmetic on the switch's result
-  if (op != 4 && scale == 1.0f) return r;
-  using Acc = typename Elem<T>::Acc;
-  constexpr int G = 16 / (int)sizeof(T);
-  union { uint4 v; T t[G]; } w;
-  w.v = r;
-  Acc x[G];
-#pragma unroll
-  for (int i = 0; i < G; i++) x[i] = finish<Acc>(Elem<T>::up(w.t[i]), op, nranks, scale);
-  uint4 o;
-  packUnit<T, G>(x, &o);
-  return o;
 }
 
 // ---------------------------------------------------------------- the body
@@ -1143,47 +1059,41 @@ cudaError_t launchTypedEmu(const FcxDevComm *dcs, const FcxCollArgs *as, int nra
                                      params, 0, s);
 }
 
-// dtype codes follow flagcxDataType_t
-#define FCX_DISPATCH_SAME(DT, CALL)                                         \
-  switch (DT) {                                                             \
-    case 0: return CALL(int8_t, int8_t);                                    \
-    case 1: return CALL(uint8_t, uint8_t);                                  \
-    case 2: return CALL(int32_t, int32_t);                                  \
-    case 3: return CALL(uint32_t, uint32_t);                                \
-    case 4: return CALL(long long, long long);                              \
-    case 5: return CALL(unsigned long long, unsigned long long);            \
-    case 6: return CALL(__half, __half);                                    \
-    case 7: return CALL(float, float);                                      \
-    case 8: return CALL(double, double);                                    \
-    case 9: return CALL(__nv_bfloat16, __nv_bfloat16);                      \
-    case 10: return CALL(F8E4, F8E4);                                       \
-    case 11: return CALL(F8E5, F8E5);                                       \
-    default: return cudaErrorInvalidValue;                                  \
-  }
-
 }  // namespace
 
 // kinds that move bytes without looking at the element type
-static bool isMoveKind(int k) { return k >= FCX_K_AG && k != FCX_K_REDUCE && k != FCX_K_RS_LL && k != FCX_K_REDUCE_LL; }
+static bool isMoveKind(int k) {
+  return (k >= FCX_K_AG && k <= FCX_K_MOVE_LL && k != FCX_K_REDUCE) || k == FCX_K_MOVE_ZC;
+}
+static bool isZcReduceKind(int k) { return k == FCX_K_AR_ZC || k == FCX_K_RS_ZC || k == FCX_K_REDUCE_ZC; }
+
+// A kind that cannot serve the call's element types or reduction must never be launched: its body would
+// be empty and recv would silently keep its old contents.
+static bool kindServes(const FcxCollArgs *a) {
+  const bool same = a->outDtype == a->dtype && a->scale == 1.0f;
+  switch (a->kind) {
+    case FCX_K_AR_LL: case FCX_K_RS_LL: case FCX_K_REDUCE_LL: return same;
+    case FCX_K_AR_NVLS: case FCX_K_RS_NVLS: {
+      if (a->outDtype != a->dtype) return false;
+      if (a->dtype == 7) return a->redop == 0 || a->redop == 4;               // fp32: the switch only adds
+      if (a->dtype == 6 || a->dtype == 9) return a->redop != 1;               // fp16 / bf16: add, min, max
+      return false;
+    }
+    default: return true;
+  }
+}
 
 extern "C" cudaError_t fcxLaunchColl(const FcxDevComm *dc, const FcxCollArgs *a, int nctas, cudaStream_t s) {
+  if (a->kind < 0 || a->kind >= FCX_K_NUM || !kindServes(a)) return cudaErrorInvalidValue;
+  if (a->kind == FCX_K_MOVE_ZC || isZcReduceKind(a->kind)) return fcxLaunchZc(dc, a, nctas, s);
   if (isMoveKind(a->kind)) {
     fcxMoveKernel<<<nctas, FCX_THREADS, 0, s>>>(*dc, *a);
     return cudaGetLastError();
   }
   if (a->kind == FCX_K_BARRIER) return launchTyped<uint8_t, uint8_t>(*dc, *a, 1, s);
 #define CALL(TI, TO) launchTyped<TI, TO>(*dc, *a, nctas, s)
-  if (a->outDtype == a->dtype) { FCX_DISPATCH_SAME(a->dtype, CALL) }
-  // fused cast: wide input, narrow output
-  if (a->dtype == 7 && a->outDtype == 9) return CALL(float, __nv_bfloat16);
-  if (a->dtype == 7 && a->outDtype == 6) return CALL(float, __half);
-  if (a->dtype == 7 && a->outDtype == 10) return CALL(float, F8E4);
-  if (a->dtype == 9 && a->outDtype == 10) return CALL(__nv_bfloat16, F8E4);
-  if (a->dtype == 9 && a->outDtype == 11) return CALL(__nv_bfloat16, F8E5);
-  if (a->dtype == 9 && a->outDtype == 7) return CALL(__nv_bfloat16, float);
-  if (a->dtype == 10 && a->outDtype == 9) return CALL(F8E4, __nv_bfloat16);
+  FCX_DISPATCH_ALL(a, CALL);
 #undef CALL
-  return cudaErrorInvalidValue;
 }
 
 extern "C" cudaError_t fcxLaunchP2p(const FcxDevComm *dc, const FcxP2pArgs *g, cudaStream_t s) {
@@ -1200,22 +1110,15 @@ extern "C" cudaError_t fcxLaunchWaitTest(const FcxDevComm *dc, uint64_t want, cu
 extern "C" cudaError_t fcxLaunchCollEmu(const FcxDevComm *dcs, const FcxCollArgs *as, const FcxCollArgs *hostArgs0,
                                         int nranks, int nctas, cudaStream_t s) {
   const FcxCollArgs *a = hostArgs0;
-  if (isMoveKind(a->kind)) {
-    void *params[] = {(void *)&dcs, (void *)&as, (void *)&nctas};
+  if (a->kind < 0 || a->kind >= FCX_K_NUM || !kindServes(a)) return cudaErrorInvalidValue;
+  void *params[] = {(void *)&dcs, (void *)&as, (void *)&nctas};
+  if (a->kind == FCX_K_MOVE_ZC || isZcReduceKind(a->kind)) return fcxLaunchZcEmu(dcs, as, hostArgs0, nranks, nctas, s);
+  if (isMoveKind(a->kind))
     return cudaLaunchCooperativeKernel((const void *)fcxMoveEmuKernel, dim3(nranks * nctas), dim3(FCX_THREADS), params, 0, s);
-  }
+  if (a->kind == FCX_K_BARRIER) return launchTypedEmu<uint8_t, uint8_t>(dcs, as, nranks, nctas, s);
 #define CALL(TI, TO) launchTypedEmu<TI, TO>(dcs, as, nranks, nctas, s)
-  if (a->kind == FCX_K_BARRIER) return CALL(uint8_t, uint8_t);
-  if (a->outDtype == a->dtype) { FCX_DISPATCH_SAME(a->dtype, CALL) }
-  if (a->dtype == 7 && a->outDtype == 9) return CALL(float, __nv_bfloat16);
-  if (a->dtype == 7 && a->outDtype == 6) return CALL(float, __half);
-  if (a->dtype == 7 && a->outDtype == 10) return CALL(float, F8E4);
-  if (a->dtype == 9 && a->outDtype == 10) return CALL(__nv_bfloat16, F8E4);
-  if (a->dtype == 9 && a->outDtype == 11) return CALL(__nv_bfloat16, F8E5);
-  if (a->dtype == 9 && a->outDtype == 7) return CALL(__nv_bfloat16, float);
-  if (a->dtype == 10 && a->outDtype == 9) return CALL(F8E4, __nv_bfloat16);
+  FCX_DISPATCH_ALL(a, CALL);
 #undef CALL
-  return cudaErrorInvalidValue;
 }
 
 extern "C" cudaError_t fcxLaunchP2pEmu(const FcxDevComm *dcs, const FcxP2pArgs *gs, int nranks, int ctasPerRank,

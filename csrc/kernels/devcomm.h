@@ -20,6 +20,12 @@
 #define FCX_MAX_SEGS 64     // registered user buffers per communicator
 #define FCX_MAX_GROUP_OPS 64
 
+// Where a user buffer lives, as seen by the peers.
+#define FCX_SEG_NONE (-1)     // not peer-visible
+#define FCX_SEG_HEAP 0        // inside the symmetric heap: peer p reaches it at heap[p] + offset
+#define FCX_SEG_ABS 0x7fff    // the offset is an address every rank can use as it is (single-GPU emulation)
+                              // 1 .. FCX_MAX_SEGS-1: registered segment, peer p reaches it at segs[seg][p] + offset
+
 // ---- control block layout (byte offsets inside a heap) -------------------
 #define FCX_OFF_FLAGS 0                      // u64 [FCX_MAX_CTAS][FCX_MAX_RANKS]
 #define FCX_OFF_DONE (8 * 1024)              // u64 [FCX_MAX_RANKS]: last finished collective of each peer
@@ -102,6 +108,13 @@ enum FcxKind : int {
   FCX_K_MOVE_LL,      // small all-gather / broadcast / gather / scatter / all-to-all: flags travel inside the data lines
   FCX_K_RS_LL,        // small reduce-scatter, same idea
   FCX_K_REDUCE_LL,    // small reduce to the root, same idea
+  // Zero-copy kinds: every rank's buffer is peer-visible (symmetric heap or a registered segment), so the
+  // kernel reads and writes the peers' user buffers directly and nothing is staged.  When the offsets agree on
+  // all ranks and the box has a multicast alias, the reducing kinds go through the switch (multimem).
+  FCX_K_AR_ZC,        // owner of a slice reduces it out of all send buffers and stores it into all recv buffers
+  FCX_K_RS_ZC,        // every rank reduces its piece out of all send buffers into its own recv buffer
+  FCX_K_REDUCE_ZC,    // the root reduces the whole vector out of all send buffers
+  FCX_K_MOVE_ZC,      // all-gather / broadcast / gather / scatter / all-to-all(v) straight between user buffers
   FCX_K_NUM
 };
 
@@ -119,8 +132,10 @@ struct FcxCollArgs {
   size_t count;          // elements of the piece handled by this launch (per-rank piece for AG/RS/A2A/gather/scatter)
   size_t sendStride;     // elements between consecutive rank pieces in the user send buffer
   size_t recvStride;     // same for the receive buffer
-  // zero-copy description: heap offsets of send/recv when they live in the heap, else ~0
+  // zero-copy description: segment (FCX_SEG_*) and byte offset inside it of send/recv when they are
+  // peer-visible; segment FCX_SEG_NONE otherwise
   uint64_t sendHeapOff, recvHeapOff;
+  int sendSeg, recvSeg;
   // all-to-all-v tables (elements), valid for FCX_K_A2AV
   uint64_t scounts[FCX_MAX_RANKS], sdispls[FCX_MAX_RANKS], rcounts[FCX_MAX_RANKS], rdispls[FCX_MAX_RANKS];
 };

@@ -10,6 +10,10 @@
 extern "C" {
 #endif
 cudaError_t fcxLaunchColl(const FcxDevComm *dc, const FcxCollArgs *a, int nctas, cudaStream_t s);
+// zero-copy kinds (zerocopy.cu); fcxLaunchColl forwards to these
+cudaError_t fcxLaunchZc(const FcxDevComm *dc, const FcxCollArgs *a, int nctas, cudaStream_t s);
+cudaError_t fcxLaunchZcEmu(const FcxDevComm *dcs, const FcxCollArgs *as, const FcxCollArgs *hostArgs0, int nranks, int nctas,
+                           cudaStream_t s);
 cudaError_t fcxLaunchP2p(const FcxDevComm *dc, const FcxP2pArgs *g, cudaStream_t s);
 cudaError_t fcxLaunchWaitTest(const FcxDevComm *dc, uint64_t want, cudaStream_t s);
 // Single-GPU emulation of `nranks` ranks in one cooperative launch.  dcs, as

@@ -115,7 +115,13 @@ __device__ __forceinline__ bool ctaBarrier(const FcxDevComm &dc, int cta, uint64
   return __syncthreads_and(ok);
 }
 
-__device__ __forceinline__ uint64_t barrierValue(uint64_t seq, unsigned phase) { return (seq << 16) | phase; }
+// Flag value of phase `phase` of collective `seq`.  The phase field is 24 bits wide: the pipelined kinds count one
+// phase per sub-chunk, and a launch never holds more than stageBytes / 16 KiB sub-chunks (the host caps the
+// staging area at 2^24 sub-chunks of the smallest size), so a phase can never carry into the sequence number.
+#define FCX_PHASE_BITS 24
+__device__ __forceinline__ uint64_t barrierValue(uint64_t seq, unsigned phase) {
+  return (seq << FCX_PHASE_BITS) | (uint64_t)(phase & ((1u << FCX_PHASE_BITS) - 1u));
+}
 
 // The sequence number of the collective that is starting.  It lives in device
 // memory (not in the launch arguments) so that a captured CUDA graph can be
@@ -315,5 +321,92 @@ __device__ __forceinline__ void mmStore(void *mc, uint4 v) {
   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y),
                "r"(v.z), "r"(v.w) : "memory");
 }
+
+// ---------------------------------------------------------------- plain copies
+
+// Copy `bytes` between two buffers in units of `unitBytes` (a multiple of 16).
+// Unit u always belongs to thread (u mod gstride), whatever the alignment, so
+// the same thread that wrote a unit into a slot is the one that reads it back
+// on the other side of a barrier.  When both pointers are 16-byte aligned the
+// loop keeps four independent 16-byte loads in flight per thread.
+__device__ __forceinline__ void copyUnits(char *dst, const char *src, size_t bytes, int unitBytes, size_t gtid,
+                                          size_t gstride) {
+  const size_t nfull = bytes / unitBytes;
+  const int tail = (int)(bytes - nfull * unitBytes);
+  uintptr_t both = (uintptr_t)dst | (uintptr_t)src;
+  if ((both & 15u) == 0) {
+    size_t u = gtid;
+    if (unitBytes == 16) {
+      // eight independent 16-byte loads in flight per thread, then eight stores
+      for (; u + 7 * gstride < nfull; u += 8 * gstride) {
+        uint4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = ld16(src + (u + i * gstride) * 16);
+#pragma unroll
+        for (int i = 0; i < 8; i++) st16(dst + (u + i * gstride) * 16, v[i]);
+      }
+      for (; u + 3 * gstride < nfull; u += 4 * gstride) {
+        uint4 v0 = ld16(src + u * 16), v1 = ld16(src + (u + gstride) * 16), v2 = ld16(src + (u + 2 * gstride) * 16),
+              v3 = ld16(src + (u + 3 * gstride) * 16);
+        st16(dst + u * 16, v0);
+        st16(dst + (u + gstride) * 16, v1);
+        st16(dst + (u + 2 * gstride) * 16, v2);
+        st16(dst + (u + 3 * gstride) * 16, v3);
+      }
+      for (; u < nfull; u += gstride) st16(dst + u * 16, ld16(src + u * 16));
+    } else {
+      const int lines = unitBytes / 16;
+      for (; u < nfull; u += gstride) {
+        uint4 v[4];
+        const char *s = src + u * unitBytes;
+        char *d = dst + u * unitBytes;
+        for (int l0 = 0; l0 < lines; l0 += 4) {
+#pragma unroll
+          for (int l = 0; l < 4; l++)
+            if (l0 + l < lines) v[l] = ld16(s + (l0 + l) * 16);
+#pragma unroll
+          for (int l = 0; l < 4; l++)
+            if (l0 + l < lines) st16(d + (l0 + l) * 16, v[l]);
+        }
+      }
+    }
+  } else if ((both & 3u) == 0 && (bytes & 3u) == 0) {
+    for (size_t u = gtid; u < nfull; u += gstride) {
+      const uint32_t *s = (const uint32_t *)(src + u * unitBytes);
+      uint32_t *d = (uint32_t *)(dst + u * unitBytes);
+      for (int i = 0; i < unitBytes / 4; i++) d[i] = s[i];
+    }
+  } else {
+    for (size_t u = gtid; u < nfull; u += gstride) {
+      const char *s = src + u * unitBytes;
+      char *d = dst + u * unitBytes;
+      for (int i = 0; i < unitBytes; i++) d[i] = s[i];
+    }
+  }
+  if (tail && (nfull % gstride) == gtid) {
+    const char *s = src + nfull * unitBytes;
+    char *d = dst + nfull * unitBytes;
+    for (int i = 0; i < tail; i++) d[i] = s[i];
+  }
+}
+
+// ---------------------------------------------------------------- NVLS helpers
+
+template <typename T>
+__device__ __forceinline__ uint4 mmFinish(uint4 r, int op, int nranks, float scale) {
+  // avg and scale need arithmetic on the switch's result
+  if (op != 4 && scale == 1.0f) return r;
+  using Acc = typename Elem<T>::Acc;
+  constexpr int G = 16 / (int)sizeof(T);
+  union { uint4 v; T t[G]; } w;
+  w.v = r;
+  Acc x[G];
+#pragma unroll
+  for (int i = 0; i < G; i++) x[i] = finish<Acc>(Elem<T>::up(w.t[i]), op, nranks, scale);
+  uint4 o;
+  packUnit<T, G>(x, &o);
+  return o;
+}
+
 
 }  // namespace fcxdev

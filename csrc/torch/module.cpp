@@ -159,7 +159,9 @@ static at::Tensor heapTensor(uint64_t comm, std::vector<int64_t> sizes, at::Scal
   FCX_OK(flagcxMemAlloc(&p, std::max<size_t>(bytes, 16), c));
   int dev = 0;
   flagcxCommGetDeviceNumber(c, &dev);
-  return at::from_blob(p, sizes, [c](void *q) { flagcxMemFree(q, c); },
+  // the tensor may outlive the communicator: it holds a reference that keeps the heap mapped until it dies
+  FCX_OK(flagcxCommHeapRetain(c));
+  return at::from_blob(p, sizes, [c](void *q) { flagcxCommHeapRelease(c, q); },
                        at::TensorOptions().dtype(dtype).device(at::Device(at::kCUDA, (c10::DeviceIndex)dev)));
 }
 
@@ -201,6 +203,27 @@ static void commBroadcast(uint64_t comm, at::Tensor &t, int64_t root) {
   StreamLayout st{cur()};
   FCX_OK(flagcxBroadcast(t.data_ptr(), t.data_ptr(), t.numel(), dtypeOf(t), (int)root, (flagcxComm_t)(uintptr_t)comm, (flagcxStream_t)&st));
 }
+// A communicator of its own for a component that launches collectives on its own stream (a communicator
+// serves one stream at a time).  Collective over `comm`; destroyed with it unless comm_destroy is called first.
+static uint64_t commSplit(uint64_t comm, int64_t color, int64_t key, int64_t stageBytes, int64_t userBytes) {
+  flagcxComm_t child = nullptr;
+  FCX_OK(flagcxCommSplitSized((flagcxComm_t)(uintptr_t)comm, (int)color, (int)key, (size_t)stageBytes, (size_t)userBytes, &child));
+  return (uint64_t)(uintptr_t)child;
+}
+static void commDestroy(uint64_t comm) { FCX_OK(flagcxCommDestroy((flagcxComm_t)(uintptr_t)comm)); }
+static void commSetCtaBudget(uint64_t comm, int64_t n) { FCX_OK(flagcxCommSetCtaBudget((flagcxComm_t)(uintptr_t)comm, (int)n)); }
+static void commPin(uint64_t comm, const std::string &kind, int64_t nctas) {
+  FCX_OK(flagcxTunerPin((flagcxComm_t)(uintptr_t)comm, kind.empty() ? nullptr : kind.c_str(), (int)nctas));
+}
+static std::pair<std::string, int> commQuery(uint64_t comm, int64_t op, int64_t bytes, const at::Tensor &like, bool zeroCopy) {
+  char kind[64] = {0};
+  int nctas = 0;
+  double est = 0;
+  FCX_OK(flagcxTunerQueryEx((flagcxComm_t)(uintptr_t)comm, (flagcxCommOp_t)op, (size_t)bytes, dtypeOf(like), flagcxSum, zeroCopy ? 1 : 0,
+                            kind, sizeof kind, &nctas, &est));
+  return {std::string(kind), nctas};
+}
+
 static py::dict commCounters(uint64_t comm) {
   flagcxCommCounters cc;
   FCX_OK(flagcxCommGetCounters((flagcxComm_t)(uintptr_t)comm, &cc));
@@ -237,4 +260,10 @@ PYBIND11_MODULE(_flagcx_torch, m) {
   m.def("comm_all_to_all_v", &fcxt::commAlltoAllv);
   m.def("comm_broadcast", &fcxt::commBroadcast);
   m.def("comm_counters", &fcxt::commCounters);
+  m.def("comm_split", &fcxt::commSplit, py::arg("comm"), py::arg("color"), py::arg("key"), py::arg("stage_bytes") = 0,
+        py::arg("user_bytes") = 0);
+  m.def("comm_destroy", &fcxt::commDestroy);
+  m.def("comm_set_cta_budget", &fcxt::commSetCtaBudget);
+  m.def("comm_pin", &fcxt::commPin, py::arg("comm"), py::arg("kind"), py::arg("nctas") = 16);
+  m.def("comm_query", &fcxt::commQuery, py::arg("comm"), py::arg("op"), py::arg("bytes"), py::arg("like"), py::arg("zero_copy") = false);
 }

@@ -10,12 +10,23 @@ CUDA graph and replayed, which removes the per-kernel launch cost of an
 eager step.  The collective kernels keep their sequence numbers in device
 memory, which is what makes them replayable.
 
+The engine owns a communicator of its own (split off the process group's), for
+two reasons: a communicator serves one stream at a time, and this one launches
+on the engine's side stream while the process group's may be busy with the
+caller's collectives; and its heap is sized for the gradients.  Gradients and
+parameters live in that communicator's symmetric heap, so each bucket is
+reduced in place through the zero-copy kernel (in-switch reduction, nothing
+staged) with a small CTA budget (``FLAGCX_DDP_CTAS``, default 16) that leaves
+the SMs to the backward pass it overlaps.
+
 This is the framework's counterpart of running ``DistributedDataParallel``
 over the reference's process-group backend (plugin/torch/flagcx/src/backend_flagcx.cpp:505-532);
-that route is supported too (``torch_ddp=True``) and is what the c10d backend tests exercise.
+stock ``DistributedDataParallel`` over this library's backend works as well
+(``bench.py --impl ours-c10d`` and the c10d backend tests run it).
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import List, Optional
 
@@ -45,20 +56,25 @@ class DataParallelTrainer:
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.native = flagcx_b200.native()
         self.comm = 0
-        if self.world > 1:
-            self.comm = flagcx_b200.get_comm_handle(group, self.device)
         self.lr, self.betas, self.eps, self.wd = lr, betas, eps, weight_decay
         self.step_no = 0
         self.launches_per_step = 0
         self.step_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
 
-        # ---- flat buffers
-        self.flat_params, self.specs = flatten_parameters(model, torch.bfloat16, self.device)
-        n = self.flat_params.numel()
-        if self.comm:
+        # ---- flat buffers (in the engine's own symmetric heap when there is anything to exchange)
+        n = sum((p.numel() + 127) // 128 * 128 for p in model.parameters())
+        if self.world > 1:
+            parent = flagcx_b200.get_comm_handle(group, self.device)
+            heap_bytes = 2 * (2 * n) + (64 << 20)
+            self.comm = self.native.comm_split(parent, 0, self.rank, stage_bytes=64 << 20, user_bytes=heap_bytes)
+            self.cta_budget = int(os.environ.get("FLAGCX_DDP_CTAS", "16"))
+            self.native.comm_set_cta_budget(self.comm, self.cta_budget)
+            buf = self.native.heap_tensor(self.comm, [n], torch.bfloat16)
+            self.flat_params, self.specs = flatten_parameters(model, torch.bfloat16, self.device, buffer=buf)
             self.flat_grads = self.native.heap_tensor(self.comm, [n], torch.bfloat16)
             self.flat_grads.zero_()
         else:
+            self.flat_params, self.specs = flatten_parameters(model, torch.bfloat16, self.device)
             self.flat_grads = torch.zeros(n, dtype=torch.bfloat16, device=self.device)
         self.master = self.flat_params.float()
         self.m = torch.zeros_like(self.master)
@@ -94,6 +110,8 @@ class DataParallelTrainer:
             self.ready_event = torch.cuda.Event()
             self.done_event = torch.cuda.Event()
 
+        self.snapshot_grads = False
+        self.grad_snapshot = None
         self.use_graph = use_graph
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.static_tokens = None
@@ -129,6 +147,8 @@ class DataParallelTrainer:
         if self.world > 1:
             self.done_event.record(self.comm_stream)
             torch.cuda.current_stream(self.device).wait_event(self.done_event)
+        if self.snapshot_grads:  # for tests: the averaged gradients as the optimizer is about to see them
+            self.grad_snapshot = self.flat_grads.clone()
         self.step_dev.add_(1)
         fused_adamw_step(self.master, self.flat_params, self.flat_grads, self.m, self.v, lr=self.lr, betas=self.betas,
                          eps=self.eps, weight_decay=self.wd, step=self.step_no + 1, zero_grad=True, step_dev=self.step_dev)

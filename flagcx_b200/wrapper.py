@@ -198,6 +198,12 @@ _SIGNATURES = {
     "flagcxAllReduceCast": (_R, [buffer_type, buffer_type, _sz, flagcxDataType_t, flagcxDataType_t, ctypes.c_float, flagcxRedOp_t,
                                  flagcxComm_t, flagcxStream_t]),
     "flagcxCommSplit": (_R, [flagcxComm_t, ctypes.c_int, ctypes.c_int, ctypes.POINTER(flagcxComm_t)]),
+    "flagcxCommSplitSized": (_R, [flagcxComm_t, ctypes.c_int, ctypes.c_int, _sz, _sz, ctypes.POINTER(flagcxComm_t)]),
+    "flagcxCommSetCtaBudget": (_R, [flagcxComm_t, ctypes.c_int]),
+    "flagcxCommHeapRetain": (_R, [flagcxComm_t]),
+    "flagcxCommHeapRelease": (_R, [flagcxComm_t, _vp]),
+    "flagcxTunerQueryEx": (_R, [flagcxComm_t, ctypes.c_int, _sz, flagcxDataType_t, flagcxRedOp_t, ctypes.c_int, ctypes.c_char_p, _sz,
+                                ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_double)]),
     "flagcxCommGetCounters": (_R, [flagcxComm_t, ctypes.POINTER(flagcxCommCounters)]),
     "flagcxCommGetClusterInfo": (_R, [flagcxComm_t, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int),
                                       ctypes.POINTER(ctypes.c_int)]),
@@ -209,6 +215,7 @@ _SIGNATURES = {
                                       ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_ulonglong),
                                       ctypes.POINTER(ctypes.c_ulonglong)]),
     "flagcxCommClearError": (_R, [flagcxComm_t]),
+    "flagcxCommRecover": (_R, [flagcxComm_t]),
     "flagcxTunerRecord": (_R, [flagcxComm_t, ctypes.c_int, _sz, ctypes.c_char_p, ctypes.c_int, ctypes.c_double]),
     "flagcxTunerSave": (_R, [flagcxComm_t, ctypes.c_char_p]),
     "flagcxTunerLoad": (_R, [flagcxComm_t, ctypes.c_char_p]),
@@ -415,6 +422,16 @@ class FLAGCXLibrary:
         self.call("flagcxCommSplit", comm, color, key, ctypes.byref(out))
         return out if out.value else None
 
+    def flagcxCommSplitSized(self, comm, color: int, key: int, stage_bytes: int = 0, user_bytes: int = 0):
+        """Split with the new communicator's heap sized explicitly (bytes of a staging half, bytes for flagcxMemAlloc)."""
+        out = flagcxComm_t()
+        self.call("flagcxCommSplitSized", comm, color, key, stage_bytes, user_bytes, ctypes.byref(out))
+        return out if out.value else None
+
+    def set_cta_budget(self, comm, max_ctas: int):
+        """Cap the CTAs of every collective of `comm` (0 lifts the cap); the same value on every rank."""
+        self.call("flagcxCommSetCtaBudget", comm, max_ctas)
+
     def counters(self, comm) -> dict:
         c = flagcxCommCounters()
         self.call("flagcxCommGetCounters", comm, ctypes.byref(c))
@@ -432,6 +449,12 @@ class FLAGCXLibrary:
         buf = ctypes.create_string_buffer(64)
         nctas, us = ctypes.c_int(), ctypes.c_double()
         self.call("flagcxTunerQuery", comm, op, nbytes, dtype, red, buf, 64, ctypes.byref(nctas), ctypes.byref(us))
+        return buf.value.decode(), nctas.value, us.value
+
+    def tuner_query_ex(self, comm, op: int, nbytes: int, dtype: int, red: int = 0, zero_copy: bool = False):
+        buf = ctypes.create_string_buffer(64)
+        nctas, us = ctypes.c_int(), ctypes.c_double()
+        self.call("flagcxTunerQueryEx", comm, op, nbytes, dtype, red, int(zero_copy), buf, 64, ctypes.byref(nctas), ctypes.byref(us))
         return buf.value.decode(), nctas.value, us.value
 
     def tuner_prior_plan(self, op: int, nbytes: int, dtype: int, nranks: int, multicast: bool = True):
