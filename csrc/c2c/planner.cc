@@ -38,6 +38,7 @@ void writeHetero(FILE *f, const C2cHeteroFunc &h, size_t cs, int ind) {
     wr(f, ind + 4, "offset", (long long)(o.offset / cs));
     wr(f, ind + 4, "count", (long long)(o.count / cs));
     wr(f, ind + 4, "isRecv", o.isRecv);
+    if (o.buffType != 1) wr(f, ind + 4, "buffType", o.buffType);  // absent = receive buffer, as in the reference's files
     fprintf(f, "%*s</P2pOp>\n", ind + 2, "");
   }
   fprintf(f, "%*s</HeteroFunc>\n", ind, "");
@@ -128,6 +129,7 @@ bool readHetero(Lexer &lx, C2cHeteroFunc *h, size_t cs) {
             else if (k == "offset") o.offset = (size_t)v * cs;
             else if (k == "count") o.count = (size_t)v * cs;
             else if (k == "isRecv") o.isRecv = (int)v;
+            else if (k == "buffType") o.buffType = (int)v;
           }))
         return false;
       h->p2pOps.push_back(o);
@@ -278,7 +280,12 @@ flagcxResult_t c2cImportXml(C2cPlan *p, const std::string &prefix, int rank, siz
 
 // ------------------------------------------------------------------ default plans
 
-bool c2cBuildPlan(C2cPlan *p, flagcxCommOp_t op, size_t count, int root, int C, int L, int myCluster, int myLocal, bool pipelined) {
+// Stage tables of the hierarchical collectives (the reference's op -> stage table is
+// flagcx/core/c2c_algo.cc:749-971, its chunk scheduling and cross-cluster send/recv search :1089-1394).
+// World rank = cluster * L + local index.  "intra" = the ranks of one cluster, "inter" = the ranks that hold
+// the same local index in every cluster.
+bool c2cBuildPlan(C2cPlan *p, flagcxCommOp_t op, size_t count, int root, int C, int L, int myCluster, int myLocal, bool pipelined,
+                  int interRanks, bool heteroP2p, const size_t *tables) {
   *p = C2cPlan();
   auto homo = [](int commOp, int sendType, size_t so, int recvType, size_t ro, size_t cnt, int homoType, int rootRank = -1) {
     C2cHomoFunc h;
@@ -286,10 +293,38 @@ bool c2cBuildPlan(C2cPlan *p, flagcxCommOp_t op, size_t count, int root, int C, 
     h.homoType = homoType; h.rootRank = rootRank;
     return h;
   };
+  auto p2p = [&](int peer, int buffType, size_t off, size_t cnt, int isRecv) {
+    C2cP2pOp o;
+    o.rank = myCluster * L + myLocal; o.peerRank = peer; o.buffType = buffType; o.offset = off; o.count = cnt; o.isRecv = isRecv;
+    return o;
+  };
   const int rootCluster = root / L, rootLocal = root % L;
+  const int K = (interRanks >= 1 && interRanks <= L && L % interRanks == 0) ? interRanks : L;  // inter ranks per cluster
+  const bool iAmInter = myLocal < K;
+  const size_t n = (size_t)C * L;
   switch (op) {
     case flagcxCommOpAllReduce: {
-      if (count == 0 || count % L != 0) return false;
+      if (count == 0) return false;
+      if (K < L) {
+        // Few network ports per cluster: piece j of the vector is reduced onto inter rank j of every cluster,
+        // all-reduced among the inter ranks j, and broadcast inside each cluster (the reference's
+        // "all-gather by broadcasts" post stage).
+        if (count % K != 0) return false;
+        const size_t pc = count / K;
+        p->totalCount = count;
+        std::vector<C2cHomoFunc> pre, post;
+        for (int j = 0; j < K; j++) {
+          pre.push_back(homo(flagcxCommOpReduce, 0, j * pc, 1, j * pc, pc, 0, j));
+          post.push_back(homo(flagcxCommOpBroadcast, 1, j * pc, 1, j * pc, pc, 2, j));
+        }
+        p->preHomoFuncSteps.push_back(pre);
+        if (iAmInter) p->homoInterFuncSteps.push_back({homo(flagcxCommOpAllReduce, 1, myLocal * pc, 1, myLocal * pc, pc, 1)});
+        else p->homoInterFuncSteps.push_back({});
+        p->postHomoFuncSteps.push_back(post);
+        p->nSeqPreSteps = p->nSeqInterSteps = p->nSeqPostSteps = 1;
+        return true;
+      }
+      if (count % L != 0) return false;
       int pieces = 1;
       if (pipelined)
         for (int cand : {4, 2})
@@ -312,7 +347,7 @@ bool c2cBuildPlan(C2cPlan *p, flagcxCommOp_t op, size_t count, int root, int C, 
     }
     case flagcxCommOpReduceScatter: {
       if (count == 0) return false;
-      p->totalCount = count * C * L;
+      p->totalCount = count * n;
       std::vector<C2cHomoFunc> pre;
       for (int c = 0; c < C; c++) pre.push_back(homo(flagcxCommOpReduceScatter, 0, (size_t)c * L * count, 2, (size_t)c * count, count, 0));
       p->preHomoFuncSteps.push_back(pre);
@@ -323,7 +358,25 @@ bool c2cBuildPlan(C2cPlan *p, flagcxCommOp_t op, size_t count, int root, int C, 
     }
     case flagcxCommOpAllGather: {
       if (count == 0) return false;
-      p->totalCount = count * C * L;
+      p->totalCount = count * n;
+      if (K < L || heteroP2p) {
+        // The cluster's pieces are gathered onto inter rank 0 at their place in the receive buffer; the inter
+        // ranks 0 of all clusters swap their cluster blocks with point-to-point transfers (the planner-built
+        // cross-cluster stage); each broadcasts the complete buffer inside its cluster.
+        const size_t block = (size_t)L * count;
+        p->preHomoFuncSteps.push_back({homo(flagcxCommOpGather, 0, 0, 1, (size_t)myCluster * block, count, 0, 0)});
+        C2cHeteroFunc het;
+        if (myLocal == 0)
+          for (int k = 1; k < C; k++) {
+            const int to = (myCluster + k) % C, from = (myCluster - k + C) % C;
+            het.p2pOps.push_back(p2p(to * L, 1, (size_t)myCluster * block, block, 0));
+            het.p2pOps.push_back(p2p(from * L, 1, (size_t)from * block, block, 1));
+          }
+        p->heteroFuncSteps.push_back({het});
+        p->postHomoFuncSteps.push_back({homo(flagcxCommOpBroadcast, 1, 0, 1, 0, n * count, 2, 0)});
+        p->nSeqPreSteps = p->nSeqPostSteps = 1;
+        return true;
+      }
       p->homoInterFuncSteps.push_back({homo(flagcxCommOpAllGather, 0, 0, 2, 0, count, 1)});
       std::vector<C2cHomoFunc> post;
       for (int c = 0; c < C; c++) post.push_back(homo(flagcxCommOpAllGather, 2, (size_t)c * count, 1, (size_t)c * L * count, count, 2));
@@ -336,6 +389,18 @@ bool c2cBuildPlan(C2cPlan *p, flagcxCommOp_t op, size_t count, int root, int C, 
       if (count == 0) return false;
       p->totalCount = count;
       bool isRoot = myCluster == rootCluster && myLocal == rootLocal;
+      if (heteroP2p) {
+        // the root sends to its counterpart in every other cluster, which then broadcasts inside its cluster
+        C2cHeteroFunc het;
+        if (isRoot)
+          for (int c = 0; c < C; c++)
+            if (c != myCluster) het.p2pOps.push_back(p2p(c * L + rootLocal, 0, 0, count, 0));
+        if (!isRoot && myLocal == rootLocal) het.p2pOps.push_back(p2p(root, 1, 0, count, 1));
+        p->heteroFuncSteps.push_back({het});
+        p->postHomoFuncSteps.push_back({homo(flagcxCommOpBroadcast, (isRoot ? 0 : 1), 0, 1, 0, count, 2, rootLocal)});
+        p->nSeqPostSteps = 1;
+        return true;
+      }
       if (myLocal == rootLocal)
         p->homoInterFuncSteps.push_back({homo(flagcxCommOpBroadcast, isRoot ? 0 : 1, 0, 1, 0, count, 1, rootCluster)});
       else
@@ -357,8 +422,66 @@ bool c2cBuildPlan(C2cPlan *p, flagcxCommOp_t op, size_t count, int root, int C, 
       p->nSeqPreSteps = p->nSeqInterSteps = 1;
       return true;
     }
+    case flagcxCommOpGather: {
+      // every cluster gathers onto the root's counterpart (scratch: L pieces), the counterparts gather their
+      // cluster blocks onto the root, where block c lands at c * L * count: rank order
+      if (count == 0) return false;
+      p->totalCount = count * n;
+      const size_t block = (size_t)L * count;
+      p->preHomoFuncSteps.push_back({homo(flagcxCommOpGather, 0, 0, 2, 0, count, 0, rootLocal)});
+      if (myLocal == rootLocal) p->homoInterFuncSteps.push_back({homo(flagcxCommOpGather, 2, 0, 1, 0, block, 1, rootCluster)});
+      else p->homoInterFuncSteps.push_back({});
+      p->scratchCount = block;
+      p->nSeqPreSteps = p->nSeqInterSteps = 1;
+      return true;
+    }
+    case flagcxCommOpScatter: {
+      // the mirror image: the root scatters cluster blocks to its counterparts, each scatters inside its cluster
+      if (count == 0) return false;
+      p->totalCount = count * n;
+      const size_t block = (size_t)L * count;
+      if (myLocal == rootLocal) p->homoInterFuncSteps.push_back({homo(flagcxCommOpScatter, 0, 0, 2, 0, block, 1, rootCluster)});
+      else p->homoInterFuncSteps.push_back({});
+      p->postHomoFuncSteps.push_back({homo(flagcxCommOpScatter, 2, 0, 1, 0, count, 2, rootLocal)});
+      p->scratchCount = block;
+      p->nSeqInterSteps = p->nSeqPostSteps = 1;
+      return true;
+    }
+    case flagcxCommOpAlltoAll: {
+      // Stage 1, inside the cluster, once per destination cluster c': rank (c,l) hands rank (c,l') the block it
+      // addresses to (c',l'); scratch of (c,l') then holds [c'][l].  Stage 2, among the ranks of equal local
+      // index: (c,l') sends (c',l') the L blocks scratch[c'][*]; what arrives from cluster c'' are the blocks of
+      // the sources (c'',0..L-1), which is exactly the order of the all-to-all's receive buffer.
+      if (count == 0) return false;
+      p->totalCount = count * n;
+      const size_t block = (size_t)L * count;
+      std::vector<C2cHomoFunc> pre;
+      for (int c = 0; c < C; c++) pre.push_back(homo(flagcxCommOpAlltoAll, 0, (size_t)c * block, 2, (size_t)c * block, count, 0));
+      p->preHomoFuncSteps.push_back(pre);
+      p->homoInterFuncSteps.push_back({homo(flagcxCommOpAlltoAll, 2, 0, 1, 0, block, 1)});
+      p->scratchCount = n * count;
+      p->nSeqPreSteps = p->nSeqInterSteps = 1;
+      return true;
+    }
+    case flagcxCommOpAlltoAllv: {
+      // Variable blocks: a list of point-to-point transfers on the world communicator, the local block as a
+      // transfer to self (the reference's cross-cluster path is the same all-pairs send/recv,
+      // flagcx/flagcx.cc:1376-1387).  Built per call: it depends on the counts.
+      if (!tables) return false;
+      const size_t *sc = tables, *sd = tables + n, *rc = tables + 2 * n, *rd = tables + 3 * n;
+      C2cHeteroFunc het;
+      const int me = myCluster * L + myLocal;
+      for (size_t k = 0; k < n; k++) {
+        const int to = (int)((me + k) % n), from = (int)((me + n - k) % n);
+        if (sc[to]) het.p2pOps.push_back(p2p(to, 0, sd[to], sc[to], 0));
+        if (rc[from]) het.p2pOps.push_back(p2p(from, 1, rd[from], rc[from], 1));
+      }
+      p->totalCount = 1;
+      p->heteroFuncSteps.push_back({het});
+      return true;
+    }
     default:
-      return false;  // gather, scatter, all-to-all(v), send/recv run flat on the world communicator
+      return false;  // send/recv and the barrier run on the world communicator as they are
   }
 }
 
@@ -392,9 +515,26 @@ flagcxResult_t ensureState(flagcxComm *c) {
     FCX_CHECK(cudaToResult(cudaEventCreateWithFlags(&s->evA, cudaEventDisableTiming), "C2C event"));
     FCX_CHECK(cudaToResult(cudaEventCreateWithFlags(&s->evB, cudaEventDisableTiming), "C2C event"));
   }
+  // How many ranks of a cluster talk across clusters (the reference's single-NIC / multi-NIC / NIC-per-rank
+  // modes, flagcx/core/c2c_algo.cc:637-672): FLAGCX_C2C_INTER_RANKS, else the number of distinct network ports
+  // that FLAGCX_TOPO_FILE gives the GPUs of this cluster, else every rank.
+  int k = (int)envInt("C2C_INTER_RANKS", 0);
+  if (k <= 0 && !c->netOfRank.empty()) {
+    std::vector<std::string> nets;
+    for (int r = first; r < first + s->clusterSize; r++)
+      if (!c->netOfRank[r].empty() && std::find(nets.begin(), nets.end(), c->netOfRank[r]) == nets.end()) nets.push_back(c->netOfRank[r]);
+    k = (int)nets.size();
+  }
+  if (k <= 0 || k > s->clusterSize || s->clusterSize % k != 0) k = s->clusterSize;
+  // every rank must use the same mode: agree on the smallest
+  std::vector<int> ks(c->nranks, k);
+  FCX_CHECK(c->bs.allGather(ks.data(), sizeof(int)));
+  for (int v : ks) k = std::min(k, v);
+  s->interRanks = k;
+  s->heteroP2p = envInt("C2C_HETERO_P2P", 0) != 0;
   s->ready = true;
-  FCX_INFO(SUB_INIT, "C2C: rank %d is local %d of cluster %d (%d clusters x %d ranks)", c->rank, s->myLocal, c->myCluster, c->nclusters,
-           s->clusterSize);
+  FCX_INFO(SUB_INIT, "C2C: rank %d is local %d of cluster %d (%d clusters x %d ranks, %d inter ranks per cluster%s)", c->rank, s->myLocal,
+           c->myCluster, c->nclusters, s->clusterSize, s->interRanks, s->heteroP2p ? ", point-to-point cross-cluster stage" : "");
   return flagcxSuccess;
 }
 
@@ -445,7 +585,8 @@ flagcxResult_t runHetero(flagcxComm *c, const C2cHeteroFunc &h, const PendingOp 
   FCX_CHECK(flagcxGroupStart(c));
   flagcxResult_t r = flagcxSuccess;
   for (auto &p : h.p2pOps) {
-    char *buf = (char *)o.recv + p.offset * es;
+    char *base = p.buffType == 0 ? (char *)o.send : p.buffType == 2 ? (char *)c->c2c->scratch : (char *)o.recv;
+    char *buf = base + p.offset * es;
     r = p.isRecv ? flagcxRecv(buf, p.count, o.dt, p.peerRank, c, &fs) : flagcxSend(buf, p.count, o.dt, p.peerRank, c, &fs);
     if (r != flagcxSuccess) break;
   }
@@ -492,7 +633,8 @@ flagcxResult_t c2cExecute(flagcxComm *c, const PendingOp &o, bool *handled) {
   if (disabled) return flagcxSuccess;
   switch (o.op) {
     case flagcxCommOpAllReduce: case flagcxCommOpReduceScatter: case flagcxCommOpAllGather: case flagcxCommOpBroadcast:
-    case flagcxCommOpReduce: break;
+    case flagcxCommOpReduce: case flagcxCommOpGather: case flagcxCommOpScatter: case flagcxCommOpAlltoAll:
+    case flagcxCommOpAlltoAllv: break;
     default: return flagcxSuccess;
   }
   if (o.outDt != o.dt || o.scale != 1.0f) return flagcxSuccess;
@@ -506,14 +648,18 @@ flagcxResult_t c2cExecute(flagcxComm *c, const PendingOp &o, bool *handled) {
   const bool pipelined = algo == "RING_PIPELINED";
 
   size_t sendTotal = o.count, recvTotal = o.count;
-  if (o.op == flagcxCommOpReduceScatter) sendTotal = o.count * c->nranks;
-  if (o.op == flagcxCommOpAllGather) recvTotal = o.count * c->nranks;
-  const size_t rootCluster = (o.op == flagcxCommOpBroadcast || o.op == flagcxCommOpReduce) ? (size_t)(o.root / L) : (size_t)-1;
+  if (o.op == flagcxCommOpReduceScatter || o.op == flagcxCommOpScatter) sendTotal = o.count * c->nranks;
+  if (o.op == flagcxCommOpAllGather || o.op == flagcxCommOpGather) recvTotal = o.count * c->nranks;
+  if (o.op == flagcxCommOpAlltoAll) sendTotal = recvTotal = o.count * c->nranks;
+  const bool rooted = o.op == flagcxCommOpBroadcast || o.op == flagcxCommOpReduce || o.op == flagcxCommOpGather || o.op == flagcxCommOpScatter;
+  const size_t rootCluster = rooted ? (size_t)(o.root / L) : (size_t)-1;
   const size_t fileHash = c2cAlgoHash(sendTotal, recvTotal, rootCluster, o.op, o.red);
   const size_t key = fileHash ^ ((size_t)o.dt << 40) ^ ((size_t)o.root << 48) ^ (pipelined ? 1ull << 63 : 0);
+  const bool perCall = o.op == flagcxCommOpAlltoAllv;  // the plan depends on this call's counts: never cached
 
   C2cPlan *plan = nullptr;
-  for (auto it = s->cache.begin(); it != s->cache.end(); ++it)
+  C2cPlan fresh;
+  for (auto it = s->cache.begin(); !perCall && it != s->cache.end(); ++it)
     if (it->key == key) {
       s->cache.splice(s->cache.begin(), s->cache, it);
       plan = &s->cache.front().plan;
@@ -527,16 +673,22 @@ flagcxResult_t c2cExecute(flagcxComm *c, const PendingOp &o, bool *handled) {
       if (prefix.empty() && !path.empty()) prefix = path + "/" + std::to_string(fileHash);
       if (prefix.empty()) { FCX_WARN("FLAGCX_C2C_ALGO=XML_INPUT needs FLAGCX_ALGO_IMPORT_PREFIX or FLAGCX_ALGO_IMPORT_PATH"); return flagcxInvalidUsage; }
       FCX_CHECK(c2cImportXml(&p, prefix, c->rank, std::max(sendTotal, recvTotal)));
-    } else if (!c2cBuildPlan(&p, o.op, o.count, o.root, C, L, c->myCluster, s->myLocal, pipelined)) {
+    } else if (!c2cBuildPlan(&p, o.op, o.count, o.root, C, L, c->myCluster, s->myLocal, pipelined, s->interRanks, s->heteroP2p,
+                             o.tables.empty() ? nullptr : o.tables.data())) {
       return flagcxSuccess;  // not planned hierarchically: run flat
     }
     std::string ex = envStr("ALGO_EXPORT_PREFIX", "");
     std::string exPath = envStr("ALGO_EXPORT_PATH", "");
     if (ex.empty() && !exPath.empty()) ex = exPath + "/" + std::to_string(fileHash);
     if (!ex.empty() && !fromXml) c2cExportXml(p, ex, c->rank);
-    s->cache.push_front({key, std::move(p)});
-    if (s->cache.size() > 16) s->cache.pop_back();
-    plan = &s->cache.front().plan;
+    if (perCall) {
+      fresh = std::move(p);
+      plan = &fresh;
+    } else {
+      s->cache.push_front({key, std::move(p)});
+      if (s->cache.size() > 16) s->cache.pop_back();
+      plan = &s->cache.front().plan;
+    }
   }
 
   FCX_CHECK(ensureScratch(c, plan->scratchCount * dtypeSize(o.dt)));

@@ -40,8 +40,9 @@ struct C2cHomoFunc {
 
 struct C2cP2pOp {
   int rank = 0, peerRank = 0;
-  size_t offset = 0, count = 0;  // elements, relative to the receive buffer
+  size_t offset = 0, count = 0;  // elements, relative to the buffer named by buffType
   int isRecv = 0;
+  int buffType = 1;              // 0 user send buffer, 1 user receive buffer (the reference's only choice), 2 scratch
 };
 
 struct C2cHeteroFunc {
@@ -73,13 +74,22 @@ size_t c2cAlgoHash(size_t sendCount, size_t recvCount, size_t rootCluster, int c
 
 // Build the default plan of a collective for a communicator of nclusters x clusterSize ranks.
 // Returns false when the operation is not planned hierarchically (the caller runs it flat).
+// interRanks: how many ranks of a cluster talk to the other clusters - the reference's three modes: 1 = one
+// network port per cluster ("single NIC"), k dividing clusterSize = several ("multi NIC"), clusterSize = every
+// rank has its own ("each NIC per rank", the natural mode inside one NVSwitch domain).  The inter ranks are
+// the local indices 0 .. interRanks-1.  heteroP2p: move data between clusters with point-to-point lists on the
+// world communicator (the reference's hetero stage) instead of collectives on the inter communicator, where
+// the operation allows it (no reduction across clusters).  tables: all-to-all-v counts and displacements
+// (scounts, sdispls, rcounts, rdispls; nranks entries each), else null.
 bool c2cBuildPlan(C2cPlan *p, flagcxCommOp_t op, size_t count, int root, int nclusters, int clusterSize, int myCluster,
-                  int myLocal, bool pipelined);
+                  int myLocal, bool pipelined, int interRanks = 0, bool heteroP2p = false, const size_t *tables = nullptr);
 
 class C2cState {
  public:
   flagcxComm *intra = nullptr, *inter = nullptr;
   int clusterSize = 0, myLocal = 0;
+  int interRanks = 0;       // ranks per cluster that talk across clusters (see c2cBuildPlan)
+  bool heteroP2p = false;   // cross-cluster stage as point-to-point lists where the operation allows it
   bool ready = false, unusable = false;
   void *scratch = nullptr;
   size_t scratchBytes = 0;

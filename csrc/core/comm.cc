@@ -33,6 +33,7 @@ flagcxResult_t cudaToResult(cudaError_t e, const char *what) {
 void fifoStop(flagcxComm *c);     // fifo.cc
 void c2cDestroy(flagcxComm *c);   // c2c/planner.cc
 flagcxResult_t topoProbeAndDump(flagcxComm *c);  // topo.cc
+bool topoNvlinkCount(const char *busId, int *active, int *version);
 
 // Clusters: ranks with the same vendor string form a cluster; each cluster
 // can further be cut into k equal parts with FLAGCX_CLUSTER_SPLIT_LIST
@@ -636,6 +637,16 @@ flagcxResult_t flagcxCommDeregister(const flagcxComm_t comm, void *handle) {
 }
 
 // ---- extensions
+
+flagcxResult_t flagcxTopoNvlinkCount(const char *busId, int *activeLinks, int *version) {
+  if (!busId || !activeLinks || !version) return flagcxInvalidArgument;
+  return topoNvlinkCount(busId, activeLinks, version) ? flagcxSuccess : flagcxNotSupported;
+}
+flagcxResult_t flagcxCommGetNetOfRank(flagcxComm_t comm, int rank, char *out, size_t outBytes) {
+  if (!validComm(comm) || !out || !outBytes || rank < 0 || rank >= comm->nranks) return flagcxInvalidArgument;
+  snprintf(out, outBytes, "%s", rank < (int)comm->netOfRank.size() ? comm->netOfRank[rank].c_str() : "");
+  return flagcxSuccess;
+}
 
 flagcxResult_t flagcxCommHeapRetain(flagcxComm_t comm) { return commHeapRetain(comm); }
 flagcxResult_t flagcxCommHeapRelease(flagcxComm_t comm, void *ptr) { return commHeapRelease(comm, ptr); }

@@ -67,6 +67,8 @@ struct flagcxComm {
   // cluster view (FLAGCX_CLUSTER_SPLIT_LIST)
   std::vector<int> clusterOf;
   int nclusters = 1, myCluster = 0;
+  // network port each rank's GPU is attached to, from FLAGCX_TOPO_FILE (empty without one)
+  std::vector<std::string> netOfRank;
 
   // device side
   fcx::SymHeap heap;

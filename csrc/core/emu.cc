@@ -170,7 +170,11 @@ flagcxResult_t flagcxEmuSendRecv(flagcxEmu_t e, int nops, const int *srcRank, co
       gs[s].ops[gs[s].nops++] = o;
     } else {
       FcxP2pOp so{}, ro{};
-      so.isRecv = 0; so.peer = d; so.buf = sendbuf[i]; so.bytes = bytes[i]; so.heapOff = ~0ull;
+      so.isRecv = 0; so.peer = d; so.buf = sendbuf[i]; so.bytes = bytes[i]; so.heapOff = ~0ull; so.seg = FCX_SEG_NONE;
+      if (envInt("EMU_P2P_ZEROCOPY", 0) != 0 && bytes[i]) {  // the receiver reads the sender's buffer where it lies
+        so.seg = FCX_SEG_ABS;
+        so.heapOff = (uint64_t)(uintptr_t)sendbuf[i];
+      }
       so.firstChunk = e->sendChunks[s][d];
       e->sendChunks[s][d] += nch;
       ro.isRecv = 1; ro.peer = s; ro.buf = recvbuf[i]; ro.bytes = bytes[i]; ro.heapOff = ~0ull;

@@ -13,11 +13,88 @@
 
 #include <cstring>
 #include <cuda_runtime.h>
+#include <dlfcn.h>
 
 namespace fcx {
 
+// NVLink state through the management library, loaded at run time (libnvidia-ml.so.1, or the library named by
+// FLAGCX_NVML_LIBRARY: the tests point it at a stand-in).  Read-only queries; nothing is ever set.
+namespace {
+struct Nvml {
+  void *h = nullptr;
+  int (*init)() = nullptr;
+  int (*shutdown)() = nullptr;
+  int (*byBusId)(const char *, void **) = nullptr;
+  int (*linkState)(void *, unsigned, unsigned *) = nullptr;
+  int (*linkVersion)(void *, unsigned, unsigned *) = nullptr;
+  bool ok = false;
+  Nvml() {
+    std::string lib = envStr("NVML_LIBRARY", "libnvidia-ml.so.1");
+    h = dlopen(lib.c_str(), RTLD_NOW | RTLD_LOCAL);
+    if (!h) return;
+    init = (int (*)())dlsym(h, "nvmlInit_v2");
+    shutdown = (int (*)())dlsym(h, "nvmlShutdown");
+    byBusId = (int (*)(const char *, void **))dlsym(h, "nvmlDeviceGetHandleByPciBusId_v2");
+    linkState = (int (*)(void *, unsigned, unsigned *))dlsym(h, "nvmlDeviceGetNvLinkState");
+    linkVersion = (int (*)(void *, unsigned, unsigned *))dlsym(h, "nvmlDeviceGetNvLinkVersion");
+    ok = init && shutdown && byBusId && linkState;
+  }
+  ~Nvml() { if (h) dlclose(h); }
+};
+}  // namespace
+
+// Number of NVLink links that are up on the GPU with this PCI bus id, and their version (0 when unknown).
+// Returns false when the management library cannot be used.
+bool topoNvlinkCount(const char *busId, int *active, int *version) {
+  *active = 0;
+  *version = 0;
+  Nvml nv;
+  if (!nv.ok || nv.init() != 0) return false;
+  void *dev = nullptr;
+  bool found = nv.byBusId(busId, &dev) == 0;
+  if (found) {
+    for (unsigned link = 0; link < 32; link++) {
+      unsigned up = 0;
+      if (nv.linkState(dev, link, &up) != 0) break;  // past the last link of this GPU
+      if (up) {
+        (*active)++;
+        unsigned v = 0;
+        if (nv.linkVersion && nv.linkVersion(dev, link, &v) == 0) *version = (int)v;
+      }
+    }
+  }
+  nv.shutdown();
+  return found;
+}
+
+// FLAGCX_TOPO_FILE (reference: flagcx/core/topo.cc:337-389, sample test/unittest/topo_demo.xml): lines
+// <gpu dev="N" net="name"> attach a network port to a GPU.  Returns the port of every device index found.
+static bool readTopoFile(const std::string &path, std::vector<std::string> *netOfDev) {
+  FILE *f = fopen(path.c_str(), "r");
+  if (!f) return false;
+  char line[512];
+  while (fgets(line, sizeof line, f)) {
+    const char *g = strstr(line, "<gpu");
+    if (!g) continue;
+    const char *d = strstr(g, "dev=\""), *n = strstr(g, "net=\"");
+    if (!d) continue;
+    int dev = atoi(d + 5);
+    if (dev < 0 || dev >= 1024) continue;
+    std::string net;
+    if (n) {
+      const char *e = strchr(n + 5, '"');
+      if (e) net.assign(n + 5, e);
+    }
+    if ((int)netOfDev->size() <= dev) netOfDev->resize(dev + 1);
+    (*netOfDev)[dev] = net;
+  }
+  fclose(f);
+  return true;
+}
+
 struct TopoRank {
   int cudaDev, smCount, multicast, ccMajor, ccMinor;
+  int nvlinks, nvlinkVersion, fabric;  // links that are up, their generation, fabric (multi-node NVLink) handles supported
   unsigned long long memBytes;
   char name[64];
   char busId[32];
@@ -35,22 +112,19 @@ flagcxResult_t topoProbeAndDump(flagcxComm *c) {
   std::string dump = envStr("TOPO_DUMP_FILE", "");
   std::string given = envStr("TOPO_FILE", "");
   if (!given.empty()) {
-    // A topology supplied by the user replaces the probe (reference: FLAGCX_TOPO_FILE).  Inside one NVSwitch
-    // domain nothing is derived from it; it is checked against the communicator and reported.
-    if (c->rank == 0) {
-      FILE *f = fopen(given.c_str(), "r");
-      if (!f) { FCX_WARN("cannot read topology file %s", given.c_str()); return flagcxSystemError; }
-      char line[512];
-      int ranks = -1;
-      while (fgets(line, sizeof line, f)) {
-        const char *at = strstr(line, "ranks=\"");
-        if (strstr(line, "<system") && at) { ranks = atoi(at + 7); break; }
-      }
-      fclose(f);
-      if (ranks != c->nranks) FCX_WARN("topology file %s describes %d ranks, the communicator has %d", given.c_str(), ranks, c->nranks);
-      else FCX_INFO(SUB_GRAPH, "topology taken from %s (%d ranks)", given.c_str(), ranks);
+    // A topology supplied by the user (reference: FLAGCX_TOPO_FILE): it says which network port each GPU is
+    // attached to.  Inside one NVSwitch domain the ports only matter to the hierarchical planner, which takes
+    // the GPUs with distinct ports as the ranks of a cluster that talk to the other clusters.
+    std::vector<std::string> netOfDev;
+    if (!readTopoFile(given, &netOfDev)) { FCX_WARN("cannot read topology file %s", given.c_str()); return flagcxSystemError; }
+    c->netOfRank.assign(c->nranks, "");
+    int known = 0;
+    for (int r = 0; r < c->nranks; r++) {
+      // host-only ranks have no device index: they are numbered by rank
+      int dev = c->peers[r].hostOnly ? r : c->peers[r].cudaDev;
+      if (dev >= 0 && dev < (int)netOfDev.size()) { c->netOfRank[r] = netOfDev[dev]; known += !netOfDev[dev].empty(); }
     }
-    return flagcxSuccess;
+    if (c->rank == 0) FCX_INFO(SUB_GRAPH, "topology file %s: network port known for %d of %d ranks", given.c_str(), known, c->nranks);
   }
   bool detect = envStr("ENABLE_TOPO_DETECT", "") == "TRUE" || !dump.empty();
   if (!detect || c->hostOnly) return flagcxSuccess;
@@ -66,6 +140,12 @@ flagcxResult_t topoProbeAndDump(flagcxComm *c) {
   me.ccMinor = p.minor;
   me.memBytes = p.totalGlobalMem;
   me.multicast = c->heap.mcBase != nullptr;
+  topoNvlinkCount(c->peers[c->rank].busId, &me.nvlinks, &me.nvlinkVersion);
+  {
+    int v = 0;  // CU_DEVICE_ATTRIBUTE_HANDLE_TYPE_FABRIC_SUPPORTED
+    if (cudaDeviceGetAttribute(&v, (cudaDeviceAttr)128, c->cudaDev) == cudaSuccess) me.fabric = v;
+    cudaGetLastError();
+  }
   snprintf(me.name, sizeof me.name, "%s", p.name);
   snprintf(me.busId, sizeof me.busId, "%s", c->peers[c->rank].busId);
   for (int r = 0; r < n && r < FCX_MAX_RANKS; r++) {
@@ -85,8 +165,10 @@ flagcxResult_t topoProbeAndDump(flagcxComm *c) {
   fprintf(f, "<system version=\"1\" domain=\"nvswitch\" ranks=\"%d\" multicast=\"%d\">\n", n, me.multicast);
   for (int r = 0; r < n; r++) {
     const TopoRank &t = all[r];
-    fprintf(f, "  <gpu rank=\"%d\" dev=\"%d\" busid=\"%s\" name=\"%s\" sm=\"%d.%d\" sms=\"%d\" mem_gib=\"%.1f\" cluster=\"%d\">\n", r, t.cudaDev,
-            t.busId, t.name, t.ccMajor, t.ccMinor, t.smCount, t.memBytes / 1073741824.0, c->clusterOf[r]);
+    fprintf(f, "  <gpu rank=\"%d\" dev=\"%d\" busid=\"%s\" name=\"%s\" sm=\"%d.%d\" sms=\"%d\" mem_gib=\"%.1f\" cluster=\"%d\" nvlinks=\"%d\" "
+               "nvlink_version=\"%d\" fabric=\"%d\" net=\"%s\">\n", r, t.cudaDev, t.busId, t.name, t.ccMajor, t.ccMinor, t.smCount,
+            t.memBytes / 1073741824.0, c->clusterOf[r], t.nvlinks, t.nvlinkVersion, t.fabric,
+            r < (int)c->netOfRank.size() ? c->netOfRank[r].c_str() : "");
     for (int q = 0; q < n; q++)
       fprintf(f, "    <path to=\"%d\" type=\"%s\" access=\"%d\" atomics=\"%d\" perf_rank=\"%d\"/>\n", q, pathType(t, r, q), t.access[q],
               t.atomics[q], t.perfRank[q]);

@@ -60,7 +60,7 @@ double pipelinedUs(double linkBytes, double localBytes, double pieceBytes, int d
 double estimateUs(const Plan &p, flagcxCommOp_t op, size_t bytesIn, int, const TunerCaps &caps) {
   const double b = (double)bytesIn, n = caps.nranks;
   const int c = p.nctas;
-  const bool mc = caps.multicast;
+  const bool mc = caps.multicast && caps.nranks > 2;  // with two ranks the zero-copy kinds use plain loads and stores
   const double zcFixed = kLaunchUs + 2 * kBarrierUs;
   switch (p.kind) {
     // zero-copy kinds: two barriers, one pass; bound by the link or by what `c` CTAs keep in flight

@@ -57,6 +57,12 @@ flagcxResult_t flagcxCommGetCounters(flagcxComm_t comm, flagcxCommCounters *out)
  * clusters on one box). */
 flagcxResult_t flagcxCommGetClusterInfo(flagcxComm_t comm, int *nclusters, int *myCluster, int *clusterOfRank /* nranks ints, may be NULL */);
 
+/* Topology queries.  NVLink links that are up on the GPU with this PCI bus id and their generation, read
+ * through the management library (flagcxNotSupported when it cannot be loaded); the network port that
+ * FLAGCX_TOPO_FILE attaches to a rank's GPU (empty string without one). */
+flagcxResult_t flagcxTopoNvlinkCount(const char *busId, int *activeLinks, int *version);
+flagcxResult_t flagcxCommGetNetOfRank(flagcxComm_t comm, int rank, char *out, size_t outBytes);
+
 /* Symmetric heap access for fused kernels written by the user: device
  * pointers through which this rank reaches every rank's heap, the multicast
  * alias (NULL when the box has none), and translation of a pointer returned by

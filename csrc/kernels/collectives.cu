@@ -294,6 +294,29 @@ __device__ void fcxCollBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta,
   const char *send = (const char *)a.send;
   char *recv = (char *)a.recv;
 
+  // Bounds of the staging area: the host cuts a message so that one launch fits, and the kernel checks it
+  // again, because a launch that does not fit would write into the other parity's half or past the heap.
+  {
+    size_t need = 0;
+    const size_t units = (a.count + G - 1) / G, sliceUnits = (units + n - 1) / n;
+    switch (a.kind) {
+      case FCX_K_AR_ONESHOT:
+      case FCX_K_RS: need = (size_t)n * units * INB; break;
+      case FCX_K_AR_TWOSHOT:
+      case FCX_K_REDUCE: need = (size_t)n * sliceUnits * (INB + OUTB); break;
+      case FCX_K_AR_NVLS: need = (size_t)n * sliceUnits * 16; break;
+      case FCX_K_RS_NVLS: need = (size_t)n * ((a.count * ESI + 15) / 16 * 16); break;
+      case FCX_K_AR_LL: case FCX_K_REDUCE_LL: need = a.count * ESI > FCX_LL_MAX_PAYLOAD ? ~(size_t)0 : 0; break;
+      case FCX_K_RS_LL: need = a.count * ESI > FCX_LL_MAX_PAYLOAD ? ~(size_t)0 : 0; break;
+      default: break;
+    }
+    if (need > dc.stageBytes) {
+      if (threadIdx.x == 0) giveUp(dc, FCX_ERR_BADARG, me, FCX_WAIT_BARRIER, cta, dc.stageBytes, need, seq);
+      epilogue(dc, seq, nctas);
+      return;
+    }
+  }
+
   switch (a.kind) {
     case FCX_K_BARRIER: {
       if (cta == 0) ctaBarrier(dc, 0, barrierValue(seq, 1), seq);
@@ -640,6 +663,19 @@ __device__ void fcxMoveBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta,
   const size_t bytes = a.count * es;
   const size_t slot = (bytes + 15) / 16 * 16;
 
+  {  // the pieces of one launch must fit the staging half (or the LL slots) they travel through
+    size_t need = 0;
+    const int mk0 = a.kind == FCX_K_MOVE_LL ? a.moveOp : a.kind;
+    if (a.kind == FCX_K_MOVE_LL) need = bytes > FCX_LL_MAX_PAYLOAD ? ~(size_t)0 : 0;
+    else if (mk0 == FCX_K_BCAST || mk0 == FCX_K_SCATTER) need = slot;
+    else if (a.kind != FCX_K_A2AV) need = (size_t)n * slot;
+    if (need > dc.stageBytes) {
+      if (threadIdx.x == 0) giveUp(dc, FCX_ERR_BADARG, me, FCX_WAIT_BARRIER, cta, dc.stageBytes, need, seq);
+      epilogue(dc, seq, nctas);
+      return;
+    }
+  }
+
   if (a.kind != FCX_K_A2AV) {
     const int mk = a.kind == FCX_K_MOVE_LL ? a.moveOp : a.kind;  // the LL form moves the same pieces
     // Every fixed-size byte mover is one exchange: piece out[p] goes into a slot of rank p's staging area,
@@ -896,8 +932,10 @@ __device__ void fcxMoveBody(const FcxDevComm &dc, const FcxCollArgs &a, int cta,
 // (NVLink stores) and raises `ready` on the receiver; the receiver copies the
 // chunk out of its own memory and raises `consumed` on the sender, which
 // frees the slot.  Two slots per (receiver, sender) pair keep both sides busy.
-// With FLAGCX_P2P_ZEROCOPY=1 a send whose buffer lives in the heap publishes
-// its heap offset instead and the receiver reads it directly.
+// A send whose buffer is peer-visible (symmetric heap or registered segment)
+// publishes where it lives instead, and the receiver reads it directly into
+// the user's receive buffer: one pass over NVLink, nothing staged
+// (FLAGCX_P2P_ZEROCOPY=0 turns that off).
 __device__ __forceinline__ FcxP2pCtl *p2pCtl(const FcxDevComm &dc, int onRank, int dir, int peer) {
   return (FcxP2pCtl *)(dc.heap[onRank] + FCX_OFF_P2P) + dir * FCX_MAX_RANKS + peer;
 }
@@ -944,6 +982,7 @@ __device__ void fcxP2pBody(const FcxDevComm &dc, const FcxP2pArgs &g, int cta) {
     if (zeroCopy) {
       if (sub == 0 && threadIdx.x == 0) {
         stRelaxed(&theirs->srcOff, op.heapOff);
+        stRelaxed(&theirs->srcSeg, (uint64_t)(int64_t)op.seg);
         stRelease(&theirs->ready, op.firstChunk + nchunks);
       }
       // the buffer stays in use until the receiver has read all of it
@@ -981,7 +1020,9 @@ __device__ void fcxP2pBody(const FcxDevComm &dc, const FcxP2pArgs &g, int cta) {
   }
   const uint64_t srcOff = ldRelaxed(&mine->srcOff);
   if (srcOff != ~0ull) {
-    if (op.bytes) copyUnits((char *)op.buf, dc.heap[peer] + srcOff, op.bytes, 16, gtid, gstride);
+    const char *src = zcResolve(dc, (int)(int64_t)ldRelaxed(&mine->srcSeg), srcOff, peer);
+    if (op.bytes && src) copyUnits((char *)op.buf, src, op.bytes, 16, gtid, gstride);
+    if (op.bytes && !src && gtid == 0) giveUp(dc, FCX_ERR_BADARG, peer, FCX_WAIT_P2P_READY, cta, 0, srcOff, op.firstChunk);
     if (opArrive(dc, opIdx, 0, g.ctasPerOp) && threadIdx.x == 0) stRelease(&theirs->consumed, op.firstChunk + nchunks);
     return;
   }

@@ -46,8 +46,8 @@ struct FcxMail {  // 64 bytes, written by the source rank before it raises its f
 struct FcxP2pCtl {  // one per (direction, peer); all counters only ever grow
   uint64_t ready;     // sender -> receiver: chunks made available so far
   uint64_t consumed;  // receiver -> sender: chunks fully read so far
-  uint64_t srcOff;    // sender -> receiver: heap offset of the data when it is peer-visible
-  uint64_t pad;
+  uint64_t srcOff;    // sender -> receiver: offset of the data inside its segment when it is peer-visible, else ~0
+  uint64_t srcSeg;    // sender -> receiver: that segment (FCX_SEG_*)
 };
 
 // Why a kernel gave up waiting.  Lives in page-locked host memory so the host
@@ -146,7 +146,8 @@ struct FcxP2pOp {
   void *buf;
   size_t bytes;
   uint64_t firstChunk;   // running chunk counter of this (direction, peer) before the op
-  uint64_t heapOff;      // send only: heap offset when the buffer is peer-visible, else ~0
+  uint64_t heapOff;      // send only: offset inside its segment when the buffer is peer-visible, else ~0
+  int seg;               // send only: that segment (FCX_SEG_*)
 };
 
 struct FcxP2pArgs {

@@ -164,6 +164,18 @@ __device__ __forceinline__ void epilogue(const FcxDevComm &dc, uint64_t seq, int
   }
 }
 
+// Rank p's copy of a peer-visible buffer, as this rank addresses it (FCX_SEG_* in devcomm.h); null when the
+// segment is unknown.
+__device__ __forceinline__ char *zcResolve(const FcxDevComm &dc, int seg, uint64_t off, int p) {
+  if (seg == FCX_SEG_HEAP) return dc.heap[p] + off;
+  if (seg == FCX_SEG_ABS) return (char *)(uintptr_t)off;
+  if (seg > 0 && seg < FCX_MAX_SEGS && dc.segs != nullptr) {
+    char *b = dc.segs[seg][p];
+    return b ? b + off : nullptr;
+  }
+  return nullptr;
+}
+
 // ------------------------------------------------------------------ element types
 
 struct F8E4 { uint8_t v; };

@@ -30,16 +30,6 @@ struct ZcPeers {
   uint64_t x[FCX_MAX_RANKS], y[FCX_MAX_RANKS];  // two free words per source rank (all-to-all-v: displacement, count)
 };
 
-__device__ __forceinline__ char *zcResolve(const FcxDevComm &dc, int seg, uint64_t off, int p) {
-  if (seg == FCX_SEG_HEAP) return dc.heap[p] + off;
-  if (seg == FCX_SEG_ABS) return (char *)(uintptr_t)off;
-  if (seg > 0 && seg < FCX_MAX_SEGS && dc.segs != nullptr) {
-    char *b = dc.segs[seg][p];
-    return b ? b + off : nullptr;
-  }
-  return nullptr;
-}
-
 // Step 1 of the protocol.  `needSend` / `needRecv`: which buffers the kind will touch on the peers; a peer
 // whose buffer is not visible, or a heap range that leaves the heap, ends the collective with a recorded
 // FCX_ERR_BADARG instead of a wild access.  sendSpan / recvSpan are the bytes a peer may touch from the offset.

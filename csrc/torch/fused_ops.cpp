@@ -45,19 +45,6 @@ static void ringExchange(uint64_t comm, const at::Tensor &src, at::Tensor &inbox
   TORCH_CHECK(e == cudaSuccess, "ring exchange launch failed: ", cudaGetErrorString(e));
 }
 
-extern "C" cudaError_t fcxCopyProbe(const FcxDevComm *dc, void *local, size_t peerOffset, size_t bytes, int mode, int peer, int *status,
-                                    int nblocks, cudaStream_t s);
-
-// Move local <-> peer's heap tensor with the chosen transfer style (0: ld/st, 1: bulk push, 2: bulk pull); returns nothing, time it outside.
-static void copyProbe(uint64_t comm, at::Tensor &local, at::Tensor &heapT, int64_t mode, int64_t peer, int64_t ctas, at::Tensor &status) {
-  c10::cuda::CUDAGuard g(local.device());
-  FcxDevComm dc = devComm(comm);
-  TORCH_CHECK(heapT.nbytes() >= local.nbytes(), "heap tensor too small");
-  auto e = fcxCopyProbe(&dc, local.data_ptr(), heapOffset(comm, heapT), local.nbytes(), (int)mode, (int)peer, status.data_ptr<int>(), (int)ctas,
-                        at::cuda::getCurrentCUDAStream().stream());
-  TORCH_CHECK(e == cudaSuccess, "copy probe launch failed: ", cudaGetErrorString(e));
-}
-
 static int64_t allocSignals(uint64_t comm, int64_t n) {
   int first = 0;
   FCX_OK2(flagcxCommAllocSignals((flagcxComm_t)(uintptr_t)comm, (int)n, &first));
@@ -70,7 +57,6 @@ void bindMoe(py::module &m);   // moe_bind.cpp
 void bindFused(py::module &m) {
   m.def("ring_exchange", &ringExchange, py::arg("comm"), py::arg("src"), py::arg("inbox"), py::arg("dst"), py::arg("slot"), py::arg("epoch"));
   m.def("alloc_signals", &allocSignals);
-  m.def("copy_probe", &copyProbe);
   bindGemm(m);
   bindMoe(m);
 }

@@ -581,6 +581,8 @@ int scratchForCurrentDevice(float **out) {
 extern "C" int fcxColSumNoAlloc(const void *a, void *out, int M, int C, int accumulate, cudaStream_t stream) {
   if (!a || !out) return FCX_NOALLOC_NULL_POINTER;
   if (M <= 0 || C <= 0 || C % 64 != 0) return FCX_NOALLOC_BAD_SHAPE;
+  // the kernels read `a` in 16-byte vectors; a raw-pointer caller with an odd offset gets a code, not a fault
+  if (((uintptr_t)a & 15u) != 0 || ((uintptr_t)out & 15u) != 0) return FCX_NOALLOC_MISALIGNED;
   const int parts = fcxColSumPartials(M);
   if ((long long)parts * C > (long long)FCX_NOALLOC_MAX_FLOATS) return FCX_NOALLOC_TOO_LARGE;
   float *scratch = nullptr;
@@ -599,6 +601,7 @@ extern "C" const char *fcxNoAllocErrorString(int code) {
     case FCX_NOALLOC_TOO_LARGE: return "shape needs more than the built-in scratch (partials x C > 262144 floats); use fcxColSum with your own scratch";
     case FCX_NOALLOC_BAD_SHAPE: return "M and C must be positive and C a multiple of 64";
     case FCX_NOALLOC_NULL_POINTER: return "input and output pointers must not be null";
+    case FCX_NOALLOC_MISALIGNED: return "input and output pointers must be 16-byte aligned";
     default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown code";
   }
 }

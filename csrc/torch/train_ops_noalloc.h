@@ -17,7 +17,9 @@
 //
 // Contract
 //   * a: [M, C] bf16 row-major, out: [C] bf16, both device memory supplied by
-//     the caller; C must be a multiple of 64.
+//     the caller, both 16-byte aligned (the kernels use 16-byte accesses; a
+//     pointer that is not is refused with FCX_NOALLOC_MISALIGNED); C must be a
+//     multiple of 64.
 //   * Limit: fcxColSumPartials(M) * C <= FCX_NOALLOC_MAX_FLOATS (262144), which
 //     always holds for C <= 8192; larger shapes are refused with
 //     FCX_NOALLOC_TOO_LARGE and nothing is launched.
@@ -40,6 +42,7 @@
 #define FCX_NOALLOC_TOO_LARGE (-1)
 #define FCX_NOALLOC_BAD_SHAPE (-2)
 #define FCX_NOALLOC_NULL_POINTER (-3)
+#define FCX_NOALLOC_MISALIGNED (-4)
 
 #ifdef __cplusplus
 extern "C" {

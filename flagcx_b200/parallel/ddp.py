@@ -90,25 +90,32 @@ class DataParallelTrainer:
         # ---- buckets, built from the end of the buffer (gradients arrive roughly in reverse order)
         self.buckets: List[_Bucket] = []
         self.bucket_of = {}
-        if self.world > 1:
-            cap = int(bucket_mb * (1 << 20) / 2)
-            end = n
-            cur_params = []
-            for i in range(len(self.specs) - 1, -1, -1):
-                name, off, cnt = self.specs[i]
-                cur_params.append(i)
-                if end - off >= cap or i == 0:
-                    b = _Bucket(off, end, len(cur_params))
-                    for j in cur_params:
-                        self.bucket_of[j] = len(self.buckets)
-                    self.buckets.append(b)
-                    end = off
-                    cur_params = []
-            for i, p in enumerate(params):
-                p.register_post_accumulate_grad_hook(self._make_hook(i))
-            self.comm_stream = torch.cuda.Stream(device=self.device, priority=-1)
-            self.ready_event = torch.cuda.Event()
-            self.done_event = torch.cuda.Event()
+        cap = int(bucket_mb * (1 << 20) / 2)
+        end = n
+        cur_params = []
+        for i in range(len(self.specs) - 1, -1, -1):
+            name, off, cnt = self.specs[i]
+            cur_params.append(i)
+            if end - off >= cap or i == 0:
+                b = _Bucket(off, end, len(cur_params))
+                for j in cur_params:
+                    self.bucket_of[j] = len(self.buckets)
+                self.buckets.append(b)
+                end = off
+                cur_params = []
+        for i, p in enumerate(params):
+            p.register_post_accumulate_grad_hook(self._make_hook(i))
+        # Side stream: a bucket's all-reduce and its share of the optimizer step run here, beside the rest of
+        # the backward pass.  A parameter whose gradient is complete is no longer read by this step's backward
+        # (the tied embedding sits in the bucket that closes last), so updating it early is safe.
+        self.side_stream = torch.cuda.Stream(device=self.device, priority=-1)
+        self.comm_stream = self.side_stream
+        self.ready_event = torch.cuda.Event()
+        self.done_event = torch.cuda.Event()
+        self.overlap_optimizer = os.environ.get("FLAGCX_DDP_OVERLAP_OPT", "1") != "0"
+        # the bucket that closes last has nothing left to overlap with: it may take more of the GPU
+        self.tail_ctas = int(os.environ.get("FLAGCX_DDP_TAIL_CTAS", "64"))
+        self._budget_now = getattr(self, "cta_budget", 0)
 
         self.snapshot_grads = False
         self.grad_snapshot = None
@@ -125,33 +132,51 @@ class DataParallelTrainer:
             b = self.buckets[self.bucket_of[idx]]
             b.pending -= 1
             if b.pending == 0:
-                self._reduce_bucket(b)
+                self._bucket_ready(b)
         return hook
 
-    def _reduce_bucket(self, b: _Bucket):
+    def _adamw(self, lo: int, hi: int):
+        fused_adamw_step(self.master[lo:hi], self.flat_params[lo:hi], self.flat_grads[lo:hi], self.m[lo:hi], self.v[lo:hi],
+                         lr=self.lr, betas=self.betas, eps=self.eps, weight_decay=self.wd, step=self.step_no + 1, zero_grad=True,
+                         step_dev=self.step_dev)
+
+    def _bucket_ready(self, b: _Bucket):
+        early_opt = self.overlap_optimizer and not self.snapshot_grads
+        if self.world == 1 and not early_opt:
+            return
         cur = torch.cuda.current_stream(self.device)
         self.ready_event.record(cur)
-        self.comm_stream.wait_event(self.ready_event)
-        g = self.flat_grads[b.start:b.end]
-        with torch.cuda.stream(self.comm_stream):
-            self.native.comm_all_reduce(self.comm, g, g, 4, 1.0)  # 4 = average
-        self.launches_per_step += 1
+        self.side_stream.wait_event(self.ready_event)
+        with torch.cuda.stream(self.side_stream):
+            if self.world > 1:
+                want = self.tail_ctas if b is self.buckets[-1] else self.cta_budget
+                if want != self._budget_now:
+                    self.native.comm_set_cta_budget(self.comm, want)
+                    self._budget_now = want
+                g = self.flat_grads[b.start:b.end]
+                self.native.comm_all_reduce(self.comm, g, g, 4, 1.0)  # 4 = average
+                self.launches_per_step += 1
+            if early_opt:
+                self._adamw(b.start, b.end)
+                self.launches_per_step += 1
 
     # ---- one optimisation step on tensors that already live on the device
     def _step_device(self, tokens, targets):
         for b in self.buckets:
             b.pending = b.nparams
         self.launches_per_step = 0
+        early_opt = self.overlap_optimizer and not self.snapshot_grads
+        self.step_dev.add_(1)  # before the backward pass: every bucket's optimizer share reads it
         loss = self.model(tokens, targets)
         loss.backward()
-        if self.world > 1:
-            self.done_event.record(self.comm_stream)
+        if self.world > 1 or early_opt:
+            self.done_event.record(self.side_stream)
             torch.cuda.current_stream(self.device).wait_event(self.done_event)
         if self.snapshot_grads:  # for tests: the averaged gradients as the optimizer is about to see them
             self.grad_snapshot = self.flat_grads.clone()
-        self.step_dev.add_(1)
-        fused_adamw_step(self.master, self.flat_params, self.flat_grads, self.m, self.v, lr=self.lr, betas=self.betas,
-                         eps=self.eps, weight_decay=self.wd, step=self.step_no + 1, zero_grad=True, step_dev=self.step_dev)
+        if not early_opt:
+            self._adamw(0, self.flat_grads.numel())
+            self.launches_per_step += 1
         return loss.detach()
 
     def _capture(self, tokens, targets):
@@ -193,8 +218,10 @@ class DataParallelTrainer:
         """Launches of this framework's own kernels in one step: per layer 2
         fused LayerNorm forward, 2 x 3 backward (dx, parameter partials, their
         reduction), bias-GELU forward + 3 backward (dx, bias partials,
-        reduction); the final LayerNorm (1 + 3), the loss kernel, AdamW, and
-        one all-reduce kernel per bucket (chunked by the staging size)."""
+        reduction); the final LayerNorm (1 + 3), the loss kernel, and per
+        bucket one all-reduce kernel (more than one rank) and one AdamW
+        kernel (one AdamW kernel in all when the optimizer is not overlapped)."""
         L = len(getattr(self.model, "blocks", []))
-        own = L * (2 + 6 + 1 + 3) + (1 + 3) + 1 + 1
-        return own + len(self.buckets)
+        own = L * (2 + 6 + 1 + 3) + (1 + 3) + 1
+        nb = len(self.buckets)
+        return own + (nb if self.world > 1 else 0) + (nb if self.overlap_optimizer else 1)

@@ -215,6 +215,8 @@ _SIGNATURES = {
                                       ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_ulonglong),
                                       ctypes.POINTER(ctypes.c_ulonglong)]),
     "flagcxCommClearError": (_R, [flagcxComm_t]),
+    "flagcxCommGetNetOfRank": (_R, [flagcxComm_t, ctypes.c_int, ctypes.c_char_p, _sz]),
+    "flagcxTopoNvlinkCount": (_R, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]),
     "flagcxCommRecover": (_R, [flagcxComm_t]),
     "flagcxTunerRecord": (_R, [flagcxComm_t, ctypes.c_int, _sz, ctypes.c_char_p, ctypes.c_int, ctypes.c_double]),
     "flagcxTunerSave": (_R, [flagcxComm_t, ctypes.c_char_p]),

@@ -343,7 +343,11 @@ def test_alltoall_and_alltoallv(lib, n):
 
 
 @pytest.mark.parametrize("n", [2, 4])
-def test_grouped_sendrecv(lib, n):
+@pytest.mark.parametrize("zero_copy", [False, True])
+def test_grouped_sendrecv(lib, n, zero_copy, monkeypatch):
+    # zero_copy: the sender publishes where its buffer lies and the receiver reads it in place (the form used
+    # for buffers in the symmetric heap or in a registered segment); otherwise data travels through staging slots
+    monkeypatch.setenv("FLAGCX_EMU_P2P_ZEROCOPY", "1" if zero_copy else "0")
     emu = Emu(lib, n)
     try:
         # a ring exchange plus a self copy per rank, two rounds, message larger than two staging chunks

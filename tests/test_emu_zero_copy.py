@@ -24,7 +24,7 @@ def lib(native_lib):
 @pytest.mark.parametrize("n", [2, 3, 4, 8])
 @pytest.mark.parametrize("count,nctas", [(1, 1), (7, 2), (4099, 3), (262147, 8), (1 << 20, 16)])
 def test_allreduce_zero_copy(lib, n, count, nctas):
-    emu = Emu(lib, n)
+    emu = Emu(lib, n, stage=16 << 20)  # the staged kind interleaved below needs (n + n) slices of staging
     try:
         for dtype in (torch.float32, torch.bfloat16):
             for rep in range(3):
@@ -190,6 +190,28 @@ def test_zero_copy_rejects_a_buffer_the_peers_cannot_see(lib):
         code = ctypes.c_int()
         lib.call("flagcxEmuGetError", emu.h, ctypes.byref(code))
         assert code.value == 3  # FCX_ERR_BADARG
+        for y in ys:
+            assert bool((y == -7.0).all())
+    finally:
+        emu.close()
+
+
+def test_a_launch_that_does_not_fit_the_staging_area_is_refused(lib):
+    """The emulator launches a message as one piece (the library proper cuts it to the staging size first); a
+    staged kind whose slots would overrun the staging half records a bad-argument error and moves nothing."""
+    n, count = 2, 1 << 20
+    emu = Emu(lib, n, stage=4 << 20)  # all-reduce needs 2 x (2 + 2) MiB here
+    try:
+        xs = _rand(n, count, torch.float32, seed=1)
+        ys = [torch.full((count,), -7.0, device="cuda") for _ in range(n)]
+        arr = ctypes.c_void_p * n
+        lib.call("flagcxEmuCollective", emu.h, OPS["allreduce"], b"ar_twoshot", 4, arr(*[x.data_ptr() for x in xs]),
+                 arr(*[y.data_ptr() for y in ys]), count, DT[torch.float32], DT[torch.float32], ctypes.c_float(1.0), 0, 0, None,
+                 ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        code = ctypes.c_int()
+        lib.call("flagcxEmuGetError", emu.h, ctypes.byref(code))
+        assert code.value == 3
         for y in ys:
             assert bool((y == -7.0).all())
     finally:

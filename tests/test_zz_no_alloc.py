@@ -35,14 +35,24 @@ def test_no_alloc_column_sum_matches_regular_entry_point_twice():
     lib = _lib()
     torch.manual_seed(0)
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    first = True
     for M, C in ((4096, 1024), (8192, 4096)):  # second call reuses (and overwrites) the same scratch
         a = torch.randn(M, C, device="cuda").bfloat16()
         out = torch.empty(C, dtype=torch.bfloat16, device="cuda")
-        before = torch.cuda.memory_allocated()
+        # Free device memory as the driver reports it (cudaMemGetInfo): unlike PyTorch's own counters it
+        # would show a cudaMalloc made behind PyTorch's back.  The first call on a device also looks up the
+        # scratch address, so the comparison brackets a call that comes after one has already been made.
+        if first:
+            rc = lib.fcxColSumNoAlloc(a.data_ptr(), out.data_ptr(), M, C, 0, stream)
+            assert rc == 0, lib.fcxNoAllocErrorString(rc).decode()
+            first = False
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
         rc = lib.fcxColSumNoAlloc(a.data_ptr(), out.data_ptr(), M, C, 0, stream)
         assert rc == 0, lib.fcxNoAllocErrorString(rc).decode()
-        assert torch.cuda.memory_allocated() == before
         torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        assert free_after >= free_before, (free_before, free_after)
         ref = nat.col_sum(a)
         torch.testing.assert_close(out.float(), ref.float(), atol=2e-2, rtol=2e-2)
         exact = a.float().sum(0)
@@ -59,3 +69,6 @@ def test_no_alloc_refuses_shapes_beyond_its_scratch():
     assert rc == -1 and b"scratch" in lib.fcxNoAllocErrorString(rc)
     assert lib.fcxColSumNoAlloc(a.data_ptr(), out.data_ptr(), 64, 100, 0, None) == -2
     assert lib.fcxColSumNoAlloc(None, out.data_ptr(), 64, 64, 0, None) == -3
+    # an odd byte offset into the matrix: refused, nothing launched
+    assert lib.fcxColSumNoAlloc(a.data_ptr() + 2, out.data_ptr(), 32, 64, 0, None) == -4
+    assert b"aligned" in lib.fcxNoAllocErrorString(-4)
