@@ -69,11 +69,14 @@ bool topoNvlinkCount(const char *busId, int *active, int *version) {
 
 // FLAGCX_TOPO_FILE (reference: flagcx/core/topo.cc:337-389, sample test/unittest/topo_demo.xml): lines
 // <gpu dev="N" net="name"> attach a network port to a GPU.  Returns the port of every device index found.
-static bool readTopoFile(const std::string &path, std::vector<std::string> *netOfDev) {
+static bool readTopoFile(const std::string &path, std::vector<std::string> *netOfDev, int *ranks) {
   FILE *f = fopen(path.c_str(), "r");
   if (!f) return false;
   char line[512];
+  *ranks = -1;
   while (fgets(line, sizeof line, f)) {
+    const char *at = strstr(line, "ranks=\"");
+    if (strstr(line, "<system") && at) *ranks = atoi(at + 7);  // a dump of this library states the world it describes
     const char *g = strstr(line, "<gpu");
     if (!g) continue;
     const char *d = strstr(g, "dev=\""), *n = strstr(g, "net=\"");
@@ -116,7 +119,10 @@ flagcxResult_t topoProbeAndDump(flagcxComm *c) {
     // attached to.  Inside one NVSwitch domain the ports only matter to the hierarchical planner, which takes
     // the GPUs with distinct ports as the ranks of a cluster that talk to the other clusters.
     std::vector<std::string> netOfDev;
-    if (!readTopoFile(given, &netOfDev)) { FCX_WARN("cannot read topology file %s", given.c_str()); return flagcxSystemError; }
+    int ranks = -1;
+    if (!readTopoFile(given, &netOfDev, &ranks)) { FCX_WARN("cannot read topology file %s", given.c_str()); return flagcxSystemError; }
+    if (ranks >= 0 && ranks != c->nranks && c->rank == 0)
+      FCX_WARN("topology file %s describes %d ranks, the communicator has %d", given.c_str(), ranks, c->nranks);
     c->netOfRank.assign(c->nranks, "");
     int known = 0;
     for (int r = 0; r < c->nranks; r++) {

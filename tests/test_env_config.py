@@ -11,13 +11,14 @@ def _worker(lib, uid, rank, world):
 
 def test_topology_file_is_read_and_checked(native_lib, tmp_path):
     topo = tmp_path / "topo.xml"
-    topo.write_text('<system version="1" domain="nvswitch" ranks="2" multicast="0">\n</system>\n')
+    topo.write_text('<system version="1" domain="nvswitch" ranks="2" multicast="0">\n  <gpu dev="0" net="mlx5_0"></gpu>\n'
+                    '  <gpu dev="1" net="mlx5_1"></gpu>\n</system>\n')
     log = tmp_path / "log_%p.txt"
     env = {"FLAGCX_TOPO_FILE": str(topo), "FLAGCX_DEBUG": "INFO", "FLAGCX_DEBUG_SUBSYS": "GRAPH,ENV", "FLAGCX_DEBUG_FILE": str(log),
            "FLAGCX_USE_HETERO_COMM": "1", "CUDA_VISIBLE_DEVICES": ""}
     run_ranks(_worker, 2, env=env)
     text = "".join(p.read_text() for p in tmp_path.glob("log_*.txt"))
-    assert "topology taken from" in text and "(2 ranks)" in text
+    assert "network port known for 2 of 2 ranks" in text
     assert "FLAGCX_USE_HETERO_COMM=1 accepted" in text
 
 
