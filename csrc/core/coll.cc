@@ -178,7 +178,9 @@ static flagcxResult_t launchOne(flagcxComm *c, FcxCollArgs &a, const Plan &plan,
   a.seq = ++c->seq;
   int nctas = std::max(1, std::min(plan.nctas, FCX_MAX_CTAS));
   if (timed) c->tuner->beginTiming(st);
-  cudaError_t e = fcxLaunchColl(&c->dev, &a, nctas, st);
+  FcxDevComm dev = c->dev;
+  if (plan.pipeBytes) dev.pipeBytes = plan.pipeBytes;  // the plan's own sub-chunk size (every rank holds the same plan)
+  cudaError_t e = fcxLaunchColl(&dev, &a, nctas, st);
   if (timed) c->tuner->endTiming(st);
   c->counters.launches++;
   if (plan.kind >= 0 && plan.kind < 24) c->counters.kindLaunches[plan.kind]++;
@@ -221,8 +223,8 @@ flagcxResult_t launchCollective(flagcxComm *c, const PendingOp &o) {
   // Switch reduction pays from three ranks on: with two, the plain exchange moves S bytes per direction and
   // the switch 1.5 S (measured on two B200s: 404 GB/s through the switch, 526 GB/s without).
   // FLAGCX_ZC_MC: 0 never, 1 from three ranks on (default), 2 always.  FLAGCX_ZC_AG_MC: the same for the
-  // multicast store of all-gather.
-  static const int zcMcEnv = (int)envInt("ZC_MC", 1), zcAgEnv = (int)envInt("ZC_AG_MC", 1);
+  // multicast store of all-gather.  flagcxCommSetZeroCopyMulticast overrides both per communicator.
+  const int zcMcEnv = c->zcMcMode, zcAgEnv = c->zcAgMcMode;
   const int zcMc = ((zcMcEnv == 2 || (zcMcEnv == 1 && n > 2)) ? 1 : 0) | ((zcAgEnv == 2 || (zcAgEnv == 1 && n > 2)) ? 2 : 0);
   a.sendSeg = a.recvSeg = FCX_SEG_NONE;
   bool zc = false;
@@ -708,6 +710,39 @@ flagcxResult_t flagcxTunerPin(flagcxComm_t comm, const char *kind, int nctas) {
   if (k < 0) return flagcxInvalidArgument;
   Plan p{k, std::max(1, nctas)};
   comm->tuner->pin(&p);
+  return flagcxSuccess;
+}
+
+// Every variant that can legally serve a call, best first by the cost model (for tuning tools).
+flagcxResult_t flagcxTunerCandidates(flagcxComm_t comm, flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red,
+                                     int zeroCopy, int maxOut, int *kinds, int *nctas, int *count) {
+  if (!validComm(comm) || !kinds || !nctas || !count || maxOut < 1 || !comm->tuner) return flagcxInvalidArgument;
+  std::vector<Plan> c = comm->tuner->candidates(op, std::max<size_t>(bytes, 1), dt, red, false, zeroCopy != 0);
+  std::stable_sort(c.begin(), c.end(), [&](const Plan &a, const Plan &b) {
+    return comm->tuner->estimate(a, op, bytes, dt) < comm->tuner->estimate(b, op, bytes, dt);
+  });
+  *count = (int)std::min<size_t>(c.size(), (size_t)maxOut);
+  for (int i = 0; i < *count; i++) { kinds[i] = c[i].kind; nctas[i] = c[i].nctas; }
+  return flagcxSuccess;
+}
+const char *flagcxKindName(int kind) { return kindName(kind); }
+
+flagcxResult_t flagcxTunerPinEx(flagcxComm_t comm, const char *kind, int nctas, unsigned int pipeBytes) {
+  if (!validComm(comm)) return flagcxInvalidArgument;
+  if (!kind) { comm->tuner->pin(nullptr); return flagcxSuccess; }
+  int k = kindFromName(kind);
+  if (k < 0) return flagcxInvalidArgument;
+  Plan p{k, std::max(1, nctas), pipeBytes};
+  comm->tuner->pin(&p);
+  return flagcxSuccess;
+}
+
+flagcxResult_t flagcxTunerRecordEx(flagcxComm_t comm, flagcxCommOp_t op, size_t bytes, const char *kind, int nctas, unsigned int pipeBytes,
+                                   double us) {
+  if (!validComm(comm) || !kind) return flagcxInvalidArgument;
+  int k = kindFromName(kind);
+  if (k < 0) return flagcxInvalidArgument;
+  comm->tuner->record(op, bytes, Plan{k, nctas, pipeBytes}, us);
   return flagcxSuccess;
 }
 

@@ -8,6 +8,7 @@
 #include <cstring>
 #include <set>
 #include <cuda_runtime.h>
+#include <dlfcn.h>
 #include <unistd.h>
 
 namespace fcx {
@@ -186,7 +187,27 @@ flagcxResult_t commCreate(flagcxComm **out, int nranks, const BootstrapHandle &h
   caps.stageBytes = c->dev.stageBytes;
   caps.pipeBytes = c->dev.pipeBytes;
   caps.maxCtas = (int)std::min<int64_t>(envInt("MAX_CTAS", 128), FCX_MAX_CTAS);
+  c->zcMcMode = (int)envInt("ZC_MC", 1);
+  c->zcAgMcMode = (int)envInt("ZC_AG_MC", 1);
   c->tuner.reset(new Tuner(&c->bs, caps));
+  // Measured table shipped with the library for this GPU model and world size (written by the tuning tool on
+  // such a machine); FLAGCX_TUNER_CACHE replaces it, FLAGCX_TUNER_DEFAULTS=0 leaves the cost-model prior alone.
+  if (!c->hostOnly && !c->hostFallback && envStr("TUNER_CACHE", "").empty() && envInt("TUNER_DEFAULTS", 1) != 0) {
+    cudaDeviceProp prop;
+    Dl_info info;
+    if (cudaGetDeviceProperties(&prop, c->cudaDev) == cudaSuccess && dladdr((void *)&commCreate, &info) && info.dli_fname) {
+      std::string dir = info.dli_fname;
+      size_t slash = dir.rfind('/');
+      dir = slash == std::string::npos ? "." : dir.substr(0, slash);
+      std::string model;
+      for (const char *q = prop.name; *q; q++)
+        if (isalnum((unsigned char)*q)) model += (char)tolower((unsigned char)*q);
+      std::string path = dir + "/tuned/" + model + "_" + std::to_string(nranks) + "gpu.json";
+      if (access(path.c_str(), R_OK) == 0 && c->tuner->load(path) == flagcxSuccess)
+        FCX_INFO(SUB_TUNING, "tuner: measured table %s", path.c_str());
+    }
+    cudaGetLastError();
+  }
   flagcxComm *raw = c.release();
   *out = raw;
   { std::lock_guard<std::mutex> lk(gCommMu); gLive.insert(raw); }
@@ -645,6 +666,12 @@ flagcxResult_t flagcxTopoNvlinkCount(const char *busId, int *activeLinks, int *v
 flagcxResult_t flagcxCommGetNetOfRank(flagcxComm_t comm, int rank, char *out, size_t outBytes) {
   if (!validComm(comm) || !out || !outBytes || rank < 0 || rank >= comm->nranks) return flagcxInvalidArgument;
   snprintf(out, outBytes, "%s", rank < (int)comm->netOfRank.size() ? comm->netOfRank[rank].c_str() : "");
+  return flagcxSuccess;
+}
+
+flagcxResult_t flagcxCommSetZeroCopyMulticast(flagcxComm_t comm, int mode) {
+  if (!validComm(comm) || mode < 0 || mode > 2) return flagcxInvalidArgument;
+  comm->zcMcMode = comm->zcAgMcMode = mode;
   return flagcxSuccess;
 }
 

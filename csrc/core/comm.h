@@ -81,6 +81,8 @@ struct flagcxComm {
   uint64_t seq = 0;
   uint64_t sendChunks[FCX_MAX_RANKS] = {}, recvChunks[FCX_MAX_RANKS] = {};
   int nextSignal = 0;
+  // zero-copy kinds through the switch: 0 never, 1 from three ranks on, 2 whenever the box has a multicast alias
+  int zcMcMode = 1, zcAgMcMode = 1;
 
   std::unique_ptr<fcx::Tuner> tuner;
   flagcxCommCounters counters{};

@@ -6,6 +6,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <functional>
 #include <sstream>
 
 namespace fcx {
@@ -214,6 +215,29 @@ std::vector<Plan> Tuner::candidates(flagcxCommOp_t op, size_t bytes, flagcxDataT
   return out;
 }
 
+// The decision for a call: the entry of its exact signature, else the generic entry of its bucket.  A call
+// that may run zero-copy also looks at the staged table of the bucket and takes the faster of the two, since a
+// staged kind serves peer-visible buffers just as well.
+bool Tuner::lookup(const Key &k, const std::function<bool(const Plan &)> &legalIn, Plan *out) const {
+  // Under a CTA budget a decision that was measured with more CTAs than the budget allows says nothing about
+  // the clamped launch (a staged kind that wins with 128 CTAs loses badly with 16): such entries are skipped and
+  // the cost model, evaluated at the budget, decides.
+  auto legal = [&](const Plan &p) { return legalIn(p) && (budget_ <= 0 || p.nctas <= budget_); };
+  auto it = best_.find(k);
+  if (it != best_.end() && legal(it->second)) { *out = it->second; return true; }
+  bool have = false;
+  double bestUs = 0;
+  for (int zc = k.zc; zc >= 0; zc--) {
+    const Key g{k.op, k.log2b, zc, -1};
+    auto b = best_.find(g);
+    if (b == best_.end() || !legal(b->second)) continue;
+    auto u = bestUs_.find(g);
+    const double us = u == bestUs_.end() ? 0.0 : u->second;
+    if (!have || us < bestUs) { *out = b->second; bestUs = us; have = true; }
+  }
+  return have;
+}
+
 static int sigOf(flagcxDataType_t dt, flagcxRedOp_t red, bool cast) { return ((int)dt << 8) | ((int)red << 4) | (cast ? 1 : 0); }
 
 void Tuner::decide(const Key &k, Search &s) {
@@ -283,9 +307,9 @@ Plan Tuner::choose(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxR
   };
   if (pinned_ && legal(pin_)) return clamp(pin_);
   const Key k{(int)op, bucket(bytes), zc ? 1 : 0, sigOf(dt, red, cast)};
-  for (const Key &kk : {k, Key{k.op, k.log2b, k.zc, -1}}) {
-    auto it = best_.find(kk);
-    if (it != best_.end() && legal(it->second)) return remember(it->second);
+  {
+    Plan found;
+    if (lookup(k, legal, &found)) return remember(found);
   }
   // order by the prior
   std::sort(cands.begin(), cands.end(), [&](const Plan &a, const Plan &b) {
@@ -320,9 +344,9 @@ Plan Tuner::peek(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRed
   };
   if (pinned_ && legal(pin_)) return clamp(pin_);
   const Key k{(int)op, bucket(bytes), zc ? 1 : 0, sigOf(dt, red, cast)};
-  for (const Key &kk : {k, Key{k.op, k.log2b, k.zc, -1}}) {
-    auto it = best_.find(kk);
-    if (it != best_.end() && legal(it->second)) return clamp(it->second);
+  {
+    Plan found;
+    if (lookup(k, legal, &found)) return clamp(found);
   }
   Plan best = cands[0];
   double bestUs = 1e30;
@@ -377,7 +401,9 @@ flagcxResult_t Tuner::load(const std::string &path) {
       if (nr != caps_.nranks || k < 0) continue;
       if ((k == FCX_K_AR_NVLS || k == FCX_K_RS_NVLS || k == FCX_K_AG_NVLS) && !caps_.multicast) continue;
       Key key{op, l2, isZcKind(k) ? 1 : 0, -1};
-      best_[key] = {k, nctas};
+      unsigned int pipe = 0;
+      if (const char *pb = strstr(line, "\"pipe_bytes\":")) pipe = (unsigned int)strtoul(pb + 13, nullptr, 10);
+      best_[key] = {k, nctas, pipe};
       bestUs_[key] = us;
       loaded++;
     }
@@ -396,8 +422,10 @@ flagcxResult_t Tuner::save(const std::string &path) const {
   for (auto &kv : best_) {
     if (kv.first.sig != -1) continue;  // the per-signature entries live for the process only
     auto us = bestUs_.find(kv.first);
-    fprintf(f, "%s {\"op\": %d, \"log2_bytes\": %d, \"nranks\": %d, \"kind\": \"%s\", \"nctas\": %d, \"us\": %.3f}", first ? "" : ",\n",
+    fprintf(f, "%s {\"op\": %d, \"log2_bytes\": %d, \"nranks\": %d, \"kind\": \"%s\", \"nctas\": %d, \"us\": %.3f", first ? "" : ",\n",
             kv.first.op, kv.first.log2b, caps_.nranks, kindName(kv.second.kind), kv.second.nctas, us == bestUs_.end() ? 0.0 : us->second);
+    if (kv.second.pipeBytes) fprintf(f, ", \"pipe_bytes\": %u", kv.second.pipeBytes);
+    fprintf(f, "}");
     first = false;
   }
   fprintf(f, "\n]\n");

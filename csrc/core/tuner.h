@@ -22,6 +22,7 @@
 #include "flagcx.h"
 #include "../kernels/devcomm.h"
 #include <cuda_runtime_api.h>
+#include <functional>
 #include <map>
 #include <string>
 #include <vector>
@@ -31,6 +32,7 @@ namespace fcx {
 struct Plan {
   int kind = 0;   // FcxKind
   int nctas = 1;
+  unsigned int pipeBytes = 0;  // bytes a rank sends per pipeline sub-chunk of a staged kind (0: the communicator's setting)
 };
 
 struct TunerCaps {
@@ -106,6 +108,7 @@ class Tuner {
   };
   static int bucket(size_t bytes);
   void decide(const Key &k, Search &s);
+  bool lookup(const Key &k, const std::function<bool(const Plan &)> &legal, Plan *out) const;
 
   Bootstrap *bs_;
   TunerCaps caps_;

@@ -81,10 +81,25 @@ flagcxResult_t flagcxTunerSave(flagcxComm_t comm, const char *path);
 flagcxResult_t flagcxTunerLoad(flagcxComm_t comm, const char *path);
 /* Force the variant of subsequent calls ("ar_twoshot", 32); kind NULL clears. */
 flagcxResult_t flagcxTunerPin(flagcxComm_t comm, const char *kind, int nctas);
+/* For tuning tools: every kernel variant (kind, CTA count) that can legally serve a call, the cost model's
+ * favourite first; the name of a kind; pin / record with an explicit pipeline sub-chunk size for the staged
+ * kinds (0 = the communicator's FLAGCX_PIPE_BYTES). */
+flagcxResult_t flagcxTunerCandidates(flagcxComm_t comm, flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red,
+                                     int zeroCopy, int maxOut, int *kinds, int *nctas, int *count);
+const char *flagcxKindName(int kind);
+flagcxResult_t flagcxTunerPinEx(flagcxComm_t comm, const char *kind, int nctas, unsigned int pipeBytes);
+flagcxResult_t flagcxTunerRecordEx(flagcxComm_t comm, flagcxCommOp_t op, size_t bytes, const char *kind, int nctas,
+                                   unsigned int pipeBytes, double us);
+
 /* Upper bound on the CTAs any collective of this communicator launches (0 lifts it).  For callers that run
  * collectives beside compute kernels (gradient buckets during the backward pass): a collective that takes
  * every SM stalls the kernels it was meant to overlap.  Every rank must set the same value. */
 flagcxResult_t flagcxCommSetCtaBudget(flagcxComm_t comm, int maxCtas);
+/* Whether the zero-copy kinds of this communicator go through the switch (multimem): 0 never, 1 from three
+ * ranks on (the default; FLAGCX_ZC_MC), 2 whenever the box has a multicast alias.  With two ranks the switch
+ * moves more bytes than a plain exchange, but it does the reduction, which suits a caller that runs its
+ * collectives under a small CTA budget.  Every rank must set the same value. */
+flagcxResult_t flagcxCommSetZeroCopyMulticast(flagcxComm_t comm, int mode);
 /* Writes a NUL-terminated description of the plan that would run. */
 flagcxResult_t flagcxTunerQuery(flagcxComm_t comm, flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, flagcxRedOp_t red,
                                 char *kindOut, size_t kindOutBytes, int *nctas, double *estimateUs);

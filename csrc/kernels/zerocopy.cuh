@@ -97,6 +97,48 @@ __device__ __forceinline__ void zcFenceBeforeClose() { __threadfence_system(); }
 
 // ---------------------------------------------------------------- reducing kinds
 
+// Units [first, first + cnt) of the range, U at a time per thread, for exactly P ranks: all U x P loads are
+// issued before anything is combined.  Returns how many units were handled (a multiple of U x gstride); the
+// caller finishes the rest.
+template <typename TIn, typename TOut, int U, int P>
+__device__ __forceinline__ size_t zcReduceBulk(const FcxDevComm &dc, const FcxCollArgs &a, const char *const *src, char *const *dst, int nd,
+                                               size_t first, size_t cnt, size_t gtid, size_t gstride) {
+  using Acc = typename Elem<TIn>::Acc;
+  constexpr int G = 16 / (int)sizeof(TIn);
+  const size_t batches = cnt / ((size_t)U * gstride);
+  const char *s[P];
+#pragma unroll
+  for (int p = 0; p < P; p++) s[p] = src[p];
+  for (size_t b = 0; b < batches; b++) {
+    const size_t u0 = first + b * U * gstride + gtid;
+    uint4 raw[U * P];
+#pragma unroll
+    for (int i = 0; i < U; i++)
+#pragma unroll
+      for (int p = 0; p < P; p++) raw[i * P + p] = ld16(s[p] + (u0 + i * gstride) * 16);
+#pragma unroll
+    for (int i = 0; i < U; i++) {
+      Acc acc[G];
+#pragma unroll
+      for (int p = 0; p < P; p++) {
+        union { uint4 v; TIn t[G]; } w;
+        w.v = raw[i * P + p];
+#pragma unroll
+        for (int e = 0; e < G; e++) {
+          const Acc x = Elem<TIn>::up(w.t[e]);
+          acc[e] = p == 0 ? x : applyOp<Acc>(acc[e], x, a.redop);
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < G; e++) acc[e] = finish<Acc>(acc[e], a.redop, P, a.scale);
+      uint4 packed;
+      packUnit<TIn, G>(acc, &packed);
+      for (int k = 0; k < nd; k++) st16(dst[k] + (u0 + i * gstride) * 16, packed);
+    }
+  }
+  return batches * U * gstride;
+}
+
 // out = finish(x_0 (op) x_1 ... (op) x_{n-1}) for `nElems` elements that start `srcOff` elements into every
 // rank's send buffer.  The result goes `dstOff` elements into: this rank's recv buffer (toSelf), every other
 // rank's recv buffer (toPeers), or both.  Ranks are combined in rank order, so the owner's result is the one
@@ -158,6 +200,22 @@ __device__ __forceinline__ void zcReduceRange(const FcxDevComm &dc, const FcxCol
           for (int k = 0; k < nd; k++) st16(dst[k] + u * 16, f);
       }
       firstPlain = nfull;  // at most one ragged unit is left for the plain path
+    }
+  }
+
+  // Plain loads from peers are latency-bound (a load over NVLink takes microseconds): the aligned bulk of the
+  // range keeps U units x P ranks = about sixteen 16-byte loads per thread in flight before it combines any.
+  if constexpr (ESI == ESO && Mm<TIn>::ok) {  // the floating-point types of gradients and activations
+    if (alS && alD) {
+      const size_t nfull = nElems / G;
+      if (nfull > firstPlain) {
+        const size_t cnt = nfull - firstPlain;
+        size_t did = 0;
+        if (n == 2) did = zcReduceBulk<TIn, TOut, 8, 2>(dc, a, src, dst, nd, firstPlain, cnt, gtid, gstride);
+        else if (n == 4) did = zcReduceBulk<TIn, TOut, 4, 4>(dc, a, src, dst, nd, firstPlain, cnt, gtid, gstride);
+        else if (n == 8) did = zcReduceBulk<TIn, TOut, 2, 8>(dc, a, src, dst, nd, firstPlain, cnt, gtid, gstride);
+        firstPlain += did;  // whole batches only: the remainder takes the unit-at-a-time path below
+      }
     }
   }
 

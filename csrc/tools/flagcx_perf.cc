@@ -13,7 +13,9 @@
 // Options: -o op (allreduce allgather reducescatter alltoall alltoallv broadcast reduce gather scatter sendrecv)
 //   -g ranks  -b min bytes  -e max bytes  -f factor  -w warm-up iterations  -n timed iterations
 //   -p 1 print the first values  -r root (-1: every root in turn)  -R 1 buffers from flagcxMemAlloc + flagcxCommRegister
-//   -d dtype (float bf16 half uint8)  -c 1 check results against a host computation  -J file append JSON lines
+//   -d dtype (float bf16 half fp8 uint8)  -O reduction (sum max min avg)  -c 1 check results against a host computation
+//   -J file append JSON lines  -T 1 tune: time every kernel variant of every (op, size) first and record the fastest
+//   (this repository's library only)  -S file write the tuned table there (load it with FLAGCX_TUNER_CACHE)
 // Sizes follow the reference: the size is the whole buffer; all-gather, reduce-scatter, all-to-all, gather and scatter
 // move size/ranks per rank.  Reported: device time (CUDA events around the -n calls), MAX over ranks, and the
 // reference-style host-timed mean over ranks; bus-bandwidth factors as in the reference's tests.
@@ -58,6 +60,12 @@ struct Api {
   flagcxResult_t (*Recv)(void *, size_t, flagcxDataType_t, int, flagcxComm_t, flagcxStream_t);
   flagcxResult_t (*GroupStart)(flagcxComm_t);
   flagcxResult_t (*GroupEnd)(flagcxComm_t);
+  // extensions of this repository's library (absent from the reference's): needed by the tune mode only
+  flagcxResult_t (*TunerCandidates)(flagcxComm_t, flagcxCommOp_t, size_t, flagcxDataType_t, flagcxRedOp_t, int, int, int *, int *, int *) = nullptr;
+  const char *(*KindName)(int) = nullptr;
+  flagcxResult_t (*TunerPinEx)(flagcxComm_t, const char *, int, unsigned int) = nullptr;
+  flagcxResult_t (*TunerRecordEx)(flagcxComm_t, flagcxCommOp_t, size_t, const char *, int, unsigned int, double) = nullptr;
+  flagcxResult_t (*TunerSave)(flagcxComm_t, const char *) = nullptr;
 };
 
 template <typename F>
@@ -93,6 +101,11 @@ bool loadApi(const char *path, Api *a) {
   ok &= sym(h, "flagcxRecv", &a->Recv);
   ok &= sym(h, "flagcxGroupStart", &a->GroupStart);
   ok &= sym(h, "flagcxGroupEnd", &a->GroupEnd);
+  a->TunerCandidates = (decltype(a->TunerCandidates))dlsym(h, "flagcxTunerCandidates");
+  a->KindName = (decltype(a->KindName))dlsym(h, "flagcxKindName");
+  a->TunerPinEx = (decltype(a->TunerPinEx))dlsym(h, "flagcxTunerPinEx");
+  a->TunerRecordEx = (decltype(a->TunerRecordEx))dlsym(h, "flagcxTunerRecordEx");
+  a->TunerSave = (decltype(a->TunerSave))dlsym(h, "flagcxTunerSave");
   return ok;
 }
 
@@ -108,8 +121,8 @@ size_t parseSize(const char *s) {
 }
 
 struct Opts {
-  std::string op = "allreduce", lib, dtype = "float", json;
-  int ranks = 0, warm = 5, iters = 20, print = 0, root = 0, reg = 0, check = 0, splitMask = 0;
+  std::string op = "allreduce", lib, dtype = "float", json, redop = "sum", tuneOut;
+  int ranks = 0, warm = 5, iters = 20, print = 0, root = 0, reg = 0, check = 0, splitMask = 0, tune = 0;
   size_t minB = 8, maxB = 128u << 20;
   double factor = 2;
 };
@@ -171,9 +184,12 @@ int worker(const Opts &o, int rank, int n, int idRead, int idWrite[], int outFd)
   flagcxStream_t st;
   if (hg->devHandle->streamCreate(&st) != flagcxSuccess) return 5;
   cudaStream_t cs = *(cudaStream_t *)st;  // the wrapper's only member
+  cudaStream_t cs_ = cs;
 
-  const bool isBf16 = o.dtype == "bf16", isHalf = o.dtype == "half", isU8 = o.dtype == "uint8";
-  const flagcxDataType_t dt = isBf16 ? flagcxBfloat16 : isHalf ? flagcxHalf : isU8 ? flagcxUint8 : flagcxFloat;
+  const bool isBf16 = o.dtype == "bf16", isHalf = o.dtype == "half", isFp8 = o.dtype == "fp8", isU8 = o.dtype == "uint8" || isFp8;
+  // fp8 (e4m3) is data type 10 of this library; the reference has no such type and moves fp8 as bytes
+  const flagcxDataType_t dt = isBf16 ? flagcxBfloat16 : isHalf ? flagcxHalf : isFp8 ? (flagcxDataType_t)10 : isU8 ? flagcxUint8 : flagcxFloat;
+  const flagcxRedOp_t red = o.redop == "max" ? flagcxMax : o.redop == "min" ? flagcxMin : o.redop == "avg" ? flagcxAvg : flagcxSum;
   const size_t es = (isBf16 || isHalf) ? 2 : isU8 ? 1 : 4;
   void *send = nullptr, *recv = nullptr, *hs = nullptr, *hr = nullptr;
   const size_t cap = std::max<size_t>(o.maxB, 64);
@@ -195,6 +211,7 @@ int worker(const Opts &o, int rank, int n, int idRead, int idWrite[], int outFd)
       if (es == 4) ((float *)host.data())[i] = v;
       else if (isBf16) { uint32_t u; memcpy(&u, &v, 4); ((uint16_t *)host.data())[i] = (uint16_t)(u >> 16); }
       else if (isHalf) ((uint16_t *)host.data())[i] = v == 0 ? 0 : (uint16_t)0;  // half only times; values unused
+      else if (isFp8) host[i] = (char)(0x30 + ((i + rank) % 8));  // e4m3 codes of 0.5 .. 0.9375: sums stay finite
       else host[i] = (char)((i + rank) % 10);
     }
     cudaMemcpy(send, host.data(), cap, cudaMemcpyHostToDevice);
@@ -215,13 +232,13 @@ int worker(const Opts &o, int rank, int n, int idRead, int idWrite[], int outFd)
     std::vector<size_t> cnt(n, count), dsp(n);
     for (int i = 0; i < n; i++) dsp[i] = i * count;
     auto call = [&](int root) {
-      if (opn == "allreduce") CK(api.AllReduce(send, recv, count, dt, flagcxSum, comm, st));
+      if (opn == "allreduce") CK(api.AllReduce(send, recv, count, dt, red, comm, st));
       else if (opn == "allgather") CK(api.AllGather(send, recv, count, dt, comm, st));
-      else if (opn == "reducescatter") CK(api.ReduceScatter(send, recv, count, dt, flagcxSum, comm, st));
+      else if (opn == "reducescatter") CK(api.ReduceScatter(send, recv, count, dt, red, comm, st));
       else if (opn == "alltoall") CK(api.AlltoAll(send, recv, count, dt, comm, st));
       else if (opn == "alltoallv") CK(api.AlltoAllv(send, cnt.data(), dsp.data(), recv, cnt.data(), dsp.data(), dt, comm, st));
       else if (opn == "broadcast") CK(api.Broadcast(send, recv, count, dt, root, comm, st));
-      else if (opn == "reduce") CK(api.Reduce(send, recv, count, dt, flagcxSum, root, comm, st));
+      else if (opn == "reduce") CK(api.Reduce(send, recv, count, dt, red, root, comm, st));
       else if (opn == "gather") CK(api.Gather(send, recv, count, dt, root, comm, st));
       else if (opn == "scatter") CK(api.Scatter(send, recv, count, dt, root, comm, st));
       else if (opn == "sendrecv") {
@@ -234,6 +251,79 @@ int worker(const Opts &o, int rank, int n, int idRead, int idWrite[], int outFd)
     int iters = size <= (256u << 20) ? o.iters : std::max(5, o.iters / 4);
     double devUs = 0, hostUs = 0;
     int bad = 0;
+    if (o.tune && api.TunerCandidates && api.TunerPinEx && api.TunerRecordEx && api.KindName && opn != "sendrecv" && opn != "alltoallv") {
+      // Tune mode: time every legal variant of this call (kind x CTA count, then sub-chunk sizes for the best
+      // staged kind), let the ranks agree on the slowest rank's time per variant, record the fastest.
+      const flagcxCommOp_t cop = opn == "allreduce" ? flagcxCommOpAllReduce : opn == "allgather" ? flagcxCommOpAllGather
+                                 : opn == "reducescatter" ? flagcxCommOpReduceScatter : opn == "alltoall" ? flagcxCommOpAlltoAll
+                                 : opn == "broadcast" ? flagcxCommOpBroadcast : opn == "reduce" ? flagcxCommOpReduce
+                                 : opn == "gather" ? flagcxCommOpGather : flagcxCommOpScatter;
+      const size_t keyBytes = count * es;
+      int kinds[64], ctas[64], nc = 0;
+      CK(api.TunerCandidates(comm, cop, keyBytes, dt, red, o.reg, 64, kinds, ctas, &nc));
+      struct Cand { int kind, ctas; unsigned pipe; };
+      std::vector<Cand> cands;
+      for (int i = 0; i < nc; i++) cands.push_back({kinds[i], ctas[i], 0u});
+      static float *agree = nullptr;  // device scratch for the cross-rank agreement
+      if (!agree) cudaMalloc(&agree, 256 * sizeof(float));
+      const int tIters = std::max(3, std::min(o.iters, size <= (64u << 20) ? 10 : 4));
+      auto timeAll = [&](std::vector<Cand> &cs, std::vector<float> &us) {
+        us.assign(cs.size(), 0.f);
+        for (size_t i = 0; i < cs.size(); i++) {
+          CK(api.TunerPinEx(comm, api.KindName(cs[i].kind), cs[i].ctas, cs[i].pipe));
+          for (int w = 0; w < 2; w++) call(roots[0]);
+          cudaEvent_t e0, e1;
+          cudaEventCreate(&e0);
+          cudaEventCreate(&e1);
+          cudaEventRecord(e0, cs_);
+          for (int k = 0; k < tIters; k++) call(roots[0]);
+          cudaEventRecord(e1, cs_);
+          cudaStreamSynchronize(cs_);
+          float ms = 0;
+          cudaEventElapsedTime(&ms, e0, e1);
+          us[i] = ms * 1e3f / tIters;
+          cudaEventDestroy(e0);
+          cudaEventDestroy(e1);
+        }
+        CK(api.TunerPinEx(comm, nullptr, 0, 0));
+        // the slowest rank's time decides (max over ranks), computed by the library itself
+        cudaMemcpyAsync(agree, us.data(), us.size() * sizeof(float), cudaMemcpyHostToDevice, cs_);
+        CK(api.AllReduce(agree, agree, us.size(), flagcxFloat, flagcxMax, comm, st));
+        cudaMemcpyAsync(us.data(), agree, us.size() * sizeof(float), cudaMemcpyDeviceToHost, cs_);
+        cudaStreamSynchronize(cs_);
+      };
+      std::vector<float> us;
+      timeAll(cands, us);
+      size_t best = 0;
+      for (size_t i = 1; i < cands.size(); i++) if (us[i] < us[best]) best = i;
+      Cand win = cands[best];
+      float winUs = us[best];
+      if (keyBytes >= (32u << 20)) {
+        // sub-chunk size only matters to the staged, pipelined kinds: try two more sizes on the best of them
+        size_t bs = cands.size();
+        for (size_t i = 0; i < cands.size(); i++) {
+          std::string kn = api.KindName(cands[i].kind);
+          bool staged = kn.find("_zc") == std::string::npos && kn.find("_ll") == std::string::npos && kn != "ar_oneshot";
+          if (staged && (bs == cands.size() || us[i] < us[bs])) bs = i;
+        }
+        if (bs < cands.size()) {
+          std::vector<Cand> more = {{cands[bs].kind, cands[bs].ctas, 4u << 20}, {cands[bs].kind, cands[bs].ctas, 64u << 20}};
+          std::vector<float> us2;
+          timeAll(more, us2);
+          for (size_t i = 0; i < more.size(); i++) {
+            CK(api.TunerRecordEx(comm, cop, keyBytes, api.KindName(more[i].kind), more[i].ctas, more[i].pipe, us2[i]));
+            if (us2[i] < winUs) { win = more[i]; winUs = us2[i]; }
+          }
+        }
+      }
+      for (size_t i = 0; i < cands.size(); i++)
+        CK(api.TunerRecordEx(comm, cop, keyBytes, api.KindName(cands[i].kind), cands[i].ctas, cands[i].pipe, us[i]));
+      if (rank == 0) {
+        printf("tune %-13s %12zu B  -> %-10s x%-3d pipe %-9u %9.2f us   (prior's pick %s x%d: %.2f us; %d variants)\n", opn.c_str(), nbytes,
+               api.KindName(win.kind), win.ctas, win.pipe, winUs, api.KindName(cands[0].kind), cands[0].ctas, us[0], (int)cands.size());
+        fflush(stdout);
+      }
+    }
     for (int root : roots) {
       for (int i = 0; i < o.warm; i++) call(root);
       cudaStreamSynchronize(cs);
@@ -253,7 +343,7 @@ int worker(const Opts &o, int rank, int n, int idRead, int idWrite[], int outFd)
       hostUs += std::chrono::duration<double, std::micro>(t1 - t0).count() / iters / roots.size();
       cudaEventDestroy(e0);
       cudaEventDestroy(e1);
-      if (o.check && es != 1 && !isHalf && (opn == "allreduce" || opn == "allgather" || opn == "reducescatter" || opn == "alltoall")) {
+      if (o.check && es != 1 && !isHalf && red == flagcxSum && (opn == "allreduce" || opn == "allgather" || opn == "reducescatter" || opn == "alltoall")) {
         size_t outElems = opn == "allreduce" ? count : opn == "reducescatter" ? count : count * n;
         outElems = std::min<size_t>(outElems, 1 << 20);
         std::vector<char> h(outElems * es);
@@ -282,6 +372,7 @@ int worker(const Opts &o, int rank, int n, int idRead, int idWrite[], int outFd)
   }
   }
   CK(api.Barrier(comm, st));
+  if (o.tune && !o.tuneOut.empty() && api.TunerSave && rank == 0) CK(api.TunerSave(comm, o.tuneOut.c_str()));
   if (o.reg) {
     api.CommDeregister(comm, hs);
     api.CommDeregister(comm, hr);
@@ -325,6 +416,9 @@ int main(int argc, char **argv) {
     else if (k == "-d") o.dtype = v;
     else if (k == "-c") o.check = atoi(v);
     else if (k == "-J") o.json = v;
+    else if (k == "-O") o.redop = v;
+    else if (k == "-T") o.tune = atoi(v);
+    else if (k == "-S") o.tuneOut = v;
     else { fprintf(stderr, "unknown option %s\n", k.c_str()); return 1; }
   }
   if (o.lib.empty()) {

@@ -30,6 +30,32 @@ static at::Tensor gemmNT(const at::Tensor &a, const at::Tensor &b, at::Tensor &e
   return c;
 }
 
+// General form on the tcgen05 path.  a_mn / b_mn say how an operand is stored: False = [M,K] / [N,K] (K contiguous),
+// True = [K,M] / [K,N] (the operand is read transposed where it lies).  So, for y = x w^T with x [T,I], w [O,I]:
+//   forward   y  = gemm(x,  w,  False, False, bias)      [T,O]
+//   dgrad     dx = gemm(dy, w,  False, True)              [T,I]   (w is [K=O, N=I])
+//   wgrad     dw = gemm(dy, x,  True,  True)              [O,I]   (dy is [K=T, M=O], x is [K=T, N=I])
+// split_k = 0 lets the launcher cut K when the output has too few tiles to fill the GPU (wgrad: K = tokens).
+static at::Tensor gemmEx(const at::Tensor &a, const at::Tensor &b, bool aMN, bool bMN, const c10::optional<at::Tensor> &bias, int64_t splitK,
+                         at::Tensor &err) {
+  checkMat(a, "a");
+  checkMat(b, "b");
+  const int64_t M = aMN ? a.size(1) : a.size(0), Ka = aMN ? a.size(0) : a.size(1);
+  const int64_t N = bMN ? b.size(1) : b.size(0), Kb = bMN ? b.size(0) : b.size(1);
+  TORCH_CHECK(Ka == Kb, "inner dimensions differ: ", Ka, " vs ", Kb);
+  const void *biasPtr = nullptr;
+  if (bias.has_value() && bias->defined()) {
+    TORCH_CHECK(bias->is_cuda() && bias->scalar_type() == at::kBFloat16 && bias->is_contiguous() && bias->numel() == N, "bias must be bf16 [N]");
+    biasPtr = bias->data_ptr();
+  }
+  c10::cuda::CUDAGuard g(a.device());
+  auto c = at::empty({M, N}, a.options());
+  auto e = fcxGemmBf16Ex(a.data_ptr(), b.data_ptr(), c.data_ptr(), (int)M, (int)N, (int)Ka, (int)a.stride(0), (int)b.stride(0), (int)c.stride(0),
+                         aMN ? 1 : 0, bMN ? 1 : 0, biasPtr, (int)splitK, err.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(e == cudaSuccess, "tcgen05 GEMM launch failed: ", cudaGetErrorString(e));
+  return c;
+}
+
 // y[M,N] = all_gather(x_local)[M,K] @ w[N,K]^T.  gathered: heap tensor [M,K]; flags: heap int64 tensor [M/128];
 // epoch: 1-based use count of this (gathered, flags) pair.
 static at::Tensor agGemm(uint64_t comm, const at::Tensor &xLocal, at::Tensor &gathered, at::Tensor &flags, const at::Tensor &w,
@@ -116,6 +142,8 @@ void bindGemm(py::module &m) {
   m.def("quant_fp8_weight", &quantFp8Weight);
   m.def("gemm_fp8_nt", &gemmFp8NT, "block-scaled e4m3 GEMM (1x128 activation scales, 128x128 weight scales) on tcgen05");
   m.def("gemm_nt", &gemmNT, "bf16 a[M,K] @ b[N,K]^T on tcgen05");
+  m.def("gemm", &gemmEx, py::arg("a"), py::arg("b"), py::arg("a_mn") = false, py::arg("b_mn") = false, py::arg("bias") = py::none(),
+        py::arg("split_k") = 0, py::arg("err"), "bf16 GEMM on tcgen05 with either operand read K-major or MN-major, optional bias row");
   m.def("ag_gemm", &agGemm);
   m.def("gemm_rs", &gemmRs);
 }

@@ -56,9 +56,11 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment s
 constexpr int THREADS = 256;
 
 // Instruction descriptor: D fp32, A/B bf16, both K-major, M = 128, N = 256.
-__device__ __forceinline__ uint32_t instrDesc(int bn) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+__device__ __forceinline__ uint32_t instrDesc(int bn, int aMN = 0, int bMN = 0) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(aMN ? 1 : 0) << 15) | ((uint32_t)(bMN ? 1 : 0) << 16) |
+         ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
+constexpr int MN_BLOCK_BYTES = 64 * BK * 2;  // one 64-column block of an MN-major tile: BK lines of 128 bytes
 
 // Tile t of this CTA's sequence -> (row block, column block).  Row blocks are
 // visited in rotated order so that (AG) the local block comes first and (RS)
@@ -133,7 +135,10 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
   const int Mrows = p.mPtr ? min(*p.mPtr, p.M) : p.M;  // the row count may live on the device
   const int bn = p.bn;  // columns per tile: 256, or 128 when that fills the SMs better
   const int nN = (p.N + bn - 1) / bn, nM = (Mrows + BM - 1) / BM;
-  const int nTiles = nN * nM, nK = (p.K + BK - 1) / BK;
+  const int nK = (p.K + BK - 1) / BK;
+  const int splitK = (MODE == FCX_GEMM_PLAIN && p.splitK > 1) ? p.splitK : 1;
+  const int kPer = (nK + splitK - 1) / splitK;  // K blocks per split
+  const int nTiles = nN * nM * splitK;
   const int gemmCtas = (MODE == FCX_GEMM_AG) ? p.gemmCtas : gridDim.x;
 
   if (threadIdx.x == 0) {
@@ -158,7 +163,8 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
       bool ok = true;
       for (int t = blockIdx.x; t < nTiles && ok; t += gemmCtas) {
         int mb, nb;
-        tileCoord(p, nM, t, &mb, &nb);
+        tileCoord(p, nM, t / splitK, &mb, &nb);
+        const int kLo = (t % splitK) * kPer, kHi = min(nK, kLo + kPer);
         const CUtensorMap *mapA = &tmA;
         int rowA = mb * BM;
         if (MODE == FCX_GEMM_AG) {
@@ -175,12 +181,21 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
             asm volatile("fence.proxy.async;" ::: "memory");  // remote generic-proxy writes -> this CTA's TMA reads
           }
         }
-        for (int kb = 0; kb < nK; kb++) {
+        for (int kb = kLo; kb < kHi; kb++) {
           if (!mbarWait(&emptyBar[stage], phase ^ 1, err)) { ok = false; break; }
           mbarExpectTx(&fullBar[stage], A_BYTES + bn * BK * 2);
           uint8_t *sa = tiles + stage * STAGE_BYTES, *sb = sa + A_BYTES;
-          tmaLoad2d(sa, mapA, kb * BK, rowA, &fullBar[stage]);
-          tmaLoad2d(sb, &tmB, kb * BK, nb * bn, &fullBar[stage]);
+          if (MODE == FCX_GEMM_PLAIN && p.aMN) {
+            // stored [K, M]: two blocks of 64 columns (M) x BK lines (K)
+            for (int j = 0; j < BM / 64; j++) tmaLoad2d(sa + j * MN_BLOCK_BYTES, mapA, rowA + j * 64, kb * BK, &fullBar[stage]);
+          } else {
+            tmaLoad2d(sa, mapA, kb * BK, rowA, &fullBar[stage]);
+          }
+          if (MODE == FCX_GEMM_PLAIN && p.bMN) {
+            for (int j = 0; j < bn / 64; j++) tmaLoad2d(sb + j * MN_BLOCK_BYTES, &tmB, nb * bn + j * 64, kb * BK, &fullBar[stage]);
+          } else {
+            tmaLoad2d(sb, &tmB, kb * BK, nb * bn, &fullBar[stage]);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -191,19 +206,24 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
       int stage = 0, buf = 0;
       uint32_t phase = 0, accPhase = 0;
       bool ok = true;
-      const uint32_t idesc = instrDesc(bn);
+      const bool aMN = MODE == FCX_GEMM_PLAIN && p.aMN, bMN = MODE == FCX_GEMM_PLAIN && p.bMN;
+      const uint32_t idesc = instrDesc(bn, aMN, bMN);
       for (int t = blockIdx.x; t < nTiles && ok; t += gemmCtas) {
         if (!mbarWait(&tmemEmpty[buf], accPhase ^ 1, err)) break;
         fenceAfter();
         const uint32_t dTmem = tmemBase + (uint32_t)buf * bn;
-        for (int kb = 0; kb < nK; kb++) {
+        const int kLo = (t % splitK) * kPer, kHi = min(nK, kLo + kPer);
+        for (int kb = kLo; kb < kHi; kb++) {
           if (!mbarWait(&fullBar[stage], phase, err)) { ok = false; break; }
           fenceAfter();
           const uint32_t sa = smemAddr(tiles + stage * STAGE_BYTES), sb = sa + A_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / 16; k++) {
-            // 16 bf16 = 32 bytes further along K inside the 128-byte swizzle row
-            mmaF16(dTmem, smemDesc(sa + k * 32), smemDesc(sb + k * 32), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            // K-major: 16 bf16 = 32 bytes further along K inside the 128-byte swizzle row;
+            // MN-major: 16 K indices = two eight-line groups = 2048 bytes further
+            const uint64_t da = aMN ? smemDescMN(sa + k * 2048, MN_BLOCK_BYTES) : smemDesc(sa + k * 32);
+            const uint64_t db = bMN ? smemDescMN(sb + k * 2048, MN_BLOCK_BYTES) : smemDesc(sb + k * 32);
+            mmaF16(dTmem, da, db, idesc, (kb > kLo || k > 0) ? 1u : 0u);
           }
           mmaCommit(&emptyBar[stage]);  // the stage may be refilled once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -223,7 +243,8 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
     bool live = true;
     for (int t = blockIdx.x; t < nTiles; t += gemmCtas) {
       int mb, nb;
-      tileCoord(p, nM, t, &mb, &nb);
+      tileCoord(p, nM, t / splitK, &mb, &nb);
+      const bool firstSplit = (t % splitK) == 0;
       if (live) live = __all_sync(0xffffffffu, mbarWait(&tmemFull[buf], accPhase, err));
       if (live) {
         fenceAfter();
@@ -250,6 +271,14 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
           for (int h = 0; h < 2; h++) {
             tmemLd32(tmemBase + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * bn + c0 + 32 * h), r);
             tmemLdWait();
+            if (MODE == FCX_GEMM_PLAIN && p.bias != nullptr && firstSplit) {
+              // every lane holds one row and the same 32 columns: the bias loads are warp-wide broadcasts
+              const __nv_bfloat16 *bias = (const __nv_bfloat16 *)p.bias + nb * bn + c0 + 32 * h;
+              const int left = p.N - (nb * bn + c0 + 32 * h);
+#pragma unroll
+              for (int j = 0; j < 32; j++)
+                if (j < left) r[j] = __float_as_uint(__uint_as_float(r[j]) + __bfloat162float(bias[j]));
+            }
 #pragma unroll
             for (int v = 0; v < 4; v++) {
               uint4 o;
@@ -272,7 +301,13 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
                 const int4 info = p.rowInfo[row0 + rr];
                 d = (__nv_bfloat16 *)(dc.heap[info.x] + p.combineOff) + ((size_t)info.y * p.topk + info.z) * p.N + col;
               }
-              if (col + 8 <= p.N) *(uint4 *)d = o;
+              if (MODE == FCX_GEMM_PLAIN && splitK > 1) {
+                // partial result of one K piece: added into C, which the launcher zeroed
+                const uint32_t *w = (const uint32_t *)&o;
+                for (int j = 0; j < 4; j++)
+                  if (col + 2 * j + 1 < p.N || (col + 2 * j < p.N && (p.N & 1) == 0))
+                    asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(d + 2 * j), "r"(w[j]) : "memory");
+              } else if (col + 8 <= p.N) *(uint4 *)d = o;
               else {
                 const __nv_bfloat16 *e = (const __nv_bfloat16 *)&o;
                 for (int j = 0; j < 8 && col + j < p.N; j++) d[j] = e[j];
@@ -424,6 +459,36 @@ extern "C" cudaError_t fcxGemmBf16(const void *a, const void *b, void *c, int M,
   FcxDevComm dc{};
   int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
   return launch<FCX_GEMM_PLAIN>(ma, mb, p, dc, std::min(tiles, smCount()), s);
+}
+
+extern "C" cudaError_t fcxGemmBf16Ex(const void *a, const void *b, void *c, int M, int N, int K, int lda, int ldb, int ldc, int aMN, int bMN,
+                                     const void *bias, int splitK, int *errFlag, cudaStream_t s) {
+  if (K % 8 || lda % 8 || ldb % 8 || ldc % 8 || M <= 0 || N <= 0 || K <= 0) return cudaErrorInvalidValue;
+  if (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) return cudaErrorInvalidValue;
+  if ((aMN && M % 8) || (bMN && N % 8) || (bias && ((uintptr_t)bias & 1))) return cudaErrorInvalidValue;
+  CUtensorMap ma, mb;
+  const int bn = pickBn(M, N, smCount());
+  // K-major operand: rows = M (or N), box of 128 (bn) rows x 64 K; MN-major operand: rows = K, box of 64 lines x 64 columns
+  const bool okA = aMN ? makeMap(&ma, a, K, M, lda, BK) : makeMap(&ma, a, M, K, lda, BM);
+  const bool okB = bMN ? makeMap(&mb, b, K, N, ldb, BK) : makeMap(&mb, b, N, K, ldb, bn);
+  if (!okA || !okB) return cudaErrorNotSupported;
+  FcxGemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.c = c; p.ldc = ldc; p.errFlag = errFlag; p.rotate = 0; p.bn = bn; p.group = tileGroup((N + bn - 1) / bn);
+  p.aMN = aMN; p.bMN = bMN; p.bias = bias;
+  const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn), nK = (K + BK - 1) / BK;
+  if (splitK <= 0) {
+    // few tiles and a long K: cut K so that the work covers the SMs (the weight-gradient GEMMs: K = tokens)
+    splitK = 1;
+    if (tiles * 2 <= smCount() && nK >= 16) splitK = std::min(std::min(8, smCount() / tiles), nK / 8);
+  }
+  if (N % 2) splitK = 1;  // the partial results are added two columns at a time
+  p.splitK = std::max(1, std::min(splitK, nK));
+  if (p.splitK > 1) {
+    cudaError_t e = cudaMemsetAsync(c, 0, ((size_t)(M - 1) * ldc + N) * 2, s);
+    if (e != cudaSuccess) return e;
+  }
+  FcxDevComm dc{};
+  return launch<FCX_GEMM_PLAIN>(ma, mb, p, dc, std::min(tiles * p.splitK, smCount()), s);
 }
 
 extern "C" cudaError_t fcxGemmBf16DynM(const void *a, const void *b, void *c, int Mmax, const int *mPtr, int N, int K, int lda, int ldb, int ldc,

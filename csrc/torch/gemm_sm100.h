@@ -31,6 +31,13 @@ struct FcxGemmParams {
   const int4 *rowInfo;
   size_t combineOff, doneOff;
   int topk;
+  // PLAIN only.  Operand storage: 0 = K-major (A is [M,K], B is [N,K], rows contiguous along K, the default);
+  // 1 = MN-major (A is stored [K,M], B is stored [K,N]: the transposed operands of the backward GEMMs, read
+  // where they lie instead of being transposed first).
+  int aMN, bMN;
+  const void *bias;     // optional bf16 [N], added to every row of C
+  int splitK;           // > 1: the K range is cut into that many pieces worked on by different CTAs, which add their
+                        // bf16 partial results into C (zeroed by the launcher) with red.global.add
 };
 
 #ifdef __cplusplus
@@ -41,6 +48,10 @@ cudaError_t fcxAgGemmBf16(const FcxDevComm *dc, const void *aLocal, const void *
                           void *c, int M, int N, int K, int ldb, int ldc, uint64_t epoch, int commCtas, int *errFlag, cudaStream_t s);
 cudaError_t fcxGemmRsBf16(const FcxDevComm *dc, const void *a, const void *b, void *out, size_t stageOff, size_t flagOff, int M, int N, int K,
                           int lda, int ldb, int ldc, uint64_t epoch, int *errFlag, cudaStream_t s);
+// General form: operand storage per FcxGemmParams::aMN / bMN (lda / ldb = elements between the stored rows),
+// optional bias row, splitK = 0 lets the launcher pick (it splits K when the tiles would fill under half of the SMs).
+cudaError_t fcxGemmBf16Ex(const void *a, const void *b, void *c, int M, int N, int K, int lda, int ldb, int ldc, int aMN, int bMN,
+                          const void *bias, int splitK, int *errFlag, cudaStream_t s);
 // c[Mmax,N] = a[*mPtr rows, K] @ b^T with the row count read on the device.
 cudaError_t fcxGemmBf16DynM(const void *a, const void *b, void *c, int Mmax, const int *mPtr, int N, int K, int lda, int ldb, int ldc,
                             int *errFlag, cudaStream_t s);

@@ -212,6 +212,7 @@ static uint64_t commSplit(uint64_t comm, int64_t color, int64_t key, int64_t sta
 }
 static void commDestroy(uint64_t comm) { FCX_OK(flagcxCommDestroy((flagcxComm_t)(uintptr_t)comm)); }
 static void commSetCtaBudget(uint64_t comm, int64_t n) { FCX_OK(flagcxCommSetCtaBudget((flagcxComm_t)(uintptr_t)comm, (int)n)); }
+static void commSetZcMulticast(uint64_t comm, int64_t mode) { FCX_OK(flagcxCommSetZeroCopyMulticast((flagcxComm_t)(uintptr_t)comm, (int)mode)); }
 static void commPin(uint64_t comm, const std::string &kind, int64_t nctas) {
   FCX_OK(flagcxTunerPin((flagcxComm_t)(uintptr_t)comm, kind.empty() ? nullptr : kind.c_str(), (int)nctas));
 }
@@ -264,6 +265,7 @@ PYBIND11_MODULE(_flagcx_torch, m) {
         py::arg("user_bytes") = 0);
   m.def("comm_destroy", &fcxt::commDestroy);
   m.def("comm_set_cta_budget", &fcxt::commSetCtaBudget);
+  m.def("comm_set_zc_multicast", &fcxt::commSetZcMulticast);
   m.def("comm_pin", &fcxt::commPin, py::arg("comm"), py::arg("kind"), py::arg("nctas") = 16);
   m.def("comm_query", &fcxt::commQuery, py::arg("comm"), py::arg("op"), py::arg("bytes"), py::arg("like"), py::arg("zero_copy") = false);
 }

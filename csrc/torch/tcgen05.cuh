@@ -55,6 +55,20 @@ __device__ __forceinline__ uint64_t smemDesc(uint32_t addr) {
   return d;
 }
 
+// The same for an MN-major tile (the operand is stored with its M or N index contiguous): the tile is a row of
+// 64-element column blocks; inside a block every K index is one 128-byte line (64 elements of M/N), eight lines
+// form a 1024-byte swizzle atom.  Leading byte offset = distance between column blocks, stride byte offset =
+// distance between eight-line groups along K.
+__device__ __forceinline__ uint64_t smemDescMN(uint32_t addr, uint32_t blockBytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3ffff) >> 4);
+  d |= (uint64_t)((blockBytes >> 4) & 0x3fff) << 16;  // leading byte offset
+  d |= (uint64_t)(1024 >> 4) << 32;                   // stride byte offset
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
 __device__ __forceinline__ void mmaF16(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"

@@ -6,22 +6,33 @@ decoder (24 layers, d_model 1024, 16 heads, FFN 4096, vocab 50257, sequence
 model code; its documentation only describes running third-party trainers on
 top of the backend (docs/user_guide.md:137-297).
 
-Per layer the model issues: fused residual-add + LayerNorm (one kernel),
-cuBLAS GEMMs for the four projections, library attention, fused bias + GELU,
-and at the end one fused softmax-cross-entropy kernel that also leaves the
-logit gradient in place.  Parameters are bf16 views into one flat buffer so
+Per layer the model issues: fused residual-add + LayerNorm (one kernel), the
+four projections on the library's own tcgen05 GEMM (forward with the bias
+added in its epilogue, input-gradient and weight-gradient GEMMs reading their
+operands transposed in place, the weight gradient with its token reduction
+split across CTAs), attention through PyTorch's scaled_dot_product_attention
+(a library flash-attention kernel: the one contraction this framework does not
+supply itself), fused bias + GELU, and at the end one fused
+softmax-cross-entropy kernel that also leaves the logit gradient in place.
+``FLAGCX_MODEL_GEMM=library`` switches the projections back to the vendor GEMM
+for comparison.  Parameters are bf16 views into one flat buffer so
 that the optimizer and the gradient all-reduce work on contiguous memory.
 """
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from flagcx_b200.ops import add_layernorm, bias_gelu, cross_entropy
+from flagcx_b200.ops import add_layernorm, bias_gelu, cross_entropy, linear
+
+
+def _linear_fn():
+    return F.linear if os.environ.get("FLAGCX_MODEL_GEMM", "own") == "library" else linear
 
 
 @dataclass
@@ -72,15 +83,16 @@ class Block(nn.Module):
     def forward(self, x, delta):
         """x: residual stream [B, T, C]; delta: pending update not yet added."""
         B, T, C = x.shape
+        lin = _linear_fn()
         x, h = add_layernorm(x, delta, self.ln1_w, self.ln1_b)
-        qkv = F.linear(h, self.qkv_w, self.qkv_b).view(B, T, 3, self.n_head, C // self.n_head)
+        qkv = lin(h, self.qkv_w, self.qkv_b).view(B, T, 3, self.n_head, C // self.n_head)
         q, k, v = qkv.unbind(2)
         att = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
         att = att.transpose(1, 2).reshape(B, T, C)
-        a = F.linear(att, self.proj_w, self.proj_b)
+        a = lin(att, self.proj_w, self.proj_b)
         x, h = add_layernorm(x, a, self.ln2_w, self.ln2_b)
-        f = bias_gelu(F.linear(h, self.fc_w), self.fc_b)
-        return x, F.linear(f, self.out_w, self.out_b)
+        f = bias_gelu(lin(h, self.fc_w), self.fc_b)
+        return x, lin(f, self.out_w, self.out_b)
 
 
 class GPT2(nn.Module):
@@ -106,7 +118,7 @@ class GPT2(nn.Module):
         for blk in self.blocks:
             x, delta = blk(x, delta)
         _, h = add_layernorm(x, delta, self.lnf_w, self.lnf_b)
-        logits = F.linear(h.view(B * T, -1), self.wte)  # [B*T, vocab_padded]
+        logits = _linear_fn()(h.view(B * T, -1), self.wte)  # [B*T, vocab_padded]
         return cross_entropy(logits, targets, self.cfg.vocab)
 
     def num_params(self) -> int:

@@ -78,3 +78,66 @@ def fused_adamw_step(master, param, grad, m, v, *, lr, betas=(0.9, 0.999), eps=1
     ``step_dev`` (int32 device scalar) overrides ``step`` and keeps the bias
     correction exact inside a replayed CUDA graph."""
     _n().adamw_(master, param, grad, m, v, lr, betas[0], betas[1], eps, weight_decay, step, grad_scale, zero_grad, step_dev)
+
+
+# ---------------------------------------------------------------- linear layers on the tcgen05 GEMM
+
+_gemm_err = {}
+
+
+def _err_flag(device):
+    """Device int the GEMM kernels set when one of their bounded waits gives up (checked by `gemm_error`)."""
+    key = (device.type, device.index)
+    if key not in _gemm_err:
+        _gemm_err[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _gemm_err[key]
+
+
+def gemm_error(device=None) -> int:
+    """Non-zero when a tcgen05 GEMM on this device gave up waiting (reads the device flag back)."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    return int(_err_flag(device).item())
+
+
+def gemm(a, b, a_mn: bool = False, b_mn: bool = False, bias=None, split_k: int = 0):
+    """bf16 GEMM on the 5th-generation tensor cores.  ``a_mn`` / ``b_mn``: the operand is stored transposed
+    ([K, M] / [K, N]) and is read where it lies.  Returns ``[M, N]`` bf16."""
+    return _n().gemm(a, b, a_mn, b_mn, bias, split_k, _err_flag(a.device))
+
+
+class _Linear(torch.autograd.Function):
+    """y = x w^T (+ bias) with all three GEMMs (forward, input gradient, weight gradient) on the library's own
+    tcgen05 kernel: the backward operands are read transposed in place, the weight gradient splits its long
+    reduction over the tokens across CTAs, the bias gradient is the library's column-sum kernel."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias = bias is not None
+        ctx.in_shape = x.shape
+        y = gemm(x2, w, False, False, bias)
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, False, True).view(ctx.in_shape)      # [T,O] x [O,I]: w read as the [K=O, N=I] operand
+        if ctx.needs_input_grad[1]:
+            dw = gemm(dy2, x2, True, True)                           # [O,T] x [T,I]: both read transposed, K = tokens
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = _n().col_sum(dy2)
+        return dx, dw, db
+
+
+def linear(x, w, bias=None):
+    """``torch.nn.functional.linear`` for bf16 CUDA tensors on the library's tcgen05 GEMM (forward and backward).
+    Shapes the kernel cannot take (inner sizes that are not multiples of 8) raise; there is no silent fallback."""
+    return _Linear.apply(x, w, bias)

@@ -4,9 +4,11 @@ library loads with ``FLAGCX_TUNER_CACHE``.
     python -m flagcx_b200.tools.tune --gpus 8 --out tuner_8gpu.json
     FLAGCX_TUNER_CACHE=tuner_8gpu.json <any program using the library>
 
-For each (operation, message size) the sweep pins one candidate (kernel kind x CTA count) at a time with
-``FLAGCX_USE_COMM_TAG`` and times it with the perf binary (device time, max over ranks); the fastest candidate of each
-size bucket goes into the table.  The reference tunes online only and forgets the result at exit
+For each (operation, message size) every legal candidate (kernel kind x CTA count, and the pipeline sub-chunk
+size of the staged kinds at large sizes) is pinned and timed on the device, the slowest rank's time counts, and
+the fastest candidate of each size bucket goes into the table: by default inside one set of rank processes
+(the perf binary's ``-T 1`` mode, seconds for a whole sweep), with ``--per-process`` one process per candidate.
+A table named ``<gpu model>_<n>gpu.json`` under ``flagcx_b200/lib/tuned`` is loaded by default on such a machine.  The reference tunes online only and forgets the result at exit
 (flagcx/core/flagcx_tuner.cc:330-341); the online search exists here too (``FLAGCX_USE_TUNER=1``).
 """
 from __future__ import annotations
@@ -117,6 +119,26 @@ def sweep(nranks: int, ops, sizes, multicast: bool, perf_bin: Path, iters: int =
     return rows
 
 
+def tune_in_process(nranks: int, ops, min_bytes: int, max_bytes: int, factor: int, out: str, perf_bin: Path, dtype: str = "float",
+                    iters: int = 10, log=None):
+    """The fast way: the perf binary's tune mode (-T 1) times every legal variant of every (operation, size)
+    inside ONE set of rank processes, first on ordinary buffers, then on buffers from flagcxMemAlloc (which adds
+    the zero-copy kinds), and the library writes the merged table.  Returns the tool's output."""
+    env = dict(os.environ, FLAGCX_TUNER_CACHE=out, FLAGCX_TUNER_DEFAULTS="0")
+    env.setdefault("FLAGCX_HEAP_USER_BYTES", str(2 * max_bytes + (256 << 20)))
+    text = ""
+    for reg in (0, 1):
+        cmd = [str(perf_bin), "-o", ",".join(ops), "-g", str(nranks), "-d", dtype, "-b", str(min_bytes), "-e", str(max_bytes), "-f", str(factor),
+               "-w", "2", "-n", str(iters), "-T", "1", "-R", str(reg), "-S", out]
+        res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=1800)
+        text += res.stdout + res.stderr
+        if log:
+            Path(log).write_text(text)
+        if res.returncode != 0:
+            raise RuntimeError(f"tune run failed (registered={reg}): {res.stderr[-2000:]}")
+    return text
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("--gpus", type=int, required=True)
@@ -127,9 +149,17 @@ def main():
     ap.add_argument("--factor", type=int, default=4)
     ap.add_argument("--no-multicast", action="store_true", help="skip the NVLS kinds")
     ap.add_argument("--rows", help="also keep every measured row in this JSON-lines file")
+    ap.add_argument("--per-process", action="store_true", help="one perf process per variant and size (slow; isolates failures)")
+    ap.add_argument("--log", help="keep the tune run's output in this file")
     args = ap.parse_args()
     from flagcx_b200 import _build
     perf = _build.build_tools()
+    if not args.per_process:
+        ops = [o for o in args.ops.split(",") if o in OPS]
+        text = tune_in_process(args.gpus, ops, args.min_bytes, args.max_bytes, args.factor, args.out, perf, log=args.log)
+        n = sum(1 for line in text.splitlines() if line.startswith("tune "))
+        print(f"{n} (operation, size) pairs tuned; table written to {args.out}")
+        return
     sizes, s = [], args.min_bytes
     while s <= args.max_bytes:
         sizes.append(s)

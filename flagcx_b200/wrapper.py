@@ -200,6 +200,7 @@ _SIGNATURES = {
     "flagcxCommSplit": (_R, [flagcxComm_t, ctypes.c_int, ctypes.c_int, ctypes.POINTER(flagcxComm_t)]),
     "flagcxCommSplitSized": (_R, [flagcxComm_t, ctypes.c_int, ctypes.c_int, _sz, _sz, ctypes.POINTER(flagcxComm_t)]),
     "flagcxCommSetCtaBudget": (_R, [flagcxComm_t, ctypes.c_int]),
+    "flagcxCommSetZeroCopyMulticast": (_R, [flagcxComm_t, ctypes.c_int]),
     "flagcxCommHeapRetain": (_R, [flagcxComm_t]),
     "flagcxCommHeapRelease": (_R, [flagcxComm_t, _vp]),
     "flagcxTunerQueryEx": (_R, [flagcxComm_t, ctypes.c_int, _sz, flagcxDataType_t, flagcxRedOp_t, ctypes.c_int, ctypes.c_char_p, _sz,

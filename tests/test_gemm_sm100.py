@@ -104,3 +104,60 @@ def test_tensor_parallel_linears_forward_and_backward(nat, comm1):
     _close(z.detach(), zr.detach(), 1024)
     for g, r in zip(got, (xr.grad, w1r.grad, w2r.grad)):
         assert (g - r).abs().max() / (r.abs().max() + 1e-12) < 5e-2
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (1024, 3072, 8192), (384, 200, 136), (1000, 72, 24)])
+def test_gemm_with_transposed_operands(nat, a_mn, b_mn, M, N, K):
+    """The backward GEMMs of a linear layer read an operand transposed where it lies (MN-major tiles)."""
+    torch.manual_seed(2)
+    a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+    ref = _ref(a, b)
+    a_st = a.t().contiguous() if a_mn else a   # stored [K, M]
+    b_st = b.t().contiguous() if b_mn else b   # stored [K, N]
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    c = nat.gemm(a_st, b_st, a_mn, b_mn, None, 1, err)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    _close(c, ref, K)
+
+
+@pytest.mark.parametrize("split_k", [0, 2, 5])
+def test_gemm_bias_and_split_k(nat, split_k):
+    torch.manual_seed(3)
+    M, N, K = 256, 512, 4096  # 4 tiles: the launcher's own choice (split_k = 0) splits K as well
+    a = (torch.randn(M, K, device="cuda") * 0.3).bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.3).bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    c = nat.gemm(a, b, False, False, bias, split_k, err)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    _close(c, _ref(a, b) + bias.float(), K)
+    # weight-gradient shape: few tiles, K = tokens, both operands transposed
+    T, O, I = 8192, 256, 384
+    dy = (torch.randn(T, O, device="cuda") * 0.3).bfloat16()
+    x = (torch.randn(T, I, device="cuda") * 0.3).bfloat16()
+    dw = nat.gemm(dy, x, True, True, None, split_k, err)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    _close(dw, dy.float().t() @ x.float(), T)
+
+
+def test_linear_autograd_matches_pytorch(nat):
+    from flagcx_b200.ops import gemm_error, linear
+    torch.manual_seed(4)
+    B, T, I, O = 4, 256, 512, 768
+    x = (torch.randn(B, T, I, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+    w = (torch.randn(O, I, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    b = torch.randn(O, device="cuda").bfloat16().requires_grad_(True)
+    g = (torch.randn(B, T, O, device="cuda") * 0.1).bfloat16()
+    y = linear(x, w, b)
+    y.backward(g)
+    xr, wr, br = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+    yr = torch.nn.functional.linear(xr, wr, br)
+    yr.backward(g.float())
+    assert gemm_error() == 0
+    for got, ref, k in ((y, yr, I), (x.grad, xr.grad, O), (w.grad, wr.grad, B * T), (b.grad, br.grad, B * T)):
+        _close(got, ref.detach(), k)

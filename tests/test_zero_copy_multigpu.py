@@ -190,7 +190,8 @@ def _zero_copy(lib, uid, rank, world, skew):
 @pytest.mark.parametrize("mode", ["switch", "plain", "skewed"])
 def test_zero_copy_collectives(native_lib, mode):
     world = _world()
-    env = {"FLAGCX_KERNEL_TIMEOUT_MS": "20000", "FLAGCX_HEAP_USER_BYTES": str(1 << 30)}
+    # the cost model decides here (no measured table): it is what sends peer-visible buffers to the zero-copy kinds
+    env = {"FLAGCX_KERNEL_TIMEOUT_MS": "20000", "FLAGCX_HEAP_USER_BYTES": str(1 << 30), "FLAGCX_TUNER_DEFAULTS": "0"}
     if mode == "plain":
         env["FLAGCX_ZC_MC"] = "0"
     res, _ = run_ranks(_zero_copy, world, args=(mode == "skewed",), timeout=900, env=env)
@@ -287,7 +288,7 @@ def test_ddp_trainer_matches_single_process_on_the_global_batch(native_lib):
     port = s.getsockname()[1]
     s.close()
     world = _world()
-    res, _ = run_ranks(_ddp_matches_single_process, world, args=(port,), timeout=600)
+    res, _ = run_ranks(_ddp_matches_single_process, world, args=(port,), timeout=600, env={"FLAGCX_TUNER_DEFAULTS": "0"})
     for r in range(world):
         out = res[r][1]
         assert out["same"]
