@@ -159,7 +159,7 @@ static void resolveSeg(flagcxComm *c, const void *p, size_t bytes, int *seg, uin
   }
 }
 
-static bool isZcKind(int k) { return k == FCX_K_AR_ZC || k == FCX_K_RS_ZC || k == FCX_K_REDUCE_ZC || k == FCX_K_MOVE_ZC; }
+static bool isZcKind(int k) { return k == FCX_K_AR_ZC || k == FCX_K_RS_ZC || k == FCX_K_REDUCE_ZC || k == FCX_K_MOVE_ZC || k == FCX_K_MOVE_CE; }
 
 // The byte mover a collective stands for when it runs in its LL form.
 static int moveKindOf(flagcxCommOp_t op) {
@@ -260,12 +260,48 @@ flagcxResult_t launchCollective(flagcxComm *c, const PendingOp &o) {
       a.useMc = c->dev.mcHeap != nullptr ? zcMc : 0;
     }
   }
-  auto launchZc = [&](const Plan &p, bool timed) {
+  auto launchZc = [&](const Plan &p, bool timed) -> flagcxResult_t {
     a.send = send;
     a.recv = recv;
     a.count = o.count;
     a.sendStride = a.recvStride = o.count;
-    return launchOne(c, a, p, o.stream, timed);
+    if (p.kind != FCX_K_MOVE_CE) return launchOne(c, a, p, o.stream, timed);
+    // Copy-engine form (the reference's own transport also moves data with copy engines and leaves the SMs
+    // alone, flagcx/core/p2p.cc:73-109; there the CPU drives two staged copies per chunk, here the copies go
+    // straight into the peers' receive buffers between two one-CTA kernels).
+    if (a.recvSeg != FCX_SEG_HEAP) {  // only symmetric-heap receive buffers: the host must know the peers' addresses
+      Plan q{FCX_K_MOVE_ZC, std::max(1, std::min(16, c->tuner->ctaBudget() > 0 ? c->tuner->ctaBudget() : 16))};
+      return launchOne(c, a, q, o.stream, timed);
+    }
+    if (timed) c->tuner->beginTiming(o.stream);
+    c->counters.kindLaunches[FCX_K_MOVE_CE]++;
+    Plan open{FCX_K_MOVE_ZC, 1};
+    a.ceOpen = 1;
+    FCX_CHECK(launchOne(c, a, open, o.stream, false));
+    a.ceOpen = 0;
+    const size_t piece = o.count * es;
+    const int me = c->rank;
+    auto copy = [&](void *dst, const void *src) -> flagcxResult_t {
+      if (dst == src || !piece) return flagcxSuccess;
+      return cudaToResult(cudaMemcpyAsync(dst, src, piece, cudaMemcpyDeviceToDevice, o.stream), "copy-engine transfer");
+    };
+    for (int k = 0; k < n; k++) {
+      const int p = (me + k) % n;
+      char *peerRecv = p == me ? recv : c->heap.base[p] + a.recvHeapOff;
+      switch (o.op) {
+        case flagcxCommOpAllGather: FCX_CHECK(copy(peerRecv + (size_t)me * piece, send)); break;
+        case flagcxCommOpAlltoAll: FCX_CHECK(copy(peerRecv + (size_t)me * piece, send + (size_t)p * piece)); break;
+        case flagcxCommOpBroadcast: if (me == o.root) FCX_CHECK(copy(peerRecv, send)); break;
+        case flagcxCommOpScatter: if (me == o.root) FCX_CHECK(copy(peerRecv, send + (size_t)p * piece)); break;
+        default: return flagcxInternalError;
+      }
+    }
+    FcxCollArgs b = a;
+    b.count = 0;
+    Plan close{FCX_K_BARRIER, 1};
+    flagcxResult_t r = launchOne(c, b, close, o.stream, false);
+    if (timed) c->tuner->endTiming(o.stream);
+    return r;
   };
 
   if (o.op == flagcxCommOpAlltoAllv) {

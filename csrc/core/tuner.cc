@@ -13,7 +13,7 @@ namespace fcx {
 
 static const char *kKindNames[FCX_K_NUM] = {"barrier", "ar_ll", "ar_oneshot", "ar_twoshot", "ar_nvls", "rs", "rs_nvls", "ag",
                                             "ag_nvls", "bcast", "reduce", "gather", "scatter", "a2a", "a2av", "move_ll", "rs_ll", "reduce_ll",
-                                            "ar_zc", "rs_zc", "reduce_zc", "move_zc"};
+                                            "ar_zc", "rs_zc", "reduce_zc", "move_zc", "move_ce"};
 
 const char *kindName(int kind) { return kind >= 0 && kind < FCX_K_NUM ? kKindNames[kind] : "?"; }
 
@@ -74,6 +74,12 @@ double estimateUs(const Plan &p, flagcxCommOp_t op, size_t bytesIn, int, const T
     case FCX_K_REDUCE_ZC:
       if (mc) return zcFixed + std::max(b / kLinkRate, b / (c * kCtaZcMmRate));
       return zcFixed + std::max(b * (n - 1) / kLinkRate, b * (n - 1) / (c * kCtaPullRate));
+    case FCX_K_MOVE_CE: {
+      // two one-CTA kernels around copy-engine transfers queued by the host: a few microseconds per copy to
+      // start, then the link rate; no SM moves data
+      const double copies = (op == flagcxCommOpBroadcast || op == flagcxCommOpScatter) ? n - 1 : n;
+      return 2 * kLaunchUs + 2 * kBarrierUs + 4.0 * copies + b * (n - 1) / kLinkRate;
+    }
     case FCX_K_MOVE_ZC:
       switch (op) {
         case flagcxCommOpBroadcast:
@@ -180,6 +186,7 @@ std::vector<Plan> Tuner::candidates(flagcxCommOp_t op, size_t bytes, flagcxDataT
       addCtas(out, FCX_K_AG, {2, 8, 16, 32, 64, 128}, units, mx);
       if (caps_.multicast && n > 1 && bytes >= 4096) addCtas(out, FCX_K_AG_NVLS, {8, 16, 32, 64, 128}, units, mx);
       if (zc && n > 1) addCtas(out, FCX_K_MOVE_ZC, {1, 2, 4, 8, 16, 24, 32, 48, 64, 96}, units, mx);
+      if (zc && n > 1 && bytes >= (256u << 10)) out.push_back({FCX_K_MOVE_CE, 1});
       break;
     case flagcxCommOpReduce:
       if (!cast && bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_REDUCE_LL, {1, 2, 4}, units, mx);
@@ -190,6 +197,7 @@ std::vector<Plan> Tuner::candidates(flagcxCommOp_t op, size_t bytes, flagcxDataT
       if (bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_MOVE_LL, {1, 2, 4}, units, mx);
       addCtas(out, FCX_K_BCAST, {1, 4, 16, 32, 64, 128}, units, mx);
       if (zc && n > 1) addCtas(out, FCX_K_MOVE_ZC, {1, 2, 4, 8, 16, 24, 32, 48, 64, 96}, units, mx);
+      if (zc && n > 1 && bytes >= (256u << 10)) out.push_back({FCX_K_MOVE_CE, 1});
       break;
     case flagcxCommOpGather:
       if (bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_MOVE_LL, {1, 2, 4}, units, mx);
@@ -200,11 +208,13 @@ std::vector<Plan> Tuner::candidates(flagcxCommOp_t op, size_t bytes, flagcxDataT
       if (bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_MOVE_LL, {1, 2, 4}, units, mx);
       addCtas(out, FCX_K_SCATTER, {1, 4, 16, 64, 128}, units, mx);
       if (zc && n > 1) addCtas(out, FCX_K_MOVE_ZC, {1, 2, 4, 8, 16, 24, 32, 48, 64, 96}, units, mx);
+      if (zc && n > 1 && bytes >= (256u << 10)) out.push_back({FCX_K_MOVE_CE, 1});
       break;
     case flagcxCommOpAlltoAll:
       if (bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_MOVE_LL, {1, 2, 4}, units, mx);
       addCtas(out, FCX_K_A2A, {2, 8, 16, 32, 64, 128}, units, mx);
       if (zc && n > 1) addCtas(out, FCX_K_MOVE_ZC, {1, 2, 4, 8, 16, 24, 32, 48, 64, 96}, units, mx);
+      if (zc && n > 1 && bytes >= (256u << 10)) out.push_back({FCX_K_MOVE_CE, 1});
       break;
     case flagcxCommOpAlltoAllv:
       addCtas(out, FCX_K_A2AV, {2, 8, 16, 32, 64, 128}, units, mx);
@@ -374,7 +384,7 @@ void Tuner::beginTiming(cudaStream_t st) {
 
 void Tuner::endTiming(cudaStream_t st) { cudaEventRecord(ev1_, st); }
 
-static bool isZcKind(int k) { return k == FCX_K_AR_ZC || k == FCX_K_RS_ZC || k == FCX_K_REDUCE_ZC || k == FCX_K_MOVE_ZC; }
+static bool isZcKind(int k) { return k == FCX_K_AR_ZC || k == FCX_K_RS_ZC || k == FCX_K_REDUCE_ZC || k == FCX_K_MOVE_ZC || k == FCX_K_MOVE_CE; }
 
 void Tuner::record(flagcxCommOp_t op, size_t bytes, const Plan &p, double us) {
   Key k{(int)op, bucket(bytes), isZcKind(p.kind) ? 1 : 0, -1};

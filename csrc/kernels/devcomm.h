@@ -115,6 +115,10 @@ enum FcxKind : int {
   FCX_K_RS_ZC,        // every rank reduces its piece out of all send buffers into its own recv buffer
   FCX_K_REDUCE_ZC,    // the root reduces the whole vector out of all send buffers
   FCX_K_MOVE_ZC,      // all-gather / broadcast / gather / scatter / all-to-all(v) straight between user buffers
+  // Copy-engine form of the push movers on symmetric-heap buffers: a one-CTA kernel opens (barrier + check that
+  // every rank's receive buffer sits at the same heap offset), the host queues one peer copy per destination on
+  // the same stream (the copy engines move the bytes, no SM does), a one-CTA barrier kernel closes.
+  FCX_K_MOVE_CE,
   FCX_K_NUM
 };
 
@@ -122,6 +126,7 @@ struct FcxCollArgs {
   int kind;
   int dtype, redop, root;
   int elemSize;          // bytes per element (the byte-moving kinds only look at this)
+  int ceOpen;            // FCX_K_MOVE_ZC launched as the opening step of FCX_K_MOVE_CE: exchange and check, move nothing
   int useMc;             // broadcast: root stores through the multicast alias
   int moveOp;            // FCX_K_MOVE_LL: which byte mover it stands for (FCX_K_AG, _BCAST, _GATHER, _SCATTER, _A2A)
   int outDtype;          // all-reduce with fused cast: element type of recv (== dtype when unused)

@@ -361,6 +361,18 @@ __device__ void fcxZcMoveBody(const FcxDevComm &dc, const FcxCollArgs &a, int ct
     default: break;
   }
   ZcPeers z;
+  if (a.ceOpen) {
+    // Opening step of the copy-engine form: after this barrier every peer's receive buffer may be written;
+    // the host's copies assume one heap offset on all ranks, which is checked here (a mismatch is recorded as a
+    // bad argument; the copies then land at this rank's offset inside the peers' heaps, never outside them).
+    if (zcExchange(dc, a, seq, cta, false, true, 0, recvSpan, nullptr, nullptr, &z)) {
+      bool same = true;
+      for (int p = 0; p < n; p++) same = same && (p == me || z.recv[p] == dc.heap[p] + a.recvHeapOff);
+      if (!same && threadIdx.x == 0) giveUp(dc, FCX_ERR_BADARG, me, FCX_WAIT_BARRIER, cta, a.recvHeapOff, 0, seq);
+    }
+    epilogue(dc, seq, nctas);
+    return;
+  }
   if (zcExchange(dc, a, seq, cta, pull, !pull, sendSpan, recvSpan, xTo, yTo, &z)) {
     const char *send = (const char *)a.send;
     char *recv = (char *)a.recv;

@@ -52,7 +52,7 @@ static at::Tensor gemmEx(const at::Tensor &a, const at::Tensor &b, bool aMN, boo
   auto c = at::empty({M, N}, a.options());
   auto e = fcxGemmBf16Ex(a.data_ptr(), b.data_ptr(), c.data_ptr(), (int)M, (int)N, (int)Ka, (int)a.stride(0), (int)b.stride(0), (int)c.stride(0),
                          aMN ? 1 : 0, bMN ? 1 : 0, biasPtr, (int)splitK, err.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream());
-  TORCH_CHECK(e == cudaSuccess, "tcgen05 GEMM launch failed: ", cudaGetErrorString(e));
+  TORCH_CHECK(e == cudaSuccess, "tcgen05 GEMM failed: ", cudaGetErrorString(e), ": ", fcxGemmLastDetail());
   return c;
 }
 

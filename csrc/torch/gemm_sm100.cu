@@ -36,6 +36,7 @@
 #include "../kernels/prims.cuh"
 
 #include <algorithm>
+#include <cstdio>
 #include <cstdlib>
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -461,25 +462,44 @@ extern "C" cudaError_t fcxGemmBf16(const void *a, const void *b, void *c, int M,
   return launch<FCX_GEMM_PLAIN>(ma, mb, p, dc, std::min(tiles, smCount()), s);
 }
 
+// What went wrong in the last fcxGemmBf16Ex call of this thread that did not return cudaSuccess.
+static thread_local char gGemmDetail[256];
+extern "C" const char *fcxGemmLastDetail() { return gGemmDetail; }
+
 extern "C" cudaError_t fcxGemmBf16Ex(const void *a, const void *b, void *c, int M, int N, int K, int lda, int ldb, int ldc, int aMN, int bMN,
                                      const void *bias, int splitK, int *errFlag, cudaStream_t s) {
   if (K % 8 || lda % 8 || ldb % 8 || ldc % 8 || M <= 0 || N <= 0 || K <= 0) return cudaErrorInvalidValue;
   if (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) return cudaErrorInvalidValue;
   if ((aMN && M % 8) || (bMN && N % 8) || (bias && ((uintptr_t)bias & 1))) return cudaErrorInvalidValue;
+  gGemmDetail[0] = 0;
+  cudaGetLastError();  // an error left behind by an earlier, unrelated call of this thread is not this launch's
   CUtensorMap ma, mb;
   const int bn = pickBn(M, N, smCount());
   // K-major operand: rows = M (or N), box of 128 (bn) rows x 64 K; MN-major operand: rows = K, box of 64 lines x 64 columns
   const bool okA = aMN ? makeMap(&ma, a, K, M, lda, BK) : makeMap(&ma, a, M, K, lda, BM);
   const bool okB = bMN ? makeMap(&mb, b, K, N, ldb, BK) : makeMap(&mb, b, N, K, ldb, bn);
-  if (!okA || !okB) return cudaErrorNotSupported;
+  if (!okA || !okB) {
+    snprintf(gGemmDetail, sizeof gGemmDetail, "tensor map of operand %s refused (M %d N %d K %d lda %d ldb %d aMN %d bMN %d a %p b %p)",
+             !okA ? "A" : "B", M, N, K, lda, ldb, aMN, bMN, a, b);
+    return cudaErrorNotSupported;
+  }
   FcxGemmParams p{};
   p.M = M; p.N = N; p.K = K; p.c = c; p.ldc = ldc; p.errFlag = errFlag; p.rotate = 0; p.bn = bn; p.group = tileGroup((N + bn - 1) / bn);
   p.aMN = aMN; p.bMN = bMN; p.bias = bias;
   const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn), nK = (K + BK - 1) / BK;
   if (splitK <= 0) {
-    // few tiles and a long K: cut K so that the work covers the SMs (the weight-gradient GEMMs: K = tokens)
+    // Few tiles and a long K (the weight-gradient GEMMs: K = tokens): cut K so that the pieces fill whole waves.
+    // A split into s pieces takes ceil(tiles * s / SMs) waves of 1/s the length; every extra piece costs some
+    // atomic traffic, counted as 4 % of a tile.
     splitK = 1;
-    if (tiles * 2 <= smCount() && nK >= 16) splitK = std::min(std::min(8, smCount() / tiles), nK / 8);
+    if (tiles < smCount() && nK >= 32) {
+      double best = 1.0;
+      for (int sk = 2; sk <= 8 && nK / sk >= 8; sk++) {
+        const double waves = (double)((tiles * sk + smCount() - 1) / smCount());
+        const double cost = waves / sk + 0.04 * (sk - 1);
+        if (cost < best - 0.05) { best = cost; splitK = sk; }
+      }
+    }
   }
   if (N % 2) splitK = 1;  // the partial results are added two columns at a time
   p.splitK = std::max(1, std::min(splitK, nK));
@@ -488,7 +508,11 @@ extern "C" cudaError_t fcxGemmBf16Ex(const void *a, const void *b, void *c, int 
     if (e != cudaSuccess) return e;
   }
   FcxDevComm dc{};
-  return launch<FCX_GEMM_PLAIN>(ma, mb, p, dc, std::min(tiles * p.splitK, smCount()), s);
+  cudaError_t e = launch<FCX_GEMM_PLAIN>(ma, mb, p, dc, std::min(tiles * p.splitK, smCount()), s);
+  if (e != cudaSuccess)
+    snprintf(gGemmDetail, sizeof gGemmDetail, "kernel launch: %s (M %d N %d K %d aMN %d bMN %d splitK %d grid %d)", cudaGetErrorString(e), M, N,
+             K, aMN, bMN, p.splitK, std::min(tiles * p.splitK, smCount()));
+  return e;
 }
 
 extern "C" cudaError_t fcxGemmBf16DynM(const void *a, const void *b, void *c, int Mmax, const int *mPtr, int N, int K, int lda, int ldb, int ldc,

@@ -52,6 +52,7 @@ cudaError_t fcxGemmRsBf16(const FcxDevComm *dc, const void *a, const void *b, vo
 // optional bias row, splitK = 0 lets the launcher pick (it splits K when the tiles would fill under half of the SMs).
 cudaError_t fcxGemmBf16Ex(const void *a, const void *b, void *c, int M, int N, int K, int lda, int ldb, int ldc, int aMN, int bMN,
                           const void *bias, int splitK, int *errFlag, cudaStream_t s);
+const char *fcxGemmLastDetail();  // what the calling thread's last failed fcxGemmBf16Ex call tripped over
 // c[Mmax,N] = a[*mPtr rows, K] @ b^T with the row count read on the device.
 cudaError_t fcxGemmBf16DynM(const void *a, const void *b, void *c, int Mmax, const int *mPtr, int N, int K, int lda, int ldb, int ldc,
                             int *errFlag, cudaStream_t s);

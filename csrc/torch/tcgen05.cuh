@@ -131,6 +131,16 @@ inline EncodeTiledFn encodeFn() {
 inline bool makeTileMap(CUtensorMap *m, const void *base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t boxRows, int elemBytes) {
   EncodeTiledFn fn = encodeFn();
   if (!fn) return false;
+  // The encoder is a driver call and wants a context bound to the calling thread.  A thread that has made no
+  // runtime call yet has none (an autograd worker whose first CUDA work is this GEMM: the runtime binds the
+  // primary context lazily, and a framework skips cudaSetDevice when the device index already matches), and the
+  // encoder then refuses every map.  Binding once per thread is enough.
+  static thread_local bool bound = false;
+  if (!bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaSetDevice(dev);
+    bound = true;
+  }
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {ld * (uint64_t)elemBytes};
   cuuint32_t box[2] = {(cuuint32_t)(128 / elemBytes), boxRows};

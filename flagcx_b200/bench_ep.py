@@ -32,6 +32,7 @@ def main():
     ap.add_argument("--topk", type=int, default=2)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--dispatch-ctas", type=int, default=64)
+    ap.add_argument("--save-dir", default="", help="leave rank 0's output here and compare with the reference arm's, if it is there")
     args = ap.parse_args()
     rank, world, lr = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     os.environ.setdefault("FLAGCX_SOCKET_IFNAME", "lo")
@@ -104,6 +105,16 @@ def main():
         other = ep.unfused_forward(x, topk_idx, topk_w, w1, w2) if args.impl == "fused" else ep.forward(x, topk_idx, topk_w, w1, w2)
         torch.cuda.synchronize()
         agree = float(((out.float() - other.float()).abs().max() / other.float().abs().max()).item())
+    # Across arms: every arm leaves rank 0's output next to the others (same seeds, same inputs), and compares it
+    # element by element with what the reference arm left there, when that arm ran before on this machine.
+    vs_ref = None
+    if rank == 0 and args.save_dir:
+        os.makedirs(args.save_dir, exist_ok=True)
+        torch.save(out.float().cpu(), os.path.join(args.save_dir, f"ep_out_{args.impl}_{world}.pt"))
+        ref_file = os.path.join(args.save_dir, f"ep_out_reference_{world}.pt")
+        if args.impl != "reference" and os.path.exists(ref_file):
+            ref = torch.load(ref_file)
+            vs_ref = float(((out.float().cpu() - ref).abs().max() / ref.abs().max()).item())
     # rows this rank's expert processed, and bytes this rank had to send to other ranks (there and back)
     rows = torch.tensor([float((topk_idx == r).sum().item()) for r in range(world)], dtype=torch.float64)
     remote = float(rows.sum() - rows[rank]) * H * 2
@@ -118,7 +129,7 @@ def main():
     if rank == 0:
         print(json.dumps({"bench": "ep_moe_layer", "impl": args.impl, "n_gpus": world, "tokens_per_rank": T, "hidden": H, "ffn": F,
                           "topk": K, "ms": round(ms, 3), "tokens_per_s": round(world * T / ms * 1e3, 1), "roofline_ms": round(roof_ms, 3),
-                          "fraction_of_roofline": round(roof_ms / ms, 3), "checksum": float(out.float().abs().mean().item()), "max_rel_diff_vs_other_path": agree,
+                          "fraction_of_roofline": round(roof_ms / ms, 3), "checksum": float(out.float().abs().mean().item()), "max_rel_diff_vs_other_path": agree, "max_rel_diff_vs_reference_arm": vs_ref,
                           "peak": "of measured" if peaks.exists() else "of fallback"}))
     dist.destroy_process_group()
 

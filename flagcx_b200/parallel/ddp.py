@@ -114,6 +114,8 @@ class DataParallelTrainer:
         self.comm_stream = self.side_stream
         self.ready_event = torch.cuda.Event()
         self.done_event = torch.cuda.Event()
+        self.pre_tail_event = torch.cuda.Event()
+        self.split_tail = os.environ.get("FLAGCX_DDP_SPLIT_TAIL", "1") != "0"
         # Measured on one B200: the per-bucket optimizer beside the backward pass gains nothing (26.7 against
         # 26.5 ms per step; the AdamW blocks and the GEMMs compete for the same SMs), so it is off by default.
         self.overlap_optimizer = os.environ.get("FLAGCX_DDP_OVERLAP_OPT", "0") != "0"
@@ -153,6 +155,8 @@ class DataParallelTrainer:
         self.side_stream.wait_event(self.ready_event)
         with torch.cuda.stream(self.side_stream):
             if self.world > 1:
+                if b is self.buckets[-1]:
+                    self.pre_tail_event.record(self.side_stream)  # every earlier bucket is reduced at this point
                 want = self.tail_ctas if b is self.buckets[-1] else self.cta_budget
                 if want != self._budget_now:
                     self.native.comm_set_cta_budget(self.comm, want)
@@ -175,6 +179,9 @@ class DataParallelTrainer:
         loss.backward()
         if self.world > 1 or early_opt:
             self.done_event.record(self.side_stream)
+            if self.world > 1 and not early_opt and not self.snapshot_grads and self.split_tail:
+                self._finish_step_split()
+                return loss.detach()
             torch.cuda.current_stream(self.device).wait_event(self.done_event)
         if self.snapshot_grads:  # for tests: the averaged gradients as the optimizer is about to see them
             self.grad_snapshot = self.flat_grads.clone()
@@ -182,6 +189,21 @@ class DataParallelTrainer:
             self._adamw(0, self.flat_grads.numel())
             self.launches_per_step += 1
         return loss.detach()
+
+    def _finish_step_split(self):
+        """More than one rank: the all-reduce of the bucket that closes last (the tied embedding, the largest
+        tensor of the model) has no backward work left to hide behind, so the optimizer hides it instead: the
+        update of everything outside that bucket runs while the bucket is still being reduced."""
+        cur = torch.cuda.current_stream(self.device)
+        tail = self.buckets[-1]
+        cur.wait_event(self.pre_tail_event)
+        n = self.flat_grads.numel()
+        if tail.end < n:
+            self._adamw(tail.end, n)
+            self.launches_per_step += 1
+        cur.wait_event(self.done_event)
+        self._adamw(tail.start, tail.end)
+        self.launches_per_step += 1
 
     def _capture(self, tokens, targets):
         self.static_tokens = tokens.clone()
@@ -222,10 +244,16 @@ class DataParallelTrainer:
         """Launches of this framework's own kernels in one step: per layer 2
         fused LayerNorm forward, 2 x 3 backward (dx, parameter partials, their
         reduction), bias-GELU forward + 3 backward (dx, bias partials,
-        reduction); the final LayerNorm (1 + 3), the loss kernel, and per
+        reduction); the tcgen05 GEMMs of the projections and the LM head; the
+        final LayerNorm (1 + 3), the loss kernel, and per
         bucket one all-reduce kernel (more than one rank) and one AdamW
         kernel (one AdamW kernel in all when the optimizer is not overlapped)."""
         L = len(getattr(self.model, "blocks", []))
         own = L * (2 + 6 + 1 + 3) + (1 + 3) + 1
+        if os.environ.get("FLAGCX_MODEL_GEMM", "own") != "library":
+            # tcgen05 GEMMs: four projections per layer and the LM head, each forward + input gradient + weight
+            # gradient; the three biased projections' bias gradients take a column-sum kernel and its reduction
+            own += L * (4 * 3 + 3 * 2) + 3
         nb = len(self.buckets)
-        return own + (nb if self.world > 1 else 0) + (nb if self.overlap_optimizer else 1)
+        adamw = nb if self.overlap_optimizer else (2 if self.world > 1 and self.split_tail else 1)
+        return own + (nb if self.world > 1 else 0) + adamw

@@ -15,7 +15,7 @@ from tests.mp_util import run_ranks
 
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 
-K_AR_ZC, K_RS_ZC, K_REDUCE_ZC, K_MOVE_ZC = 18, 19, 20, 21
+K_AR_ZC, K_RS_ZC, K_REDUCE_ZC, K_MOVE_ZC, K_MOVE_CE = 18, 19, 20, 21, 22
 
 
 def _world():
@@ -147,6 +147,34 @@ def _zero_copy(lib, uid, rank, world, skew):
         off = sum(psc[:rank])
         exp.append(big[p][off:off + psc[rank]])
     check("alltoallv", dst[:sum(rc)], torch.cat(exp), 0)
+    if not skew:  # the copy-engine form needs one heap offset on all ranks (checked on the device)
+        # copy-engine form of the push movers: two one-CTA kernels around peer copies queued by the host
+        lib.tuner_pin(comm, "move_ce", 1)
+        cnt = (1 << 19) + 64
+        xs = [_seeded(r, cnt * world, torch.float32, "cpu", salt=8) for r in range(world)]
+        x, g = heap(cnt * world, torch.float32), heap(cnt * world, torch.float32)
+        x.copy_(xs[rank])
+        for rep in range(2):
+            g.zero_()
+            lib.flagcxAllGather(x.data_ptr(), g.data_ptr(), cnt, 7, comm, st)
+            torch.cuda.synchronize()
+            check(f"allgather copy-engine {rep}", g, torch.cat([t[:cnt] for t in xs]), 0)
+        g.zero_()
+        lib.flagcxAlltoAll(x.data_ptr(), g.data_ptr(), cnt, 7, comm, st)
+        torch.cuda.synchronize()
+        check("alltoall copy-engine", g, torch.cat([xs[p][rank * cnt:(rank + 1) * cnt] for p in range(world)]), 0)
+        b = heap(cnt, torch.float32)
+        b.copy_(xs[rank][:cnt])
+        lib.flagcxBroadcast(b.data_ptr(), b.data_ptr(), cnt, 7, world - 1, comm, st)
+        torch.cuda.synchronize()
+        check("broadcast copy-engine", b, xs[world - 1][:cnt], 0)
+        sc_ = heap(cnt, torch.float32)
+        sc_.zero_()
+        lib.flagcxScatter(x.data_ptr(), sc_.data_ptr(), cnt, 7, 0, comm, st)
+        torch.cuda.synchronize()
+        check("scatter copy-engine", sc_, xs[0][rank * cnt:(rank + 1) * cnt], 0)
+        lib.tuner_pin(comm, None)
+        del x, g, b, sc_
     kinds_heap = lib.counters(comm)["kind_launches"]
 
     # registered cudaMalloc buffers (not in the heap): same kernels through the segment table
@@ -201,6 +229,7 @@ def test_zero_copy_collectives(native_lib, mode):
         assert out["async"] == 0
         k = out["kinds"]
         assert k[K_AR_ZC] > 0 and k[K_RS_ZC] > 0 and k[K_MOVE_ZC] > 0, k
+        assert k[K_MOVE_CE] == (0 if mode == "skewed" else 5), k
         assert out["registered_zc"] == 1
 
 
