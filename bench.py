@@ -153,6 +153,9 @@ def main():
         from baseline.reference_arm import build_reference
         runner = build_reference(args, rank, world, local_rank, device)
     elif args.impl == "ours-c10d":
+        # the buckets' all-reduces run beside the backward pass: cap their CTAs (the library's default is tuned
+        # for a collective that has the GPU to itself)
+        os.environ.setdefault("FLAGCX_TORCH_CTAS", "32")
         import flagcx  # registers this framework's backend  # noqa: F401
         from baseline.reference_arm import build_stock_ddp
         dist.init_process_group("cpu:gloo,cuda:flagcx", rank=rank, world_size=world)

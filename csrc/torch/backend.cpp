@@ -181,6 +181,14 @@ class FlagcxBackend : public c10d::Backend {
     flagcxResult_t r = flagcxCommInitRankEx(&c, getSize(), &id, getRank(), dev.is_cuda() ? 0u : FLAGCX_INIT_HOST_ONLY);
     FCX_TORCH_CHECK(r);
     flagcxCommSetTimeoutMs(c, (int)std::max<int64_t>(1000, timeout_.count()));
+    // FLAGCX_TORCH_CTAS=n caps the CTAs of this backend's collectives: for trainers whose collectives overlap
+    // compute (DistributedDataParallel's buckets during the backward pass)
+    if (dev.is_cuda()) {
+      if (const char *cap = getenv("FLAGCX_TORCH_CTAS")) {
+        int n = atoi(cap);
+        if (n > 0) flagcxCommSetCtaBudget(c, n);
+      }
+    }
     comms_[key] = c;
     if (dev.is_cuda()) {
       stream_ = std::make_unique<c10::cuda::CUDAStream>(c10::cuda::getStreamFromPool(/*isHighPriority=*/true, dev.index()));

@@ -9,7 +9,9 @@ CUDA-event time with the achieved fraction of the measured HBM copy rate
 layernorm_fwd, layernorm_bwd, bias_gelu, emu_allreduce (8 emulated ranks,
 two-shot kernel, one cooperative launch on this GPU), emu_allgather, gemm
 (tcgen05 GEMM, against the measured cuBLAS rate), gemm_fp8 (block-scaled e4m3 GEMM), moe_dispatch and moe_layer
-(expert-parallel kernels on a one-rank communicator)."""
+(expert-parallel kernels on a one-rank communicator), emu_allreduce_zc / emu_allreduce_ll / emu_sendrecv (zero-copy,
+LL and grouped send/recv kernels on emulated ranks), gemm_dgrad / gemm_wgrad (transposed-operand GEMMs), gemm_ag /
+gemm_rs (fused all-gather / reduce-scatter GEMMs on a one-rank communicator)."""
 from __future__ import annotations
 
 import argparse
@@ -108,6 +110,76 @@ def main():
         st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
         ms = timed(lambda: lib.call("flagcxEmuCollective", emu, op, kind, 16, s, r, count, 7, 7, ctypes.c_float(1.0), 0, 0, None, st))
         lib.call("flagcxEmuDestroy", emu)
+    elif args.case in ("emu_allreduce_zc", "emu_allreduce_ll", "emu_sendrecv"):
+        # the zero-copy all-reduce (plain peer loads, 16 in flight per thread: one GPU has no switch to reduce in),
+        # the LL all-reduce at 4 KiB, and the grouped send/recv kernel, each as 8 (2) emulated ranks in one launch
+        from flagcx_b200.wrapper import FLAGCXLibrary
+        lib = FLAGCXLibrary()
+        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        if args.case == "emu_sendrecv":
+            n, nbytes_each = 2, 64 << 20
+            emu = ctypes.c_void_p()
+            lib.call("flagcxEmuCreate", ctypes.byref(emu), n, 1 << 20)
+            sb = [torch.randint(0, 255, (nbytes_each,), device="cuda", dtype=torch.uint8) for _ in range(n)]
+            rb = [torch.empty_like(t) for t in sb]
+            k = n
+            args_ = (emu, k, (ctypes.c_int * k)(*range(n)), (ctypes.c_int * k)(*[(r + 1) % n for r in range(n)]),
+                     (ctypes.c_void_p * k)(*[t.data_ptr() for t in sb]), (ctypes.c_void_p * k)(*[t.data_ptr() for t in rb]),
+                     (ctypes.c_size_t * k)(*[nbytes_each] * k), 16, st)
+            ms = timed(lambda: lib.call("flagcxEmuSendRecv", *args_))
+            nbytes = n * nbytes_each * 4  # staged: read + write into the slot, read + write out of it
+        else:
+            n = 8
+            emu = ctypes.c_void_p()
+            lib.call("flagcxEmuCreate", ctypes.byref(emu), n, 1 << 20)
+            arr = ctypes.c_void_p * n
+            zc = args.case == "emu_allreduce_zc"
+            count = (8 << 20) if zc else 1024
+            xs = [torch.randn(count, device="cuda") for _ in range(n)]
+            ys = [torch.empty_like(x) for x in xs]
+            s, r = arr(*[x.data_ptr() for x in xs]), arr(*[y.data_ptr() for y in ys])
+            kind, ctas = (b"ar_zc", 16) if zc else (b"ar_ll", 1)
+            ms = timed(lambda: lib.call("flagcxEmuCollective", emu, 6, kind, ctas, s, r, count, 7, 7, ctypes.c_float(1.0), 0, 0, None, st))
+            nbytes = n * count * 4 * 2 if zc else n * count * 4 * (1 + 2 * (n - 1) * 2 + 1)  # zc: every element read once and written once per rank
+        lib.call("flagcxEmuDestroy", emu)
+    elif args.case in ("gemm_dgrad", "gemm_wgrad", "gemm_ag", "gemm_rs"):
+        # the backward GEMMs of a linear layer (operands read transposed in place; the weight gradient splits K) and
+        # the fused all-gather / reduce-scatter forms on a one-rank communicator (comm CTAs, flags, staging and tail
+        # reduction all run, with this GPU as its own peer)
+        err = torch.zeros(1, dtype=torch.int32, device="cuda")
+        pk = ROOT / "MEASURED_PEAKS.json"
+        tf_peak = json.loads(pk.read_text())["bf16_tflops"] if pk.exists() else 1590.0
+        if args.case in ("gemm_dgrad", "gemm_wgrad"):
+            T, O, I = 8192, 4096, 4096
+            dy = (torch.randn(T, O, device="cuda") * 0.1).bfloat16()
+            w = (torch.randn(O, I, device="cuda") * 0.1).bfloat16()
+            x = (torch.randn(T, I, device="cuda") * 0.1).bfloat16()
+            if args.case == "gemm_dgrad":
+                ms = timed(lambda: nat.gemm(dy, w, False, True, None, 0, err))
+            else:
+                ms = timed(lambda: nat.gemm(dy, x, True, True, None, 0, err))
+            flops = 2.0 * T * O * I
+        else:
+            import os
+            os.environ.setdefault("FLAGCX_HEAP_USER_BYTES", "1G")
+            from flagcx_b200.parallel.tp import TensorParallelContext
+            from flagcx_b200.wrapper import FLAGCXLibrary
+            lib = FLAGCXLibrary()
+            comm = lib.flagcxCommInitRank(1, lib.flagcxGetUniqueId(), 0)
+            M, N, K = 8192, 4096, 4096
+            tp = TensorParallelContext(comm.value, 1, 0, max_rows=M, max_k=K, max_n=N, comm_ctas=4)
+            a = (torch.randn(M, K, device="cuda") * 0.1).bfloat16()
+            b = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+            ms = timed((lambda: tp.ag_gemm(a, b)) if args.case == "gemm_ag" else (lambda: tp.gemm_rs(a, b)))
+            torch.cuda.synchronize()
+            tp.check()
+            del tp
+            lib.flagcxCommDestroy(comm)
+            flops = 2.0 * M * N * K
+        tf = flops / (ms * 1e-3) / 1e12
+        print(json.dumps({"case": args.case, "ms": round(ms, 4), "tflops": round(tf, 1), "fraction_of_gemm_peak": round(tf / tf_peak, 3),
+                          "peak": label, "err": int(err.item())}))
+        return
     elif args.case == "gemm_fp8":
         M, N, K = 8192, 4096, 4096
         a = (torch.randn(M, K, device="cuda") * 0.1).bfloat16()

@@ -56,7 +56,7 @@ def _worker(lib, uid, rank, world):
             out["fails"].append(("unfused_gemm_rs", rep, float(e)))
     tp.check()
     # ring exchange with the in-kernel API: two inboxes used alternately
-    slot = nat.alloc_signals(comm.value, 1)
+    slot = nat.alloc_signals(comm.value, 2)  # data-ready signal and consumed acknowledgement
     inbox = [nat.heap_tensor(comm.value, [1 << 20], torch.float32) for _ in range(2)]
     for epoch in range(1, 5):
         src = torch.full((1 << 20,), float(rank * 10 + epoch), device="cuda")

@@ -147,6 +147,7 @@ def _zero_copy(lib, uid, rank, world, skew):
         off = sum(psc[:rank])
         exp.append(big[p][off:off + psc[rank]])
     check("alltoallv", dst[:sum(rc)], torch.cat(exp), 0)
+    del src, dst  # their sizes differ between the ranks: freed, so that what follows sits at one heap offset everywhere
     if not skew:  # the copy-engine form needs one heap offset on all ranks (checked on the device)
         # copy-engine form of the push movers: two one-CTA kernels around peer copies queued by the host
         lib.tuner_pin(comm, "move_ce", 1)
