@@ -37,7 +37,7 @@ static at::Tensor gemmNT(const at::Tensor &a, const at::Tensor &b, at::Tensor &e
 //   wgrad     dw = gemm(dy, x,  True,  True)              [O,I]   (dy is [K=T, M=O], x is [K=T, N=I])
 // split_k = 0 lets the launcher cut K when the output has too few tiles to fill the GPU (wgrad: K = tokens).
 static at::Tensor gemmEx(const at::Tensor &a, const at::Tensor &b, bool aMN, bool bMN, const c10::optional<at::Tensor> &bias, int64_t splitK,
-                         at::Tensor &err) {
+                         at::Tensor &err, int64_t pair) {
   checkMat(a, "a");
   checkMat(b, "b");
   const int64_t M = aMN ? a.size(1) : a.size(0), Ka = aMN ? a.size(0) : a.size(1);
@@ -50,8 +50,10 @@ static at::Tensor gemmEx(const at::Tensor &a, const at::Tensor &b, bool aMN, boo
   }
   c10::cuda::CUDAGuard g(a.device());
   auto c = at::empty({M, N}, a.options());
+  fcxGemmSetPairOverride((int)pair);
   auto e = fcxGemmBf16Ex(a.data_ptr(), b.data_ptr(), c.data_ptr(), (int)M, (int)N, (int)Ka, (int)a.stride(0), (int)b.stride(0), (int)c.stride(0),
                          aMN ? 1 : 0, bMN ? 1 : 0, biasPtr, (int)splitK, err.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream());
+  fcxGemmSetPairOverride(-1);
   TORCH_CHECK(e == cudaSuccess, "tcgen05 GEMM failed: ", cudaGetErrorString(e), ": ", fcxGemmLastDetail());
   return c;
 }
@@ -143,7 +145,9 @@ void bindGemm(py::module &m) {
   m.def("gemm_fp8_nt", &gemmFp8NT, "block-scaled e4m3 GEMM (1x128 activation scales, 128x128 weight scales) on tcgen05");
   m.def("gemm_nt", &gemmNT, "bf16 a[M,K] @ b[N,K]^T on tcgen05");
   m.def("gemm", &gemmEx, py::arg("a"), py::arg("b"), py::arg("a_mn") = false, py::arg("b_mn") = false, py::arg("bias") = py::none(),
-        py::arg("split_k") = 0, py::arg("err"), "bf16 GEMM on tcgen05 with either operand read K-major or MN-major, optional bias row");
+        py::arg("split_k") = 0, py::arg("err"), py::arg("pair") = -1,
+        "bf16 GEMM on tcgen05 with either operand read K-major or MN-major, optional bias row; pair: -1 kernel chosen by shape, "
+        "0 one-CTA kernel (128 x 256 tiles), 1 CTA-pair kernel (cta_group::2, 256 x 256 tiles)");
   m.def("ag_gemm", &agGemm);
   m.def("gemm_rs", &gemmRs);
 }

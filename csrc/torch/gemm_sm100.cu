@@ -466,6 +466,10 @@ extern "C" cudaError_t fcxGemmBf16(const void *a, const void *b, void *c, int M,
 static thread_local char gGemmDetail[256];
 extern "C" const char *fcxGemmLastDetail() { return gGemmDetail; }
 
+// Kernel choice of this thread's next fcxGemmBf16Ex calls: -1 by shape (the default), 0 one-CTA kernel, 1 pair kernel.
+static thread_local int gPairOverride = -1;
+extern "C" void fcxGemmSetPairOverride(int v) { gPairOverride = v; }
+
 extern "C" cudaError_t fcxGemmBf16Ex(const void *a, const void *b, void *c, int M, int N, int K, int lda, int ldb, int ldc, int aMN, int bMN,
                                      const void *bias, int splitK, int *errFlag, cudaStream_t s) {
   if (K % 8 || lda % 8 || ldb % 8 || ldc % 8 || M <= 0 || N <= 0 || K <= 0) return cudaErrorInvalidValue;
@@ -473,6 +477,9 @@ extern "C" cudaError_t fcxGemmBf16Ex(const void *a, const void *b, void *c, int 
   if ((aMN && M % 8) || (bMN && N % 8) || (bias && ((uintptr_t)bias & 1))) return cudaErrorInvalidValue;
   gGemmDetail[0] = 0;
   cudaGetLastError();  // an error left behind by an earlier, unrelated call of this thread is not this launch's
+  if (gPairOverride >= 0 ? gPairOverride > 0 : fcxGemmPairSuits(M, N, K) != 0)  // CTA pairs on 256 x 256 tiles (gemm2_sm100.cu)
+    return fcxGemmPairBf16(a, b, c, M, N, K, lda, ldb, ldc, aMN, bMN, bias, splitK, tileGroup((N + 255) / 256) / 2, errFlag, s, gGemmDetail,
+                           sizeof gGemmDetail);
   CUtensorMap ma, mb;
   const int bn = pickBn(M, N, smCount());
   // K-major operand: rows = M (or N), box of 128 (bn) rows x 64 K; MN-major operand: rows = K, box of 64 lines x 64 columns
@@ -503,6 +510,7 @@ extern "C" cudaError_t fcxGemmBf16Ex(const void *a, const void *b, void *c, int 
   }
   if (N % 2) splitK = 1;  // the partial results are added two columns at a time
   p.splitK = std::max(1, std::min(splitK, nK));
+  p.splitK = (nK + (nK + p.splitK - 1) / p.splitK - 1) / ((nK + p.splitK - 1) / p.splitK);  // no piece may be empty
   if (p.splitK > 1) {
     cudaError_t e = cudaMemsetAsync(c, 0, ((size_t)(M - 1) * ldc + N) * 2, s);
     if (e != cudaSuccess) return e;

@@ -161,3 +161,42 @@ def test_linear_autograd_matches_pytorch(nat):
     assert gemm_error() == 0
     for got, ref, k in ((y, yr, I), (x.grad, xr.grad, O), (w.grad, wr.grad, B * T), (b.grad, br.grad, B * T)):
         _close(got, ref.detach(), k)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 1024), (2048, 3072, 4096), (384, 200, 136), (104, 72, 24), (4096, 1024, 8192)])
+def test_pair_kernel(nat, a_mn, b_mn, M, N, K):
+    """The cta_group::2 kernel (two CTAs per 256 x 256 tile), forced for every shape: whole tiles, ragged edges,
+    a row count that leaves the second CTA of a pair without rows, and all four operand orientations."""
+    torch.manual_seed(6)
+    a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+    ref = _ref(a, b)
+    a_st = a.t().contiguous() if a_mn else a
+    b_st = b.t().contiguous() if b_mn else b
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    c = nat.gemm(a_st, b_st, a_mn, b_mn, None, 1, err, 1)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    _close(c, ref, K)
+
+
+@pytest.mark.parametrize("split_k", [0, 3, 7])
+def test_pair_kernel_bias_and_split_k(nat, split_k):
+    torch.manual_seed(7)
+    M, N, K = 512, 512, 4096
+    a = (torch.randn(M, K, device="cuda") * 0.3).bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.3).bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    c = nat.gemm(a, b, False, False, bias, split_k, err, 1)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    _close(c, _ref(a, b) + bias.float(), K)
+    T, O, I = 8192, 1024, 384  # weight-gradient shape: K = tokens, both operands transposed
+    dy = (torch.randn(T, O, device="cuda") * 0.3).bfloat16()
+    x = (torch.randn(T, I, device="cuda") * 0.3).bfloat16()
+    dw = nat.gemm(dy, x, True, True, None, split_k, err, 1)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    _close(dw, dy.float().t() @ x.float(), T)
