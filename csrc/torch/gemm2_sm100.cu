@@ -8,10 +8,11 @@
 // CTA's 128 accumulator rows and the two B halves for the 256 columns, and writes each CTA's accumulator into that
 // CTA's own TMEM.  Against the one-CTA kernel (128 x 256 tile, 48 KB per K block of 64 through one SM's shared
 // memory) a CTA now feeds 32 KB per K block for the same math, which lifts the shared-memory bound on the MMA rate
-// and halves the L2 reads of B; the smaller stage also buys a 6-deep pipeline.
+// and halves the L2 reads of B; the smaller stage also buys a 5-deep pipeline.
 //
-// Roles per CTA (256 threads): warp 0 TMA producer, warp 1 MMA issuer (leader CTA only), warp 2 TMEM allocation,
-// warps 4-7 epilogue (TMEM -> registers -> shared-memory transposition -> 128-byte global stores).
+// Roles per CTA (384 threads): warp 0 TMA producer, warp 1 MMA issuer (leader CTA only), warp 2 TMEM allocation,
+// warps 4-11 epilogue (TMEM -> registers -> bf16 blocks in shared memory -> TMA store, or TMA add for split K and
+// accumulated gradients).
 // Barriers: the leader's full[stage] collects the bytes of both CTAs' loads; tcgen05.commit arrives on empty[stage]
 // and accFull[buf] of BOTH CTAs (barrier multicast inside the cluster; that is a signal, not a load); the epilogue
 // warps of both CTAs arrive on the leader's accEmpty[buf].  Every wait is bounded: after the limit the kernel
@@ -36,11 +37,13 @@ using namespace fcxmma;
 constexpr int BM = 128;    // accumulator rows per CTA (256 per pair)
 constexpr int BN = 256;    // columns per tile
 constexpr int BNH = 128;   // B columns that one CTA holds
-constexpr int BK = 64, STAGES = 6;
+constexpr int BK = 64, STAGES = 5;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BNH * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int EPI_BYTES = 4 * 32 * 128;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 256;
-constexpr int THREADS = 256;
+constexpr int STG_BYTES = 32 * 64;                 // staging block: 32 rows x 32 bf16 columns
+constexpr int EPI_BYTES = 8 * 2 * STG_BYTES;        // 8 epilogue warps, two blocks each
+constexpr int BIAS_BYTES = 8 * 128 * 4;  // per epilogue warp: its 128 bias values as fp32
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BIAS_BYTES + 1024 + 256;
+constexpr int THREADS = 384;
 constexpr int MN_BLOCK_BYTES = 64 * BK * 2;
 
 __device__ __forceinline__ uint32_t ctaRankInCluster() {
@@ -99,7 +102,8 @@ __device__ __forceinline__ void tileCoord2(int group, int nM, int nN, int t, int
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
-    fcxGemmPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const FcxGemmParams p) {
+    fcxGemmPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
+                      const FcxGemmParams p) {
   extern __shared__ uint8_t smemRaw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int *err = p.errFlag;
@@ -108,7 +112,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 
   uint8_t *tiles = (uint8_t *)(((uintptr_t)smemRaw + 1023) & ~(uintptr_t)1023);
   uint8_t *epiStage = tiles + STAGES * STAGE_BYTES;
-  uint64_t *bars = (uint64_t *)(epiStage + EPI_BYTES);
+  float *biasStage = (float *)(epiStage + EPI_BYTES);
+  uint64_t *bars = (uint64_t *)(epiStage + EPI_BYTES + BIAS_BYTES);
   uint64_t *fullBar = bars, *emptyBar = bars + STAGES, *accFull = bars + 2 * STAGES, *accEmpty = bars + 2 * STAGES + 2;
   uint32_t *tmemBaseSlot = (uint32_t *)(bars + 2 * STAGES + 4);
 
@@ -120,7 +125,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbarInit(&fullBar[s], 1); mbarInit(&emptyBar[s], 1); }
-    for (int b = 0; b < 2; b++) { mbarInit(&accFull[b], 1); mbarInit(&accEmpty[b], 8); }  // 4 epilogue warps in each CTA
+    for (int b = 0; b < 2; b++) { mbarInit(&accFull[b], 1); mbarInit(&accEmpty[b], 16); }  // 8 epilogue warps in each CTA
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
@@ -194,11 +199,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
       }
     }
   } else if (warp >= 4) {
-    // ---- epilogue (both CTAs): warp w owns TMEM lanes [32*(w%4), +32) = 32 of this CTA's 128 rows
-    const int q = warp & 3;
+    // ---- epilogue (both CTAs, 8 warps): warp w owns TMEM lanes [32*(w%4), +32) = 32 of this CTA's 128 rows, and the
+    // left (warps 4-7) or right (warps 8-11) 128 of the tile's 256 columns.  32 columns at a time: tcgen05.ld (one row
+    // per lane), bias, fp32 -> bf16, 16-byte stores into a staging block laid out as the TMA's 64-byte swizzle wants it
+    // (conflict-free), then ONE thread hands the 32 x 32 block to the TMA unit, as a store or, for a piece of a split K
+    // or an accumulated gradient, as a reduction (add) into C.  The TMA clips what lies beyond M and N.  Two staging
+    // blocks per warp: the next block is filled while the unit still reads the previous one.
+    const int ew = warp - 4, q = ew & 3, half = ew >> 2;
     int buf = 0;
-    uint32_t accPhase = 0;
+    uint32_t accPhase = 0, chunkNo = 0;
     bool live = true;
+    uint8_t *stgBase = epiStage + (size_t)ew * 2 * STG_BYTES;
+    float *biasW = biasStage + ew * 128;
+    const bool reduce = splitK > 1 || p.accumulate;
     for (int t = pair; t < nTiles; t += nPairs) {
       int mb, nb;
       tileCoord2(p.group, nM, nN, t / splitK, &mb, &nb);
@@ -206,55 +219,59 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
       if (live) live = __all_sync(0xffffffffu, mbarWait(&accFull[buf], accPhase, err));
       if (live) {
         fenceAfter();
-        const int row0 = mb * 2 * BM + (int)cr * BM + q * 32;
-        __nv_bfloat16 *dst0 = (__nv_bfloat16 *)p.c + (size_t)row0 * p.ldc;
-        uint4 *stg = (uint4 *)(epiStage + (size_t)q * 32 * 128);
+        const int row0 = mb * 2 * BM + (int)cr * BM + q * 32, colBase = nb * BN + half * 128;
+        const bool addBias = p.bias != nullptr && firstSplit;
+        if (addBias) {  // this warp's 128 bias values, once per tile, as fp32 in shared memory (columns past N read as 0)
+          const __nv_bfloat16 *bias = (const __nv_bfloat16 *)p.bias;
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const int cidx = colBase + j * 32 + lane;
+            biasW[j * 32 + lane] = cidx < p.N ? __bfloat162float(bias[cidx]) : 0.f;
+          }
+          __syncwarp();
+        }
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 64) {
-          if (nb * BN + c0 >= p.N) break;
+        for (int c0 = 0; c0 < 128; c0 += 32) {
+          if (colBase + c0 >= p.N || row0 >= p.M) break;
           uint32_t r[32];
+          tmemLd32(tmemBase + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + half * 128 + c0), r);
+          // the staging block used two blocks ago must have been read out by the TMA unit
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          __syncwarp();
+          tmemLdWait();
+          if (addBias) {
+            const float4 *bv = (const float4 *)(biasW + c0);  // same address in every lane: broadcast reads
 #pragma unroll
-          for (int h = 0; h < 2; h++) {
-            tmemLd32(tmemBase + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c0 + 32 * h), r);
-            tmemLdWait();
-            if (p.bias != nullptr && firstSplit) {
-              const __nv_bfloat16 *bias = (const __nv_bfloat16 *)p.bias + nb * BN + c0 + 32 * h;
-              const int left = p.N - (nb * BN + c0 + 32 * h);
-#pragma unroll
-              for (int j = 0; j < 32; j++)
-                if (j < left) r[j] = __float_as_uint(__uint_as_float(r[j]) + __bfloat162float(bias[j]));
-            }
-#pragma unroll
-            for (int v = 0; v < 4; v++) {
-              uint4 o;
-              o.x = pack2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-              o.y = pack2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-              o.z = pack2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-              o.w = pack2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-              stg[lane * 8 + ((4 * h + v) ^ (lane & 7))] = o;
+            for (int j = 0; j < 8; j++) {
+              const float4 f = bv[j];
+              r[4 * j + 0] = __float_as_uint(__uint_as_float(r[4 * j + 0]) + f.x);
+              r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + f.y);
+              r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + f.z);
+              r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + f.w);
             }
           }
-          __syncwarp();
-          const int col = nb * BN + c0 + (lane & 7) * 8;
+          uint4 *stg = (uint4 *)(stgBase + (chunkNo & 1) * STG_BYTES);
 #pragma unroll
-          for (int i = 0; i < 8; i++) {
-            const int rr = i * 4 + (lane >> 3);
-            uint4 o = stg[rr * 8 + ((lane & 7) ^ (rr & 7))];
-            if (row0 + rr < p.M) {
-              __nv_bfloat16 *d = dst0 + (size_t)rr * p.ldc + col;
-              if (splitK > 1) {
-                const uint32_t *w = (const uint32_t *)&o;
-                for (int j = 0; j < 4; j++)
-                  if (col + 2 * j + 1 < p.N || (col + 2 * j < p.N && (p.N & 1) == 0))
-                    asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(d + 2 * j), "r"(w[j]) : "memory");
-              } else if (col + 8 <= p.N) *(uint4 *)d = o;
-              else {
-                const __nv_bfloat16 *e = (const __nv_bfloat16 *)&o;
-                for (int j = 0; j < 8 && col + j < p.N; j++) d[j] = e[j];
-              }
-            }
+          for (int v = 0; v < 4; v++) {
+            uint4 o;
+            o.x = pack2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+            o.y = pack2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+            o.z = pack2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+            o.w = pack2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+            stg[lane * 4 + (v ^ ((lane >> 1) & 3))] = o;  // row = lane (64 bytes), 16-byte chunk XOR bits 1-2 of the row
           }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> the TMA unit's reads
           __syncwarp();
+          if (lane == 0) {
+            if (reduce)
+              asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                           ::"l"(&tmC), "r"(colBase + c0), "r"(row0), "r"(smemAddr(stg)) : "memory");
+            else
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+                           ::"l"(&tmC), "r"(colBase + c0), "r"(row0), "r"(smemAddr(stg)) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+          chunkNo++;
         }
         fenceBefore();
         __syncwarp();
@@ -262,6 +279,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
       }
       if (++buf == 2) { buf = 0; accPhase ^= 1; }
     }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // every block has reached C
   }
 
   // ---- tear-down: nobody leaves, and no TMEM is freed, while the peer may still read this CTA's shared memory,
@@ -307,12 +325,16 @@ extern "C" int fcxGemmPairSuits(int M, int N, int K) {
 }
 
 extern "C" cudaError_t fcxGemmPairBf16(const void *a, const void *b, void *c, int M, int N, int K, int lda, int ldb, int ldc, int aMN, int bMN,
-                                       const void *bias, int splitK, int group, int *errFlag, cudaStream_t s, char *detail, size_t detailLen) {
+                                       const void *bias, int splitK, int accumulate, int group, int *errFlag, cudaStream_t s, char *detail,
+                                       size_t detailLen) {
   CUtensorMap ma, mb;
   const bool okA = aMN ? makeTileMap(&ma, a, K, M, lda, BK, 2) : makeTileMap(&ma, a, M, K, lda, BM, 2);
   const bool okB = bMN ? makeTileMap(&mb, b, K, N, ldb, BK, 2) : makeTileMap(&mb, b, N, K, ldb, BNH, 2);
-  if (!okA || !okB) {
-    if (detail) snprintf(detail, detailLen, "tensor map of operand %s refused (pair kernel, M %d N %d K %d)", !okA ? "A" : "B", M, N, K);
+  CUtensorMap mc;
+  const bool okC = makeStoreMap(&mc, c, M, N, ldc);
+  if (!okA || !okB || !okC) {
+    if (detail)
+      snprintf(detail, detailLen, "tensor map of %s refused (pair kernel, M %d N %d K %d)", !okA ? "operand A" : !okB ? "operand B" : "C", M, N, K);
     return cudaErrorNotSupported;
   }
   static bool attr = false;
@@ -325,26 +347,14 @@ extern "C" cudaError_t fcxGemmPairBf16(const void *a, const void *b, void *c, in
   p.M = M; p.N = N; p.K = K; p.c = c; p.ldc = ldc; p.errFlag = errFlag; p.bn = BN; p.group = group;
   p.aMN = aMN; p.bMN = bMN; p.bias = bias;
   const int units = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN), nK = (K + BK - 1) / BK, pairs = smCount2() / 2;
-  if (splitK <= 0) {
-    splitK = 1;
-    if (units < pairs && nK >= 32) {
-      double best = 1.0;
-      for (int sk = 2; sk <= 8 && nK / sk >= 8; sk++) {
-        const double waves = (double)((units * sk + pairs - 1) / pairs);
-        const double cost = waves / sk + 0.04 * (sk - 1);
-        if (cost < best - 0.05) { best = cost; splitK = sk; }
-      }
-    }
-  }
-  if (N % 2) splitK = 1;
-  p.splitK = std::max(1, std::min(splitK, nK));
-  p.splitK = (nK + (nK + p.splitK - 1) / p.splitK - 1) / ((nK + p.splitK - 1) / p.splitK);  // no piece may be empty
-  if (p.splitK > 1) {
+  p.splitK = fcxGemmPickSplitK(splitK, units, pairs, nK, N);
+  p.accumulate = accumulate;
+  if (p.splitK > 1 && !accumulate) {
     cudaError_t e = cudaMemsetAsync(c, 0, ((size_t)(M - 1) * ldc + N) * 2, s);
     if (e != cudaSuccess) return e;
   }
   const int grid = 2 * std::min(units * p.splitK, pairs);
-  fcxGemmPairKernel<<<grid, THREADS, SMEM_BYTES, s>>>(ma, mb, p);
+  fcxGemmPairKernel<<<grid, THREADS, SMEM_BYTES, s>>>(ma, mb, mc, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess && detail)
     snprintf(detail, detailLen, "pair kernel launch: %s (M %d N %d K %d splitK %d grid %d)", cudaGetErrorString(e), M, N, K, p.splitK, grid);

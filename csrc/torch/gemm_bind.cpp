@@ -37,7 +37,7 @@ static at::Tensor gemmNT(const at::Tensor &a, const at::Tensor &b, at::Tensor &e
 //   wgrad     dw = gemm(dy, x,  True,  True)              [O,I]   (dy is [K=T, M=O], x is [K=T, N=I])
 // split_k = 0 lets the launcher cut K when the output has too few tiles to fill the GPU (wgrad: K = tokens).
 static at::Tensor gemmEx(const at::Tensor &a, const at::Tensor &b, bool aMN, bool bMN, const c10::optional<at::Tensor> &bias, int64_t splitK,
-                         at::Tensor &err, int64_t pair) {
+                         at::Tensor &err, int64_t pair, const c10::optional<at::Tensor> &out, bool accumulate) {
   checkMat(a, "a");
   checkMat(b, "b");
   const int64_t M = aMN ? a.size(1) : a.size(0), Ka = aMN ? a.size(0) : a.size(1);
@@ -49,11 +49,19 @@ static at::Tensor gemmEx(const at::Tensor &a, const at::Tensor &b, bool aMN, boo
     biasPtr = bias->data_ptr();
   }
   c10::cuda::CUDAGuard g(a.device());
-  auto c = at::empty({M, N}, a.options());
-  fcxGemmSetPairOverride((int)pair);
-  auto e = fcxGemmBf16Ex(a.data_ptr(), b.data_ptr(), c.data_ptr(), (int)M, (int)N, (int)Ka, (int)a.stride(0), (int)b.stride(0), (int)c.stride(0),
-                         aMN ? 1 : 0, bMN ? 1 : 0, biasPtr, (int)splitK, err.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream());
-  fcxGemmSetPairOverride(-1);
+  at::Tensor c;
+  if (out.has_value() && out->defined()) {
+    c = *out;
+    TORCH_CHECK(c.is_cuda() && c.scalar_type() == at::kBFloat16 && c.dim() == 2 && c.size(0) == M && c.size(1) == N && c.stride(1) == 1,
+                "out must be a bf16 [M, N] CUDA matrix with contiguous rows");
+  } else {
+    TORCH_CHECK(!accumulate, "accumulate needs out");
+    c = at::empty({M, N}, a.options());
+  }
+  FcxGemmOpts o{};
+  o.aMN = aMN ? 1 : 0; o.bMN = bMN ? 1 : 0; o.bias = biasPtr; o.splitK = (int)splitK; o.accumulate = accumulate ? 1 : 0; o.pair = (int)pair;
+  auto e = fcxGemmBf16Opts(a.data_ptr(), b.data_ptr(), c.data_ptr(), (int)M, (int)N, (int)Ka, (int)a.stride(0), (int)b.stride(0),
+                           (int)c.stride(0), &o, err.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(e == cudaSuccess, "tcgen05 GEMM failed: ", cudaGetErrorString(e), ": ", fcxGemmLastDetail());
   return c;
 }
@@ -145,7 +153,8 @@ void bindGemm(py::module &m) {
   m.def("gemm_fp8_nt", &gemmFp8NT, "block-scaled e4m3 GEMM (1x128 activation scales, 128x128 weight scales) on tcgen05");
   m.def("gemm_nt", &gemmNT, "bf16 a[M,K] @ b[N,K]^T on tcgen05");
   m.def("gemm", &gemmEx, py::arg("a"), py::arg("b"), py::arg("a_mn") = false, py::arg("b_mn") = false, py::arg("bias") = py::none(),
-        py::arg("split_k") = 0, py::arg("err"), py::arg("pair") = -1,
+        py::arg("split_k") = 0, py::arg("err"), py::arg("pair") = -1, py::arg("out") = py::none(), py::arg("accumulate") = false,
+        "out: write the result there; accumulate: add it to what out holds (a gradient that collects contributions). "
         "bf16 GEMM on tcgen05 with either operand read K-major or MN-major, optional bias row; pair: -1 kernel chosen by shape, "
         "0 one-CTA kernel (128 x 256 tiles), 1 CTA-pair kernel (cta_group::2, 256 x 256 tiles)");
   m.def("ag_gemm", &agGemm);

@@ -53,7 +53,8 @@ using namespace fcxmma;
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int EPI_BYTES = 4 * 32 * 128;  // per epilogue warp: 32 rows x 64 bf16
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int BIAS_BYTES = 4 * 256 * 4;  // per epilogue warp: the tile's bias values as fp32
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BIAS_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr int THREADS = 256;
 
 // Instruction descriptor: D fp32, A/B bf16, both K-major, M = 128, N = 256.
@@ -129,7 +130,8 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
   // ------------------------------------------------------------ GEMM CTAs
   uint8_t *tiles = (uint8_t *)(((uintptr_t)smemRaw + 1023) & ~(uintptr_t)1023);
   uint8_t *epiStage = tiles + STAGES * STAGE_BYTES;
-  uint64_t *bars = (uint64_t *)(epiStage + EPI_BYTES);
+  float *biasStage = (float *)(epiStage + EPI_BYTES);
+  uint64_t *bars = (uint64_t *)(epiStage + EPI_BYTES + BIAS_BYTES);
   uint64_t *fullBar = bars, *emptyBar = bars + STAGES, *tmemFull = bars + 2 * STAGES, *tmemEmpty = bars + 2 * STAGES + 2;
   uint32_t *tmemBaseSlot = (uint32_t *)(bars + 2 * STAGES + 4);
 
@@ -265,6 +267,18 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
         // shared memory (32 rows x 128 bytes per warp, 16-byte chunks XOR-swizzled by row)
         // turns that into stores where 8 lanes write one full 128-byte line of a row.
         uint4 *stg = (uint4 *)(epiStage + (size_t)q * 32 * 128);
+        // the tile's bias values, once per tile and warp, as fp32 in shared memory (columns past N read as 0)
+        const bool addBias = MODE == FCX_GEMM_PLAIN && p.bias != nullptr && firstSplit;
+        float *biasW = biasStage + q * 256;
+        if (addBias) {
+          const __nv_bfloat16 *bias = (const __nv_bfloat16 *)p.bias;
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            const int cidx = nb * bn + j * 32 + lane;
+            biasW[j * 32 + lane] = (j * 32 < bn && cidx < p.N) ? __bfloat162float(bias[cidx]) : 0.f;
+          }
+          __syncwarp();
+        }
 #pragma unroll 1
         for (int c0 = 0; c0 < bn; c0 += 64) {
           uint32_t r[32];
@@ -272,13 +286,17 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
           for (int h = 0; h < 2; h++) {
             tmemLd32(tmemBase + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * bn + c0 + 32 * h), r);
             tmemLdWait();
-            if (MODE == FCX_GEMM_PLAIN && p.bias != nullptr && firstSplit) {
-              // every lane holds one row and the same 32 columns: the bias loads are warp-wide broadcasts
-              const __nv_bfloat16 *bias = (const __nv_bfloat16 *)p.bias + nb * bn + c0 + 32 * h;
-              const int left = p.N - (nb * bn + c0 + 32 * h);
+            if (addBias) {
+              // every lane holds one row and the same 32 columns: broadcast reads of the staged bias values
+              const float4 *bv = (const float4 *)(biasW + c0 + 32 * h);
 #pragma unroll
-              for (int j = 0; j < 32; j++)
-                if (j < left) r[j] = __float_as_uint(__uint_as_float(r[j]) + __bfloat162float(bias[j]));
+              for (int j = 0; j < 8; j++) {
+                const float4 f = bv[j];
+                r[4 * j + 0] = __float_as_uint(__uint_as_float(r[4 * j + 0]) + f.x);
+                r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + f.y);
+                r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + f.z);
+                r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + f.w);
+              }
             }
 #pragma unroll
             for (int v = 0; v < 4; v++) {
@@ -302,8 +320,8 @@ __global__ void __launch_bounds__(THREADS, 1) fcxGemmKernel(const __grid_constan
                 const int4 info = p.rowInfo[row0 + rr];
                 d = (__nv_bfloat16 *)(dc.heap[info.x] + p.combineOff) + ((size_t)info.y * p.topk + info.z) * p.N + col;
               }
-              if (MODE == FCX_GEMM_PLAIN && splitK > 1) {
-                // partial result of one K piece: added into C, which the launcher zeroed
+              if (MODE == FCX_GEMM_PLAIN && (splitK > 1 || p.accumulate)) {
+                // one K piece of several, or a contribution to a gradient that is being accumulated: added into C
                 const uint32_t *w = (const uint32_t *)&o;
                 for (int j = 0; j < 4; j++)
                   if (col + 2 * j + 1 < p.N || (col + 2 * j < p.N && (p.N & 1) == 0))
@@ -462,24 +480,46 @@ extern "C" cudaError_t fcxGemmBf16(const void *a, const void *b, void *c, int M,
   return launch<FCX_GEMM_PLAIN>(ma, mb, p, dc, std::min(tiles, smCount()), s);
 }
 
+// Pieces to cut K into.  requested > 0: that many (at most one per K block, and no piece may be empty).  Otherwise: few
+// tiles and a long K (the weight-gradient GEMMs: K = tokens) are cut so that the pieces fill whole waves; a split into
+// s pieces takes ceil(units * s / slots) waves of 1/s the length, and every extra piece costs some atomic traffic,
+// counted as 4 % of a tile.
+extern "C" int fcxGemmPickSplitK(int requested, int units, int slots, int nK, int N) {
+  int splitK = requested;
+  if (splitK <= 0) {
+    splitK = 1;
+    if (units < slots && nK >= 32) {
+      double best = 1.0;
+      for (int sk = 2; sk <= 8 && nK / sk >= 8; sk++) {
+        const double waves = (double)((units * sk + slots - 1) / slots);
+        const double cost = waves / sk + 0.04 * (sk - 1);
+        if (cost < best - 0.05) { best = cost; splitK = sk; }
+      }
+    }
+  }
+  if (N % 2) return 1;  // the partial results are added two columns at a time
+  splitK = std::max(1, std::min(splitK, nK));
+  const int kPer = (nK + splitK - 1) / splitK;
+  return (nK + kPer - 1) / kPer;
+}
+
 // What went wrong in the last fcxGemmBf16Ex call of this thread that did not return cudaSuccess.
 static thread_local char gGemmDetail[256];
 extern "C" const char *fcxGemmLastDetail() { return gGemmDetail; }
 
-// Kernel choice of this thread's next fcxGemmBf16Ex calls: -1 by shape (the default), 0 one-CTA kernel, 1 pair kernel.
-static thread_local int gPairOverride = -1;
-extern "C" void fcxGemmSetPairOverride(int v) { gPairOverride = v; }
-
-extern "C" cudaError_t fcxGemmBf16Ex(const void *a, const void *b, void *c, int M, int N, int K, int lda, int ldb, int ldc, int aMN, int bMN,
-                                     const void *bias, int splitK, int *errFlag, cudaStream_t s) {
+extern "C" cudaError_t fcxGemmBf16Opts(const void *a, const void *b, void *c, int M, int N, int K, int lda, int ldb, int ldc,
+                                       const FcxGemmOpts *o, int *errFlag, cudaStream_t s) {
+  const int aMN = o->aMN, bMN = o->bMN, accumulate = o->accumulate;
+  const void *bias = o->bias;
+  int splitK = o->splitK;
   if (K % 8 || lda % 8 || ldb % 8 || ldc % 8 || M <= 0 || N <= 0 || K <= 0) return cudaErrorInvalidValue;
   if (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) return cudaErrorInvalidValue;
-  if ((aMN && M % 8) || (bMN && N % 8) || (bias && ((uintptr_t)bias & 1))) return cudaErrorInvalidValue;
+  if ((aMN && M % 8) || (bMN && N % 8) || (bias && ((uintptr_t)bias & 1)) || (accumulate && N % 2)) return cudaErrorInvalidValue;
   gGemmDetail[0] = 0;
   cudaGetLastError();  // an error left behind by an earlier, unrelated call of this thread is not this launch's
-  if (gPairOverride >= 0 ? gPairOverride > 0 : fcxGemmPairSuits(M, N, K) != 0)  // CTA pairs on 256 x 256 tiles (gemm2_sm100.cu)
-    return fcxGemmPairBf16(a, b, c, M, N, K, lda, ldb, ldc, aMN, bMN, bias, splitK, tileGroup((N + 255) / 256) / 2, errFlag, s, gGemmDetail,
-                           sizeof gGemmDetail);
+  if (o->pair >= 0 ? o->pair > 0 : fcxGemmPairSuits(M, N, K) != 0)  // CTA pairs on 256 x 256 tiles (gemm2_sm100.cu)
+    return fcxGemmPairBf16(a, b, c, M, N, K, lda, ldb, ldc, aMN, bMN, bias, splitK, accumulate, tileGroup((N + 255) / 256) / 2, errFlag, s,
+                           gGemmDetail, sizeof gGemmDetail);
   CUtensorMap ma, mb;
   const int bn = pickBn(M, N, smCount());
   // K-major operand: rows = M (or N), box of 128 (bn) rows x 64 K; MN-major operand: rows = K, box of 64 lines x 64 columns
@@ -492,26 +532,10 @@ extern "C" cudaError_t fcxGemmBf16Ex(const void *a, const void *b, void *c, int 
   }
   FcxGemmParams p{};
   p.M = M; p.N = N; p.K = K; p.c = c; p.ldc = ldc; p.errFlag = errFlag; p.rotate = 0; p.bn = bn; p.group = tileGroup((N + bn - 1) / bn);
-  p.aMN = aMN; p.bMN = bMN; p.bias = bias;
+  p.aMN = aMN; p.bMN = bMN; p.bias = bias; p.accumulate = accumulate;
   const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn), nK = (K + BK - 1) / BK;
-  if (splitK <= 0) {
-    // Few tiles and a long K (the weight-gradient GEMMs: K = tokens): cut K so that the pieces fill whole waves.
-    // A split into s pieces takes ceil(tiles * s / SMs) waves of 1/s the length; every extra piece costs some
-    // atomic traffic, counted as 4 % of a tile.
-    splitK = 1;
-    if (tiles < smCount() && nK >= 32) {
-      double best = 1.0;
-      for (int sk = 2; sk <= 8 && nK / sk >= 8; sk++) {
-        const double waves = (double)((tiles * sk + smCount() - 1) / smCount());
-        const double cost = waves / sk + 0.04 * (sk - 1);
-        if (cost < best - 0.05) { best = cost; splitK = sk; }
-      }
-    }
-  }
-  if (N % 2) splitK = 1;  // the partial results are added two columns at a time
-  p.splitK = std::max(1, std::min(splitK, nK));
-  p.splitK = (nK + (nK + p.splitK - 1) / p.splitK - 1) / ((nK + p.splitK - 1) / p.splitK);  // no piece may be empty
-  if (p.splitK > 1) {
+  p.splitK = fcxGemmPickSplitK(splitK, tiles, smCount(), nK, N);
+  if (p.splitK > 1 && !accumulate) {
     cudaError_t e = cudaMemsetAsync(c, 0, ((size_t)(M - 1) * ldc + N) * 2, s);
     if (e != cudaSuccess) return e;
   }
@@ -521,6 +545,13 @@ extern "C" cudaError_t fcxGemmBf16Ex(const void *a, const void *b, void *c, int 
     snprintf(gGemmDetail, sizeof gGemmDetail, "kernel launch: %s (M %d N %d K %d aMN %d bMN %d splitK %d grid %d)", cudaGetErrorString(e), M, N,
              K, aMN, bMN, p.splitK, std::min(tiles * p.splitK, smCount()));
   return e;
+}
+
+extern "C" cudaError_t fcxGemmBf16Ex(const void *a, const void *b, void *c, int M, int N, int K, int lda, int ldb, int ldc, int aMN, int bMN,
+                                     const void *bias, int splitK, int *errFlag, cudaStream_t s) {
+  FcxGemmOpts o{};
+  o.aMN = aMN; o.bMN = bMN; o.bias = bias; o.splitK = splitK; o.accumulate = 0; o.pair = -1;
+  return fcxGemmBf16Opts(a, b, c, M, N, K, lda, ldb, ldc, &o, errFlag, s);
 }
 
 extern "C" cudaError_t fcxGemmBf16DynM(const void *a, const void *b, void *c, int Mmax, const int *mPtr, int N, int K, int lda, int ldb, int ldc,

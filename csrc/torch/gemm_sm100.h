@@ -36,6 +36,7 @@ struct FcxGemmParams {
   // where they lie instead of being transposed first).
   int aMN, bMN;
   const void *bias;     // optional bf16 [N], added to every row of C
+  int accumulate;       // the result is added to what C holds (red.global.add) instead of replacing it
   int splitK;           // > 1: the K range is cut into that many pieces worked on by different CTAs, which add their
                         // bf16 partial results into C (zeroed by the launcher) with red.global.add
 };
@@ -52,13 +53,22 @@ cudaError_t fcxGemmRsBf16(const FcxDevComm *dc, const void *a, const void *b, vo
 // optional bias row, splitK = 0 lets the launcher pick (it splits K when the tiles would fill under half of the SMs).
 cudaError_t fcxGemmBf16Ex(const void *a, const void *b, void *c, int M, int N, int K, int lda, int ldb, int ldc, int aMN, int bMN,
                           const void *bias, int splitK, int *errFlag, cudaStream_t s);
-// The same on CTA pairs (tcgen05.mma.cta_group::2, 256 x 256 tiles; gemm2_sm100.cu).  fcxGemmBf16Ex forwards to it when
-// fcxGemmPairSuits says so (FLAGCX_GEMM_2SM: 0 never, 1 by shape, 2 whenever possible).
+// The same with every option in a struct.  pair: -1 kernel chosen by shape (FLAGCX_GEMM_2SM: 0 never the pair kernel, 1 by
+// shape, 2 whenever possible), 0 one-CTA kernel (128 x 256 tiles), 1 CTA-pair kernel (tcgen05.mma.cta_group::2, 256 x 256
+// tiles; gemm2_sm100.cu).  accumulate: C += A B^T (a gradient that collects several contributions; C is not zeroed).
+typedef struct FcxGemmOpts {
+  int aMN, bMN;
+  const void *bias;
+  int splitK, accumulate, pair;
+} FcxGemmOpts;
+cudaError_t fcxGemmBf16Opts(const void *a, const void *b, void *c, int M, int N, int K, int lda, int ldb, int ldc, const FcxGemmOpts *o,
+                            int *errFlag, cudaStream_t s);
+int fcxGemmPickSplitK(int requested, int units, int slots, int nK, int N);
 int fcxGemmPairMode();
 int fcxGemmPairSuits(int M, int N, int K);
 cudaError_t fcxGemmPairBf16(const void *a, const void *b, void *c, int M, int N, int K, int lda, int ldb, int ldc, int aMN, int bMN,
-                            const void *bias, int splitK, int group, int *errFlag, cudaStream_t s, char *detail, size_t detailLen);
-void fcxGemmSetPairOverride(int v);  // this thread's next fcxGemmBf16Ex calls: -1 choose by shape, 0 one-CTA kernel, 1 pair kernel
+                            const void *bias, int splitK, int accumulate, int group, int *errFlag, cudaStream_t s, char *detail,
+                            size_t detailLen);
 const char *fcxGemmLastDetail();  // what the calling thread's last failed fcxGemmBf16Ex call tripped over
 // c[Mmax,N] = a[*mPtr rows, K] @ b^T with the row count read on the device.
 cudaError_t fcxGemmBf16DynM(const void *a, const void *b, void *c, int Mmax, const int *mPtr, int N, int K, int lda, int ldb, int ldc,

@@ -49,17 +49,26 @@ static std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> layernormFwd(c
 // dx (+ dres), dgamma, dbeta
 static std::tuple<at::Tensor, at::Tensor, at::Tensor> layernormBwd(const at::Tensor &dy, const at::Tensor &x, const at::Tensor &gamma,
                                                                   const at::Tensor &mean, const at::Tensor &rstd,
-                                                                  const c10::optional<at::Tensor> &dres) {
+                                                                  const c10::optional<at::Tensor> &dres,
+                                                                  const c10::optional<at::Tensor> &dgammaInto,
+                                                                  const c10::optional<at::Tensor> &dbetaInto) {
   checkBf16(dy, "dy");
   checkBf16(x, "x");
   c10::cuda::CUDAGuard g(x.device());
   const int C = (int)x.size(-1), M = (int)(x.numel() / C);
   auto dx = at::empty_like(x);
-  auto dgamma = at::empty_like(gamma), dbeta = at::empty_like(gamma);
+  // with both targets given the parameter gradients are added to them (they are the parameters' .grad)
+  const bool into = dgammaInto.has_value() && dgammaInto->defined() && dbetaInto.has_value() && dbetaInto->defined();
+  if (into) {
+    checkBf16(*dgammaInto, "dgamma_into");
+    checkBf16(*dbetaInto, "dbeta_into");
+    TORCH_CHECK(dgammaInto->numel() == C && dbetaInto->numel() == C, "gradient targets must have one element per column");
+  }
+  auto dgamma = into ? *dgammaInto : at::empty_like(gamma), dbeta = into ? *dbetaInto : at::empty_like(gamma);
   auto partial = at::empty({fcxLnPartials(M), 2, C}, x.options().dtype(at::kFloat));
   const void *dr = dres.has_value() && dres->defined() ? dres->data_ptr() : nullptr;
   CUDA_OK(fcxLayerNormBwd(dy.data_ptr(), x.data_ptr(), gamma.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(), dr,
-                          dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), partial.data_ptr<float>(), M, C, 0, cur()));
+                          dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), partial.data_ptr<float>(), M, C, into ? 1 : 0, cur()));
   return {dx, dgamma, dbeta};
 }
 
@@ -74,26 +83,37 @@ static at::Tensor biasGeluFwd(const at::Tensor &x, const at::Tensor &bias) {
 }
 
 // returns (dx, dbias)
-static std::tuple<at::Tensor, at::Tensor> biasGeluBwd(const at::Tensor &dy, const at::Tensor &x, const at::Tensor &bias) {
+static std::tuple<at::Tensor, at::Tensor> biasGeluBwd(const at::Tensor &dy, const at::Tensor &x, const at::Tensor &bias,
+                                                        const c10::optional<at::Tensor> &dbiasInto) {
   checkBf16(dy, "dy");
   checkBf16(x, "x");
   c10::cuda::CUDAGuard g(x.device());
   const int C = (int)x.size(-1), M = (int)(x.numel() / C);
   auto dx = at::empty_like(x);
   CUDA_OK(fcxBiasGeluBwd(dy.data_ptr(), x.data_ptr(), bias.data_ptr(), dx.data_ptr(), M, C, cur()));
-  auto dbias = at::empty_like(bias);
+  const bool into = dbiasInto.has_value() && dbiasInto->defined();
+  if (into) {
+    checkBf16(*dbiasInto, "dbias_into");
+    TORCH_CHECK(dbiasInto->numel() == C, "dbias_into must have one element per column");
+  }
+  auto dbias = into ? *dbiasInto : at::empty_like(bias);
   auto partial = at::empty({fcxColSumPartials(M), C}, x.options().dtype(at::kFloat));
-  CUDA_OK(fcxColSum(dx.data_ptr(), dbias.data_ptr(), partial.data_ptr<float>(), M, C, 0, cur()));
+  CUDA_OK(fcxColSum(dx.data_ptr(), dbias.data_ptr(), partial.data_ptr<float>(), M, C, into ? 1 : 0, cur()));
   return {dx, dbias};
 }
 
-static at::Tensor colSum(const at::Tensor &a) {
+static at::Tensor colSum(const at::Tensor &a, const c10::optional<at::Tensor> &intoT) {
   checkBf16(a, "a");
   c10::cuda::CUDAGuard g(a.device());
   const int C = (int)a.size(-1), M = (int)(a.numel() / C);
-  auto out = at::empty({C}, a.options());
+  const bool into = intoT.has_value() && intoT->defined();
+  if (into) {
+    checkBf16(*intoT, "into");
+    TORCH_CHECK(intoT->numel() == C, "into must have one element per column");
+  }
+  auto out = into ? *intoT : at::empty({C}, a.options());
   auto partial = at::empty({fcxColSumPartials(M), C}, a.options().dtype(at::kFloat));
-  CUDA_OK(fcxColSum(a.data_ptr(), out.data_ptr(), partial.data_ptr<float>(), M, C, 0, cur()));
+  CUDA_OK(fcxColSum(a.data_ptr(), out.data_ptr(), partial.data_ptr<float>(), M, C, into ? 1 : 0, cur()));
   return out;
 }
 
@@ -245,10 +265,11 @@ PYBIND11_MODULE(_flagcx_torch, m) {
   fcxt::bindBackend(m);
   fcxt::bindFused(m);
   m.def("layernorm_fwd", &fcxt::layernormFwd, py::arg("x"), py::arg("delta"), py::arg("gamma"), py::arg("beta"), py::arg("eps") = 1e-5);
-  m.def("layernorm_bwd", &fcxt::layernormBwd);
+  m.def("layernorm_bwd", &fcxt::layernormBwd, py::arg("dy"), py::arg("x"), py::arg("gamma"), py::arg("mean"), py::arg("rstd"), py::arg("dres"),
+        py::arg("dgamma_into") = py::none(), py::arg("dbeta_into") = py::none());
   m.def("bias_gelu_fwd", &fcxt::biasGeluFwd);
-  m.def("bias_gelu_bwd", &fcxt::biasGeluBwd);
-  m.def("col_sum", &fcxt::colSum);
+  m.def("bias_gelu_bwd", &fcxt::biasGeluBwd, py::arg("dy"), py::arg("x"), py::arg("bias"), py::arg("dbias_into") = py::none());
+  m.def("col_sum", &fcxt::colSum, py::arg("a"), py::arg("into") = py::none());
   m.def("cross_entropy_", &fcxt::crossEntropy);
   m.def("adamw_", &fcxt::adamw, py::arg("master"), py::arg("param"), py::arg("grad"), py::arg("m"), py::arg("v"), py::arg("lr"),
         py::arg("b1"), py::arg("b2"), py::arg("eps"), py::arg("wd"), py::arg("step"), py::arg("grad_scale"), py::arg("zero_grad"),

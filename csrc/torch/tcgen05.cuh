@@ -150,4 +150,17 @@ inline bool makeTileMap(CUtensorMap *m, const void *base, uint64_t rows, uint64_
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Row-major bf16 [rows, cols] output with `ld` elements between rows, written (or added to) in blocks of 32 rows x 32
+// columns that lie in shared memory with the 64-byte swizzle; the unit clips blocks at the matrix edge.
+inline bool makeStoreMap(CUtensorMap *m, const void *base, uint64_t rows, uint64_t cols, uint64_t ld) {
+  EncodeTiledFn fn = encodeFn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void *)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace fcxmma

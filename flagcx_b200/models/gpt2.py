@@ -124,6 +124,18 @@ class GPT2(nn.Module):
     def num_params(self) -> int:
         return sum(p.numel() for p in self.parameters())
 
+    def direct_grad_parameters(self):
+        """``(parameter, counted)`` pairs for ``flagcx_b200.ops.enable_direct_grad``: parameters whose gradient this
+        model's fused ops can add straight into ``.grad``.  ``counted`` is False for the token embedding: it is tied
+        to the output projection, whose weight gradient is added in place early in the backward pass, while the
+        embedding lookup's own gradient still arrives through autograd at the very end and announces the parameter."""
+        out = []
+        for p in self.parameters():
+            if p is self.wpe:
+                continue
+            out.append((p, p is not self.wte))
+        return out
+
 
 def flatten_parameters(model: nn.Module, dtype=torch.bfloat16, device="cuda", buffer: torch.Tensor | None = None):
     """Move every parameter into one flat ``dtype`` buffer (each parameter

@@ -9,6 +9,32 @@ def _n():
     return flagcx_b200.native()
 
 
+def enable_direct_grad(param: torch.Tensor, ready=None) -> None:
+    """Let this library's backward kernels add a parameter's gradient straight into ``param.grad`` (which must
+    exist, e.g. as a view of a flat gradient buffer that the optimizer zeroes) instead of returning a temporary
+    that autograd then adds with a kernel of its own.  ``ready(param)`` is called once the contribution has been
+    queued: autograd's post-accumulate hooks do not fire for a gradient that never passes through autograd.
+    Only for parameters that enter the graph through exactly one of this module's ops."""
+    param._fcx_direct_grad = True
+    param._fcx_grad_ready = ready
+
+
+def _direct(param):
+    """The tensor to accumulate into, or None when the parameter's gradient goes through autograd."""
+    if param is None or not getattr(param, "_fcx_direct_grad", False):
+        return None
+    g = param.grad
+    if g is None or g.dtype != torch.bfloat16 or not g.is_contiguous():
+        return None
+    return g
+
+
+def _done(param):
+    cb = getattr(param, "_fcx_grad_ready", None)
+    if cb is not None:
+        cb(param)
+
+
 class _AddLayerNorm(torch.autograd.Function):
     """(res, y) = (x + delta, LayerNorm(x + delta)); one pass over the row."""
 
@@ -17,12 +43,20 @@ class _AddLayerNorm(torch.autograd.Function):
         res, y, mean, rstd = _n().layernorm_fwd(x, delta, gamma, beta, eps)
         ctx.save_for_backward(res, gamma, mean, rstd)
         ctx.has_delta = delta is not None
+        ctx.params = (gamma, beta)
         return res, y
 
     @staticmethod
     def backward(ctx, dres, dy):
         res, gamma, mean, rstd = ctx.saved_tensors
         dres = dres.contiguous() if dres is not None else None
+        pg, pb = ctx.params
+        gg, gb = _direct(pg), _direct(pb)
+        if gg is not None and gb is not None:
+            dx, _, _ = _n().layernorm_bwd(dy.contiguous(), res, gamma, mean, rstd, dres, gg, gb)
+            _done(pg)
+            _done(pb)
+            return dx, (dx if ctx.has_delta else None), None, None, None
         dx, dgamma, dbeta = _n().layernorm_bwd(dy.contiguous(), res, gamma, mean, rstd, dres)
         return dx, (dx if ctx.has_delta else None), dgamma, dbeta, None
 
@@ -36,11 +70,17 @@ class _BiasGelu(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, bias):
         ctx.save_for_backward(x, bias)
+        ctx.bias_param = bias
         return _n().bias_gelu_fwd(x, bias)
 
     @staticmethod
     def backward(ctx, dy):
         x, bias = ctx.saved_tensors
+        gb = _direct(ctx.bias_param)
+        if gb is not None:
+            dx, _ = _n().bias_gelu_bwd(dy.contiguous(), x, bias, gb)
+            _done(ctx.bias_param)
+            return dx, None
         dx, dbias = _n().bias_gelu_bwd(dy.contiguous(), x, bias)
         return dx, dbias
 
@@ -118,6 +158,7 @@ class _Linear(torch.autograd.Function):
         ctx.save_for_backward(x2, w)
         ctx.has_bias = bias is not None
         ctx.in_shape = x.shape
+        ctx.params = (w, bias)
         y = gemm(x2, w, False, False, bias)
         return y.view(*x.shape[:-1], w.shape[0])
 
@@ -130,10 +171,22 @@ class _Linear(torch.autograd.Function):
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, w, False, True).view(ctx.in_shape)      # [T,O] x [O,I]: w read as the [K=O, N=I] operand
+        pw, pb = ctx.params
         if ctx.needs_input_grad[1]:
-            dw = gemm(dy2, x2, True, True)                           # [O,T] x [T,I]: both read transposed, K = tokens
+            gw = _direct(pw)
+            if gw is not None and gw.shape[1] % 2 == 0:
+                # [O,T] x [T,I]: both read transposed, K = tokens; added into the parameter's gradient in place
+                _n().gemm(dy2, x2, True, True, None, 0, _err_flag(dy2.device), -1, gw, True)
+                _done(pw)
+            else:
+                dw = gemm(dy2, x2, True, True)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = _n().col_sum(dy2)
+            gb = _direct(pb)
+            if gb is not None:
+                _n().col_sum(dy2, gb)
+                _done(pb)
+            else:
+                db = _n().col_sum(dy2)
         return dx, dw, db
 
 

@@ -107,6 +107,15 @@ class DataParallelTrainer:
                 cur_params = []
         for i, p in enumerate(params):
             p.register_post_accumulate_grad_hook(self._make_hook(i))
+        # Gradients that the fused backward kernels add straight into the flat buffer never pass through autograd:
+        # those parameters announce themselves through the same bucket bookkeeping.
+        self.direct_grads = 0
+        if os.environ.get("FLAGCX_DDP_DIRECT_GRAD", "1") != "0" and hasattr(model, "direct_grad_parameters"):
+            from flagcx_b200.ops import enable_direct_grad
+            index = {id(p): i for i, p in enumerate(params)}
+            for p, counted in model.direct_grad_parameters():
+                enable_direct_grad(p, self._make_hook(index[id(p)]) if counted else None)
+                self.direct_grads += 1
         # Side stream: a bucket's all-reduce and its share of the optimizer step run here, beside the rest of
         # the backward pass.  A parameter whose gradient is complete is no longer read by this step's backward
         # (the tied embedding sits in the bucket that closes last), so updating it early is safe.
