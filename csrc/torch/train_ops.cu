@@ -33,42 +33,86 @@ __device__ __forceinline__ float warpMax(float v) {
 
 struct alignas(16) Bf8 { bf16 v[8]; };
 
+// Eight bf16 <-> eight floats.  The 16 bytes move as ONE 128-bit access wherever they live (global or shared memory:
+// read field by field, a vector in shared memory turns into eight 2-byte loads); a bf16 is the upper half of a float.
 __device__ __forceinline__ void unpack8(const Bf8 &p, float *f) {
+  const uint4 u = *reinterpret_cast<const uint4 *>(&p);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-  for (int i = 0; i < 8; i++) f[i] = __bfloat162float(p.v[i]);
+  for (int i = 0; i < 4; i++) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
 }
 __device__ __forceinline__ Bf8 pack8(const float *f) {
-  Bf8 p;
+  uint4 u;
+  uint32_t *w = reinterpret_cast<uint32_t *>(&u);
 #pragma unroll
-  for (int i = 0; i < 8; i++) p.v[i] = __float2bfloat16_rn(f[i]);
+  for (int i = 0; i < 4; i++) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t *>(&h);
+  }
+  Bf8 p;
+  *reinterpret_cast<uint4 *>(&p) = u;
   return p;
 }
 
 // ---------------------------------------------------------------- LayerNorm
-// One warp per row; C is a multiple of 256 and at most 256*MAXV, so each lane
-// keeps its C/32 values in registers between the statistics and the output.
-template <int MAXV>
-__global__ void __launch_bounds__(256) lnFwdKernel(const bf16 *__restrict__ x, const bf16 *__restrict__ delta,
-                                                   const bf16 *__restrict__ gamma, const bf16 *__restrict__ beta,
-                                                   bf16 *__restrict__ resOut, bf16 *__restrict__ y, float *__restrict__ mean,
-                                                   float *__restrict__ rstd, int M, int C, float eps) {
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  const int nwarps = (gridDim.x * blockDim.x) >> 5;
-  const int nv = C / 256;  // 16-byte vectors per lane
-  for (int row = warp; row < M; row += nwarps) {
-    const Bf8 *xr = (const Bf8 *)(x + (size_t)row * C);
-    const Bf8 *dr = delta ? (const Bf8 *)(delta + (size_t)row * C) : nullptr;
+// One warp per row, persistent over rows, 16 warps per SM (8 for rows wider than 1024).  The rows a warp will work on
+// are streamed into a private three-deep ring in shared memory with cp.async two rows ahead, so that every SM keeps
+// ~128 KB of loads in flight whatever the warps are computing; a lane copies exactly the 16-byte vectors that it later reads, so
+// the ring needs no barrier, only cp.async.wait_group.  C is a multiple of 256 and at most 256 * MAXV.
+__device__ __forceinline__ void cpAsync16(void *smemDst, const void *gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smemDst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cpAsyncCommit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cpAsyncWait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int MAXV, int STAGES, int LN_WARPS>
+__global__ void __launch_bounds__(LN_WARPS * 32, 1) lnFwdKernel(const bf16 *__restrict__ x, const bf16 *__restrict__ delta,
+                                                                const bf16 *__restrict__ gamma, const bf16 *__restrict__ beta,
+                                                                bf16 *__restrict__ resOut, bf16 *__restrict__ y,
+                                                                float *__restrict__ mean, float *__restrict__ rstd, int M, int C,
+                                                                float eps) {
+  extern __shared__ __align__(16) uint8_t lnSmem[];
+  const int warpInCta = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = blockIdx.x * LN_WARPS + warpInCta, nwarps = gridDim.x * LN_WARPS;
+  const int nv = C / 256;  // 16-byte vectors per lane and row
+  const int narr = delta ? 2 : 1;
+  const size_t rowBytes = (size_t)C * 2;
+  uint8_t *ring = lnSmem + (size_t)warpInCta * STAGES * 2 * rowBytes;
+  auto issue = [&](int row, int st) {
+    if (row < M) {
+      uint8_t *dst = ring + (size_t)st * 2 * rowBytes;
+#pragma unroll
+      for (int i = 0; i < MAXV; i++)
+        if (i < nv) {
+          cpAsync16(dst + (i * 32 + lane) * 16, (const uint8_t *)(x + (size_t)row * C) + (i * 32 + lane) * 16);
+          if (narr == 2) cpAsync16(dst + rowBytes + (i * 32 + lane) * 16, (const uint8_t *)(delta + (size_t)row * C) + (i * 32 + lane) * 16);
+        }
+    }
+    cpAsyncCommit();  // an empty group past the last row keeps the group count uniform
+  };
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; st++) issue(warp + st * nwarps, st);
+  int k = 0;
+  for (int row = warp; row < M; row += nwarps, k++) {
+    issue(row + (STAGES - 1) * nwarps, (k + STAGES - 1) % STAGES);
+    cpAsyncWait<STAGES - 1>();
+    const Bf8 *xr = (const Bf8 *)(ring + (size_t)(k % STAGES) * 2 * rowBytes);
+    const Bf8 *dr = (const Bf8 *)((const uint8_t *)xr + rowBytes);
     float v[MAXV][8];
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < MAXV; i++)
       if (i < nv) {
         unpack8(xr[i * 32 + lane], v[i]);
-        if (dr) {
+        if (narr == 2) {
           float d[8];
           unpack8(dr[i * 32 + lane], d);
 #pragma unroll
-          for (int k = 0; k < 8; k++) v[i][k] += d[k];
+          for (int j = 0; j < 8; j++) v[i][j] += d[j];
           // the residual stream is kept in bf16: round it here so that the
           // statistics see what the next layer will read
           Bf8 r = pack8(v[i]);
@@ -76,7 +120,7 @@ __global__ void __launch_bounds__(256) lnFwdKernel(const bf16 *__restrict__ x, c
           unpack8(r, v[i]);
         }
 #pragma unroll
-        for (int k = 0; k < 8; k++) s += v[i][k];
+        for (int j = 0; j < 8; j++) s += v[i][j];
       }
     const float mu = warpSum(s) / C;
     float q = 0.f;
@@ -84,7 +128,7 @@ __global__ void __launch_bounds__(256) lnFwdKernel(const bf16 *__restrict__ x, c
     for (int i = 0; i < MAXV; i++)
       if (i < nv) {
 #pragma unroll
-        for (int k = 0; k < 8; k++) { float d = v[i][k] - mu; q += d * d; }
+        for (int j = 0; j < 8; j++) { float d = v[i][j] - mu; q += d * d; }
       }
     const float rs = rsqrtf(warpSum(q) / C + eps);
     if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
@@ -95,40 +139,72 @@ __global__ void __launch_bounds__(256) lnFwdKernel(const bf16 *__restrict__ x, c
         unpack8(((const Bf8 *)gamma)[i * 32 + lane], g);
         unpack8(((const Bf8 *)beta)[i * 32 + lane], b);
 #pragma unroll
-        for (int k = 0; k < 8; k++) o[k] = (v[i][k] - mu) * rs * g[k] + b[k];
+        for (int j = 0; j < 8; j++) o[j] = (v[i][j] - mu) * rs * g[j] + b[j];
         ((Bf8 *)(y + (size_t)row * C))[i * 32 + lane] = pack8(o);
       }
   }
+  cpAsyncWait<0>();
 }
 
 // Backward, part 1: dx = rstd * (g*dy - mean(g*dy) - xhat * mean(g*dy*xhat)) [+ dres].
-// One warp per row, few registers, so that several CTAs share an SM and hide
-// the memory latency.
-template <int MAXV>
-__global__ void __launch_bounds__(256, 3) lnBwdDxKernel(const bf16 *__restrict__ dy, const bf16 *__restrict__ x,
-                                                        const bf16 *__restrict__ gamma, const float *__restrict__ mean,
-                                                        const float *__restrict__ rstd, const bf16 *__restrict__ dres,
-                                                        bf16 *__restrict__ dx, int M, int C) {
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+// Same streaming scheme for dy and x; the residual gradient, needed only for the last step of a row, is loaded into
+// registers when the row's turn begins.
+template <int MAXV, int STAGES, int LN_WARPS>
+__global__ void __launch_bounds__(LN_WARPS * 32, 1) lnBwdDxKernel(const bf16 *__restrict__ dy, const bf16 *__restrict__ x,
+                                                                  const bf16 *__restrict__ gamma, const float *__restrict__ mean,
+                                                                  const float *__restrict__ rstd, const bf16 *__restrict__ dres,
+                                                                  bf16 *__restrict__ dx, int M, int C) {
+  extern __shared__ __align__(16) uint8_t lnSmem[];
+  const int warpInCta = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = blockIdx.x * LN_WARPS + warpInCta, nwarps = gridDim.x * LN_WARPS;
   const int nv = C / 256;
-  for (int row = warp; row < M; row += nwarps) {
-    const float mu = mean[row], rs = rstd[row];
+  const size_t rowBytes = (size_t)C * 2;
+  uint8_t *ring = lnSmem + (size_t)warpInCta * STAGES * 2 * rowBytes;
+  auto issue = [&](int row, int st) {
+    if (row < M) {
+      uint8_t *dst = ring + (size_t)st * 2 * rowBytes;
+#pragma unroll
+      for (int i = 0; i < MAXV; i++)
+        if (i < nv) {
+          const size_t off = (size_t)(i * 32 + lane) * 16;
+          cpAsync16(dst + off, (const uint8_t *)(dy + (size_t)row * C) + off);
+          cpAsync16(dst + rowBytes + off, (const uint8_t *)(x + (size_t)row * C) + off);
+        }
+    }
+    cpAsyncCommit();
+  };
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; st++) issue(warp + st * nwarps, st);
+  float muN = warp < M ? mean[warp] : 0.f, rsN = warp < M ? rstd[warp] : 0.f;  // statistics one row ahead
+  int k = 0;
+  for (int row = warp; row < M; row += nwarps, k++) {
+    issue(row + (STAGES - 1) * nwarps, (k + STAGES - 1) % STAGES);
+    const float mu = muN, rs = rsN;
+    if (row + nwarps < M) { muN = mean[row + nwarps]; rsN = rstd[row + nwarps]; }
+    Bf8 dr[MAXV];
+    if (dres) {
+#pragma unroll
+      for (int i = 0; i < MAXV; i++)
+        if (i < nv) dr[i] = ((const Bf8 *)(dres + (size_t)row * C))[i * 32 + lane];
+    }
+    cpAsyncWait<STAGES - 1>();
+    const uint8_t *base = ring + (size_t)(k % STAGES) * 2 * rowBytes;
+    const Bf8 *dyr = (const Bf8 *)base, *xr = (const Bf8 *)(base + rowBytes);
     float gy[MAXV][8], xh[MAXV][8];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < MAXV; i++)
       if (i < nv) {
         float d[8], xv[8], g[8];
-        unpack8(((const Bf8 *)(dy + (size_t)row * C))[i * 32 + lane], d);
-        unpack8(((const Bf8 *)(x + (size_t)row * C))[i * 32 + lane], xv);
+        unpack8(dyr[i * 32 + lane], d);
+        unpack8(xr[i * 32 + lane], xv);
         unpack8(((const Bf8 *)gamma)[i * 32 + lane], g);
 #pragma unroll
-        for (int k = 0; k < 8; k++) {
-          xh[i][k] = (xv[k] - mu) * rs;
-          gy[i][k] = g[k] * d[k];
-          s1 += gy[i][k];
-          s2 += gy[i][k] * xh[i][k];
+        for (int j = 0; j < 8; j++) {
+          xh[i][j] = (xv[j] - mu) * rs;
+          gy[i][j] = g[j] * d[j];
+          s1 += gy[i][j];
+          s2 += gy[i][j] * xh[i][j];
         }
       }
     s1 = warpSum(s1) / C;
@@ -137,15 +213,16 @@ __global__ void __launch_bounds__(256, 3) lnBwdDxKernel(const bf16 *__restrict__
     for (int i = 0; i < MAXV; i++)
       if (i < nv) {
         float o[8];
-        if (dres) unpack8(((const Bf8 *)(dres + (size_t)row * C))[i * 32 + lane], o);
+        if (dres) unpack8(dr[i], o);
 #pragma unroll
-        for (int k = 0; k < 8; k++) {
-          float t = rs * (gy[i][k] - s1 - xh[i][k] * s2);
-          o[k] = dres ? o[k] + t : t;
+        for (int j = 0; j < 8; j++) {
+          float t = rs * (gy[i][j] - s1 - xh[i][j] * s2);
+          o[j] = dres ? o[j] + t : t;
         }
         ((Bf8 *)(dx + (size_t)row * C))[i * 32 + lane] = pack8(o);
       }
   }
+  cpAsyncWait<0>();
 }
 
 // Backward, part 2: dgamma[c] = sum_r dy[r,c] * xhat[r,c], dbeta[c] = sum_r dy[r,c].
@@ -161,17 +238,26 @@ __global__ void __launch_bounds__(256) lnBwdParamKernel(const bf16 *__restrict__
   const int rowsPer = (M + gridDim.y - 1) / gridDim.y;
   const int r0 = blockIdx.y * rowsPer, r1 = min(M, r0 + rowsPer);
   int r = r0 + ty;
-  for (; r + 32 < r1; r += 64) {  // two rows in flight per thread
-    float d0[8], x0[8], d1[8], x1[8];
-    unpack8(*(const Bf8 *)(dy + (size_t)r * C + col0 + tx * 8), d0);
-    unpack8(*(const Bf8 *)(x + (size_t)r * C + col0 + tx * 8), x0);
-    unpack8(*(const Bf8 *)(dy + (size_t)(r + 32) * C + col0 + tx * 8), d1);
-    unpack8(*(const Bf8 *)(x + (size_t)(r + 32) * C + col0 + tx * 8), x1);
-    const float m0 = mean[r], s0 = rstd[r], m1 = mean[r + 32], s1 = rstd[r + 32];
+  for (; r + 96 < r1; r += 128) {  // four rows (eight 16-byte loads) in flight per thread
+    Bf8 pd[4], px[4];
+    float m[4], sd[4];
 #pragma unroll
-    for (int k = 0; k < 8; k++) {
-      dg[k] += d0[k] * (x0[k] - m0) * s0 + d1[k] * (x1[k] - m1) * s1;
-      db[k] += d0[k] + d1[k];
+    for (int u = 0; u < 4; u++) {
+      pd[u] = *(const Bf8 *)(dy + (size_t)(r + 32 * u) * C + col0 + tx * 8);
+      px[u] = *(const Bf8 *)(x + (size_t)(r + 32 * u) * C + col0 + tx * 8);
+      m[u] = mean[r + 32 * u];
+      sd[u] = rstd[r + 32 * u];
+    }
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      float d0[8], x0[8];
+      unpack8(pd[u], d0);
+      unpack8(px[u], x0);
+#pragma unroll
+      for (int k = 0; k < 8; k++) {
+        dg[k] += d0[k] * (x0[k] - m[u]) * sd[u];
+        db[k] += d0[k];
+      }
     }
   }
   for (; r < r1; r += 32) {
@@ -296,7 +382,20 @@ __global__ void __launch_bounds__(256) colSumKernel(const bf16 *__restrict__ a, 
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   const int rowsPer = (M + gridDim.y - 1) / gridDim.y;
   const int r0 = blockIdx.y * rowsPer, r1 = min(M, r0 + rowsPer);
-  for (int r = r0 + ty; r < r1; r += 32) {
+  int r = r0 + ty;
+  for (; r + 96 < r1; r += 128) {  // four rows in flight per thread
+    Bf8 p[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) p[u] = *(const Bf8 *)(a + (size_t)(r + 32 * u) * C + col0 + tx * 8);
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      float v[8];
+      unpack8(p[u], v);
+#pragma unroll
+      for (int k = 0; k < 8; k++) acc[k] += v[k];
+    }
+  }
+  for (; r < r1; r += 32) {
     float v[8];
     unpack8(*(const Bf8 *)(a + (size_t)r * C + col0 + tx * 8), v);
 #pragma unroll
@@ -394,6 +493,108 @@ __global__ void __launch_bounds__(1024) ceFwdBwdKernel(bf16 *__restrict__ logits
   }
 }
 
+// The same for rows that fit twice into shared memory (Vpad <= 56 K): persistent CTAs, one per SM, walk the rows; the
+// row a CTA works on lies in shared memory, and the next row streams in with cp.async during the three passes over the
+// current one, so the logits are read from DRAM exactly once and the reads never wait for the arithmetic.  A thread
+// copies exactly the vectors it reads itself, so the only synchronisation of the ring is cp.async.wait_group.
+__global__ void __launch_bounds__(1024, 1) ceFwdBwdStreamKernel(bf16 *__restrict__ logits, const int64_t *__restrict__ targets,
+                                                                float *__restrict__ losses, int M, int V, int Vpad,
+                                                                float gradScale) {
+  extern __shared__ __align__(16) uint8_t ceSmem[];
+  __shared__ float red[2][32];
+  __shared__ float bcast[2];
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  const int nvecPad = Vpad / 8;
+  const size_t rowBytes = (size_t)Vpad * 2;
+  auto issue = [&](int row, int b) {
+    if (row < M) {
+      const uint8_t *src = (const uint8_t *)(logits + (size_t)row * Vpad);
+      uint8_t *dst = ceSmem + (size_t)b * rowBytes;
+      for (int i = tid; i < nvecPad; i += 1024) cpAsync16(dst + (size_t)i * 16, src + (size_t)i * 16);
+    }
+    cpAsyncCommit();
+  };
+  issue(blockIdx.x, 0);
+  int k = 0;
+  for (int row = blockIdx.x; row < M; row += gridDim.x, k++) {
+    issue(row + gridDim.x, (k + 1) & 1);
+    bf16 *lr = logits + (size_t)row * Vpad;
+    const int tgt = (int)targets[row];
+    const float tgtLogit = (tgt >= 0 && tgt < V) ? __bfloat162float(lr[tgt]) : 0.f;  // before the row is overwritten
+    cpAsyncWait<1>();
+    Bf8 *sr = (Bf8 *)(ceSmem + (size_t)(k & 1) * rowBytes);
+    // pass 1: row maximum, on packed bf16 pairs
+    __nv_bfloat162 mx2 = __floats2bfloat162_rn(-INFINITY, -INFINITY);
+    float mx = -INFINITY;
+    for (int i = tid; i < nvecPad; i += 1024) {
+      if (i * 8 + 8 <= V) {
+        const Bf8 pv = sr[i];
+        const __nv_bfloat162 *h = (const __nv_bfloat162 *)&pv;
+#pragma unroll
+        for (int j = 0; j < 4; j++) mx2 = __hmax2(mx2, h[j]);
+      } else {
+        float v[8];
+        unpack8(sr[i], v);
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+          if (i * 8 + j < V) mx = fmaxf(mx, v[j]);
+      }
+    }
+    mx = fmaxf(mx, fmaxf(__low2float(mx2), __high2float(mx2)));
+    mx = warpMax(mx);
+    if (lane == 0) red[0][wid] = mx;
+    __syncthreads();
+    if (wid == 0) {
+      float v = warpMax(red[0][lane]);
+      if (lane == 0) bcast[0] = v;
+    }
+    __syncthreads();
+    mx = bcast[0];
+    // pass 2: e = exp(v - max), summed in fp32 and left in the row buffer as bf16 (columns past V become 0), so that
+    // the gradient pass needs no second exponential
+    const float kLog2e = 1.4426950408889634f, mxl = mx * kLog2e;
+    float sum = 0.f;
+    for (int i = tid; i < nvecPad; i += 1024) {
+      float v[8];
+      unpack8(sr[i], v);
+      const bool whole = i * 8 + 8 <= V;
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        float e = exp2f(fmaf(v[j], kLog2e, -mxl));
+        if (!whole && i * 8 + j >= V) e = 0.f;
+        sum += e;
+        v[j] = e;
+      }
+      sr[i] = pack8(v);
+    }
+    sum = warpSum(sum);
+    if (lane == 0) red[1][wid] = sum;
+    __syncthreads();
+    if (wid == 0) {
+      float v = warpSum(red[1][lane]);
+      if (lane == 0) bcast[1] = v;
+    }
+    __syncthreads();
+    sum = bcast[1];
+    if (tid == 0) losses[row] = tgt >= 0 ? (logf(sum) + mx - tgtLogit) : 0.f;
+    // pass 3: gradient = (e / sum - onehot) * scale
+    const float gs = tgt >= 0 ? gradScale : 0.f, scale = gs / sum;
+    const int tgtVec = (tgt >= 0 && tgt < V) ? (tgt >> 3) : -1;
+    for (int i = tid; i < nvecPad; i += 1024) {
+      float v[8];
+      unpack8(sr[i], v);
+#pragma unroll
+      for (int j = 0; j < 8; j++) v[j] *= scale;
+      ((Bf8 *)lr)[i] = pack8(v);
+    }
+    // the target column, by the thread that stored the vector around it a moment ago
+    if (tgtVec >= 0 && (tgtVec & 1023) == tid)
+      lr[tgt] = __float2bfloat16_rn(__bfloat162float(((const bf16 *)sr)[tgt]) * scale - gs);
+    // red / bcast are rewritten only after the next row's first barrier pair; nothing else is shared between rows
+  }
+  cpAsyncWait<0>();
+}
+
 // ---------------------------------------------------------------- AdamW on flat buffers
 // master (fp32) is the truth; param (bf16) is refreshed from it.  The gradient
 // is read once and cleared, so no separate zero_grad pass is needed.
@@ -475,14 +676,25 @@ int fcxLnPartials(int M) { return max(1, min(32, M / 128)); }
 cudaError_t fcxLayerNormFwd(const void *x, const void *delta, const void *gamma, const void *beta, void *resOut, void *y,
                             float *mean, float *rstd, int M, int C, float eps, cudaStream_t s) {
   if (C % 256 != 0 || C > 256 * 8) return cudaErrorInvalidValue;
-  int grid = min(smCount() * 8, (M + 7) / 8);
-  if (C <= 1024)
-    lnFwdKernel<4><<<grid, 256, 0, s>>>((const bf16 *)x, (const bf16 *)delta, (const bf16 *)gamma, (const bf16 *)beta,
-                                        (bf16 *)resOut, (bf16 *)y, mean, rstd, M, C, eps);
-  else
-    lnFwdKernel<8><<<grid, 256, 0, s>>>((const bf16 *)x, (const bf16 *)delta, (const bf16 *)gamma, (const bf16 *)beta,
-                                        (bf16 *)resOut, (bf16 *)y, mean, rstd, M, C, eps);
-  return cudaGetLastError();
+  // rows up to 1024 wide: 16 warps per SM (the arithmetic needs the issue slots), wider rows: 8 warps; either way
+  // warps x 3-deep ring x (x, delta) x row bytes <= 192 KB
+  const int warps = C <= 1024 ? 16 : 8;
+  const int grid = std::max(1, std::min(smCount(), (M + warps - 1) / warps));
+  const size_t smem = (size_t)warps * 3 * 2 * C * 2;
+  auto run = [&](auto kernel) {
+    // both instantiations have the same pointer type, so this lambda exists once: remember the kernels by address
+    static thread_local const void *configured[2] = {nullptr, nullptr};
+    const void *id = (const void *)kernel;
+    if (configured[0] != id && configured[1] != id) {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      if (e != cudaSuccess) return e;
+      configured[configured[0] ? 1 : 0] = id;
+    }
+    kernel<<<grid, warps * 32, smem, s>>>((const bf16 *)x, (const bf16 *)delta, (const bf16 *)gamma, (const bf16 *)beta, (bf16 *)resOut,
+                                          (bf16 *)y, mean, rstd, M, C, eps);
+    return cudaGetLastError();
+  };
+  return C <= 1024 ? run(lnFwdKernel<4, 3, 16>) : run(lnFwdKernel<8, 3, 8>);
 }
 
 // `partial` must hold fcxLnPartials(M) * 2 * C floats.
@@ -490,13 +702,24 @@ cudaError_t fcxLayerNormBwd(const void *dy, const void *x, const void *gamma, co
                             const void *dres, void *dx, void *dgamma, void *dbeta, float *partial, int M, int C, int accumulate,
                             cudaStream_t s) {
   if (C % 256 != 0 || C > 256 * 8) return cudaErrorInvalidValue;
-  int grid = min(smCount() * 6, (M + 7) / 8);
-  if (C <= 1024)
-    lnBwdDxKernel<4><<<grid, 256, 0, s>>>((const bf16 *)dy, (const bf16 *)x, (const bf16 *)gamma, mean, rstd, (const bf16 *)dres,
-                                          (bf16 *)dx, M, C);
-  else
-    lnBwdDxKernel<8><<<grid, 256, 0, s>>>((const bf16 *)dy, (const bf16 *)x, (const bf16 *)gamma, mean, rstd, (const bf16 *)dres,
-                                          (bf16 *)dx, M, C);
+  const int warps = C <= 1024 ? 16 : 8;
+  const int grid = std::max(1, std::min(smCount(), (M + warps - 1) / warps));
+  const size_t smem = (size_t)warps * 3 * 2 * C * 2;  // warps x 3-deep ring x (dy, x) x row bytes <= 192 KB
+  auto run = [&](auto kernel) {
+    // both instantiations have the same pointer type, so this lambda exists once: remember the kernels by address
+    static thread_local const void *configured[2] = {nullptr, nullptr};
+    const void *id = (const void *)kernel;
+    if (configured[0] != id && configured[1] != id) {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      if (e != cudaSuccess) return e;
+      configured[configured[0] ? 1 : 0] = id;
+    }
+    kernel<<<grid, warps * 32, smem, s>>>((const bf16 *)dy, (const bf16 *)x, (const bf16 *)gamma, mean, rstd, (const bf16 *)dres, (bf16 *)dx,
+                                          M, C);
+    return cudaGetLastError();
+  };
+  cudaError_t e = C <= 1024 ? run(lnBwdDxKernel<4, 3, 16>) : run(lnBwdDxKernel<8, 3, 8>);
+  if (e != cudaSuccess) return e;
   int parts = fcxLnPartials(M);
   lnBwdParamKernel<<<dim3(C / 64, parts), 256, 0, s>>>((const bf16 *)dy, (const bf16 *)x, mean, rstd, partial, M, C);
   lnBwdReduceKernel<<<(2 * C + 255) / 256, 256, 0, s>>>(partial, parts, C, (bf16 *)dgamma, (bf16 *)dbeta, accumulate);
@@ -533,7 +756,18 @@ cudaError_t fcxColSum(const void *a, void *out, float *partial, int M, int C, in
 cudaError_t fcxCrossEntropyFwdBwd(void *logits, const int64_t *targets, float *losses, int M, int V, int Vpad, float gradScale,
                                   cudaStream_t s) {
   if (Vpad % 8 != 0 || V > Vpad) return cudaErrorInvalidValue;
-  ceFwdBwdKernel<<<M, 1024, 0, s>>>((bf16 *)logits, targets, losses, V, Vpad, gradScale);
+  const size_t ring = (size_t)Vpad * 2 * 2;
+  if (ring <= 224 * 1024 && ((uintptr_t)logits & 15) == 0) {
+    static thread_local bool attr = false;
+    if (!attr) {
+      cudaError_t e = cudaFuncSetAttribute(ceFwdBwdStreamKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+      if (e != cudaSuccess) return e;
+      attr = true;
+    }
+    ceFwdBwdStreamKernel<<<std::min(M, smCount()), 1024, ring, s>>>((bf16 *)logits, targets, losses, M, V, Vpad, gradScale);
+  } else {
+    ceFwdBwdKernel<<<M, 1024, 0, s>>>((bf16 *)logits, targets, losses, V, Vpad, gradScale);
+  }
   return cudaGetLastError();
 }
 
