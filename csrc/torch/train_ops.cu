@@ -57,6 +57,10 @@ __device__ __forceinline__ Bf8 pack8(const float *f) {
   return p;
 }
 
+// Tickets of the one-launch reductions (colSumFusedKernel, lnBwdParamKernel): one counter per 64-column block.
+__device__ unsigned int gColTickets[1024];
+__device__ unsigned int gLnTickets[1024];
+
 // ---------------------------------------------------------------- LayerNorm
 // One warp per row, persistent over rows, 16 warps per SM (8 for rows wider than 1024).  The rows a warp will work on
 // are streamed into a private three-deep ring in shared memory with cp.async two rows ahead, so that every SM keeps
@@ -227,10 +231,11 @@ __global__ void __launch_bounds__(LN_WARPS * 32, 1) lnBwdDxKernel(const bf16 *__
 
 // Backward, part 2: dgamma[c] = sum_r dy[r,c] * xhat[r,c], dbeta[c] = sum_r dy[r,c].
 // A CTA owns 64 columns and one slice of the rows; partial sums go to
-// `partial` ([gridDim.y][2][C], fp32 scratch) and are folded by lnBwdReduceKernel.
+// `partial` ([gridDim.y][2][C], fp32 scratch); the CTA that finishes a column block last folds them into dgamma / dbeta.
 __global__ void __launch_bounds__(256) lnBwdParamKernel(const bf16 *__restrict__ dy, const bf16 *__restrict__ x,
                                                         const float *__restrict__ mean, const float *__restrict__ rstd,
-                                                        float *__restrict__ partial, int M, int C) {
+                                                        float *__restrict__ partial, int M, int C, bf16 *__restrict__ dgamma,
+                                                        bf16 *__restrict__ dbeta, int accumulate) {
   __shared__ float redG[32][64 + 1], redB[32][64 + 1];
   const int col0 = blockIdx.x * 64;
   const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
@@ -281,19 +286,34 @@ __global__ void __launch_bounds__(256) lnBwdParamKernel(const bf16 *__restrict__
 #pragma unroll 8
     for (int j = 0; j < 32; j++) s += isB ? redB[j][c] : redG[j][c];
     partial[((size_t)blockIdx.y * 2 + (isB ? 1 : 0)) * C + col0 + c] = s;
+    __threadfence();
   }
-}
-
-__global__ void lnBwdReduceKernel(const float *__restrict__ partial, int nparts, int C, bf16 *__restrict__ dgamma,
-                                  bf16 *__restrict__ dbeta, int accumulate) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= 2 * C) return;
-  float s = 0.f;
-#pragma unroll 8
-  for (int p = 0; p < nparts; p++) s += partial[(size_t)p * 2 * C + c];
-  bf16 *dst = c < C ? dgamma + c : dbeta + (c - C);
-  if (accumulate) s += __bfloat162float(*dst);
-  *dst = __float2bfloat16_rn(s);
+  if (dgamma == nullptr) return;  // partial sums only
+  // the CTA that finishes this 64-column block last folds them (ticket scheme of colSumFusedKernel)
+  __shared__ unsigned int ticket;
+  __syncthreads();
+  if (threadIdx.x == 0) ticket = atomicAdd(&gLnTickets[blockIdx.x], 1u);
+  __syncthreads();
+  if (ticket != gridDim.y - 1) return;
+  __threadfence();
+  {
+    // 128 outputs (64 dgamma, 64 dbeta), two halves of the partial sums per output
+    const int o = threadIdx.x & 127, half = threadIdx.x >> 7, c = o & 63;
+    const bool isB = o >= 64;
+    float s = 0.f;
+    for (int p = half; p < (int)gridDim.y; p += 2) s += __ldcg(partial + ((size_t)p * 2 + (isB ? 1 : 0)) * C + col0 + c);
+    __syncthreads();
+    float *fold = &redB[0][0];
+    fold[half * 128 + o] = s;
+    __syncthreads();
+    if (threadIdx.x < 128) {
+      s = fold[o] + fold[128 + o];
+      bf16 *dst = isB ? dbeta + col0 + c : dgamma + col0 + c;
+      if (accumulate) s += __bfloat162float(*dst);
+      *dst = __float2bfloat16_rn(s);
+    }
+  }
+  if (threadIdx.x == 0) gLnTickets[blockIdx.x] = 0;
 }
 
 // ---------------------------------------------------------------- bias + GELU (tanh form)
@@ -423,6 +443,68 @@ __global__ void colSumReduceKernel(const float *__restrict__ partial, int nparts
   out[c] = __float2bfloat16_rn(s);
 }
 
+// Both steps of the column sum in ONE launch: the CTA that finishes a 64-column block last (a ticket per block, taken
+// after the partial sums are visible) folds the block's partial sums and writes the result.  The tickets live in the
+// library image and return to zero by themselves; concurrent calls on one device would share them, so calls must be
+// stream-ordered (they are: the backward pass runs on one stream).
+__global__ void __launch_bounds__(256) colSumFusedKernel(const bf16 *__restrict__ a, float *__restrict__ partial, bf16 *__restrict__ out,
+                                                         int M, int C, int accumulate) {
+  const int col0 = blockIdx.x * 64;
+  const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  const int rowsPer = (M + gridDim.y - 1) / gridDim.y;
+  const int r0 = blockIdx.y * rowsPer, r1 = min(M, r0 + rowsPer);
+  int r = r0 + ty;
+  for (; r + 96 < r1; r += 128) {
+    Bf8 p[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) p[u] = *(const Bf8 *)(a + (size_t)(r + 32 * u) * C + col0 + tx * 8);
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      float v[8];
+      unpack8(p[u], v);
+#pragma unroll
+      for (int k = 0; k < 8; k++) acc[k] += v[k];
+    }
+  }
+  for (; r < r1; r += 32) {
+    float v[8];
+    unpack8(*(const Bf8 *)(a + (size_t)r * C + col0 + tx * 8), v);
+#pragma unroll
+    for (int k = 0; k < 8; k++) acc[k] += v[k];
+  }
+  __shared__ float red[32][64 + 1];
+  __shared__ unsigned int ticket;
+#pragma unroll
+  for (int k = 0; k < 8; k++) red[ty][tx * 8 + k] = acc[k];
+  __syncthreads();
+  if (threadIdx.x < 64) {
+    float s = 0.f;
+#pragma unroll 8
+    for (int j = 0; j < 32; j++) s += red[j][threadIdx.x];
+    partial[(size_t)blockIdx.y * C + col0 + threadIdx.x] = s;
+    __threadfence();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) ticket = atomicAdd(&gColTickets[blockIdx.x], 1u);
+  __syncthreads();
+  if (ticket != gridDim.y - 1) return;
+  __threadfence();
+  // last CTA of this column block: four groups of 64 threads fold a quarter of the partial sums each
+  const int c = threadIdx.x & 63, grp = threadIdx.x >> 6;
+  float s = 0.f;
+  for (int p = grp; p < (int)gridDim.y; p += 4) s += __ldcg(partial + (size_t)p * C + col0 + c);
+  __syncthreads();  // red is reused
+  red[grp][c] = s;
+  __syncthreads();
+  if (threadIdx.x < 64) {
+    s = red[0][c] + red[1][c] + red[2][c] + red[3][c];
+    if (accumulate) s += __bfloat162float(out[col0 + c]);
+    out[col0 + c] = __float2bfloat16_rn(s);
+  }
+  if (threadIdx.x == 0) gColTickets[blockIdx.x] = 0;
+}
+
 // ---------------------------------------------------------------- softmax cross-entropy
 // One CTA per row of logits [M, Vpad] (V valid columns).  Writes the loss of
 // the row and overwrites the logits with (softmax - onehot) * gradScale.
@@ -526,19 +608,18 @@ __global__ void __launch_bounds__(1024, 1) ceFwdBwdStreamKernel(bf16 *__restrict
     // pass 1: row maximum, on packed bf16 pairs
     __nv_bfloat162 mx2 = __floats2bfloat162_rn(-INFINITY, -INFINITY);
     float mx = -INFINITY;
-    for (int i = tid; i < nvecPad; i += 1024) {
-      if (i * 8 + 8 <= V) {
-        const Bf8 pv = sr[i];
-        const __nv_bfloat162 *h = (const __nv_bfloat162 *)&pv;
+    for (int i = tid; i < V / 8; i += 1024) {
+      const Bf8 pv = sr[i];
+      const __nv_bfloat162 *h = (const __nv_bfloat162 *)&pv;
 #pragma unroll
-        for (int j = 0; j < 4; j++) mx2 = __hmax2(mx2, h[j]);
-      } else {
-        float v[8];
-        unpack8(sr[i], v);
+      for (int j = 0; j < 4; j++) mx2 = __hmax2(mx2, h[j]);
+    }
+    for (int i = V / 8 + tid; i < nvecPad; i += 1024) {
+      float v[8];
+      unpack8(sr[i], v);
 #pragma unroll
-        for (int j = 0; j < 8; j++)
-          if (i * 8 + j < V) mx = fmaxf(mx, v[j]);
-      }
+      for (int j = 0; j < 8; j++)
+        if (i * 8 + j < V) mx = fmaxf(mx, v[j]);
     }
     mx = fmaxf(mx, fmaxf(__low2float(mx2), __high2float(mx2)));
     mx = warpMax(mx);
@@ -553,20 +634,33 @@ __global__ void __launch_bounds__(1024, 1) ceFwdBwdStreamKernel(bf16 *__restrict
     // pass 2: e = exp(v - max), summed in fp32 and left in the row buffer as bf16 (columns past V become 0), so that
     // the gradient pass needs no second exponential
     const float kLog2e = 1.4426950408889634f, mxl = mx * kLog2e;
-    float sum = 0.f;
-    for (int i = tid; i < nvecPad; i += 1024) {
+    float sum = 0.f, sumB = 0.f;
+    const int nvecFull = V / 8;
+    for (int i = tid; i < nvecFull; i += 1024) {  // whole vectors: no masks, two independent partial sums
       float v[8];
       unpack8(sr[i], v);
-      const bool whole = i * 8 + 8 <= V;
 #pragma unroll
       for (int j = 0; j < 8; j++) {
-        float e = exp2f(fmaf(v[j], kLog2e, -mxl));
-        if (!whole && i * 8 + j >= V) e = 0.f;
+        float e;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(fmaf(v[j], kLog2e, -mxl)));
+        if (j & 1) sumB += e; else sum += e;
+        v[j] = e;
+      }
+      sr[i] = pack8(v);
+    }
+    for (int i = nvecFull + tid; i < nvecPad; i += 1024) {  // the ragged vector and the padding behind it
+      float v[8];
+      unpack8(sr[i], v);
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        float e = 0.f;
+        if (i * 8 + j < V) asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(fmaf(v[j], kLog2e, -mxl)));
         sum += e;
         v[j] = e;
       }
       sr[i] = pack8(v);
     }
+    sum += sumB;
     sum = warpSum(sum);
     if (lane == 0) red[1][wid] = sum;
     __syncthreads();
@@ -721,8 +815,9 @@ cudaError_t fcxLayerNormBwd(const void *dy, const void *x, const void *gamma, co
   cudaError_t e = C <= 1024 ? run(lnBwdDxKernel<4, 3, 16>) : run(lnBwdDxKernel<8, 3, 8>);
   if (e != cudaSuccess) return e;
   int parts = fcxLnPartials(M);
-  lnBwdParamKernel<<<dim3(C / 64, parts), 256, 0, s>>>((const bf16 *)dy, (const bf16 *)x, mean, rstd, partial, M, C);
-  lnBwdReduceKernel<<<(2 * C + 255) / 256, 256, 0, s>>>(partial, parts, C, (bf16 *)dgamma, (bf16 *)dbeta, accumulate);
+  // C <= 2048 here, so the 64-column blocks fit the ticket array: parameter partials and their reduction in one launch
+  lnBwdParamKernel<<<dim3(C / 64, parts), 256, 0, s>>>((const bf16 *)dy, (const bf16 *)x, mean, rstd, partial, M, C, (bf16 *)dgamma,
+                                                       (bf16 *)dbeta, accumulate);
   return cudaGetLastError();
 }
 
@@ -748,6 +843,10 @@ int fcxColSumPartials(int M) { return max(1, min(32, M / 256)); }
 cudaError_t fcxColSum(const void *a, void *out, float *partial, int M, int C, int accumulate, cudaStream_t s) {
   if (C % 64 != 0) return cudaErrorInvalidValue;
   int parts = fcxColSumPartials(M);
+  if (C / 64 <= 1024) {
+    colSumFusedKernel<<<dim3(C / 64, parts), 256, 0, s>>>((const bf16 *)a, partial, (bf16 *)out, M, C, accumulate);
+    return cudaGetLastError();
+  }
   colSumKernel<<<dim3(C / 64, parts), 256, 0, s>>>((const bf16 *)a, partial, M, C);
   colSumReduceKernel<<<(C + 255) / 256, 256, 0, s>>>(partial, parts, C, (bf16 *)out, accumulate);
   return cudaGetLastError();

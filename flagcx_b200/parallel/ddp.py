@@ -251,18 +251,18 @@ class DataParallelTrainer:
 
     def kernels_per_step(self) -> int:
         """Launches of this framework's own kernels in one step: per layer 2
-        fused LayerNorm forward, 2 x 3 backward (dx, parameter partials, their
-        reduction), bias-GELU forward + 3 backward (dx, bias partials,
-        reduction); the tcgen05 GEMMs of the projections and the LM head; the
-        final LayerNorm (1 + 3), the loss kernel, and per
-        bucket one all-reduce kernel (more than one rank) and one AdamW
-        kernel (one AdamW kernel in all when the optimizer is not overlapped)."""
+        fused LayerNorm forward, 2 x 2 backward (dx; parameter gradients with
+        their reduction), bias-GELU forward + 2 backward (dx; bias gradient);
+        the tcgen05 GEMMs of the projections and the LM head; the final
+        LayerNorm (1 + 2), the loss kernel, and per bucket one all-reduce
+        kernel (more than one rank) and one AdamW kernel (one AdamW kernel in
+        all when the optimizer is not overlapped)."""
         L = len(getattr(self.model, "blocks", []))
-        own = L * (2 + 6 + 1 + 3) + (1 + 3) + 1
+        own = L * (2 + 4 + 1 + 2) + (1 + 2) + 1
         if os.environ.get("FLAGCX_MODEL_GEMM", "own") != "library":
             # tcgen05 GEMMs: four projections per layer and the LM head, each forward + input gradient + weight
-            # gradient; the three biased projections' bias gradients take a column-sum kernel and its reduction
-            own += L * (4 * 3 + 3 * 2) + 3
+            # gradient; the three biased projections' bias gradients take one column-sum kernel each
+            own += L * (4 * 3 + 3) + 3
         nb = len(self.buckets)
         adamw = nb if self.overlap_optimizer else (2 if self.world > 1 and self.split_tail else 1)
         return own + (nb if self.world > 1 else 0) + adamw
