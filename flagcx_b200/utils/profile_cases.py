@@ -7,7 +7,7 @@ couple of warm-up launches and three measured ones, and prints the
 CUDA-event time with the achieved fraction of the measured HBM copy rate
 (MEASURED_PEAKS.json, else 6.65 TB/s).  Cases: adamw, cross_entropy,
 layernorm_fwd, layernorm_bwd, bias_gelu, emu_allreduce (8 emulated ranks,
-two-shot kernel, one cooperative launch on this GPU), emu_allgather, gemm
+two-shot kernel, one cooperative launch on this GPU), emu_allgather, gemm / gemm_one_cta
 (tcgen05 GEMM, against the measured cuBLAS rate), gemm_fp8 (block-scaled e4m3 GEMM), moe_dispatch and moe_layer
 (expert-parallel kernels on a one-rank communicator), emu_allreduce_zc / emu_allreduce_ll / emu_sendrecv (zero-copy,
 LL and grouped send/recv kernels on emulated ranks), gemm_dgrad / gemm_wgrad (transposed-operand GEMMs), gemm_ag /
@@ -192,17 +192,18 @@ def main():
         print(json.dumps({"case": "gemm_fp8", "shape": [M, N, K], "ms": round(ms, 4), "tflops": round(tf, 1),
                           "fraction_of_nominal_fp8_peak": round(tf / 4500.0, 3), "err": int(err.item())}))
         return
-    elif args.case == "gemm":
-        # tensor-core bound: reported against the measured cuBLAS bf16 rate instead of the copy rate
+    elif args.case in ("gemm", "gemm_one_cta"):
+        # tensor-core bound: reported against the measured cuBLAS bf16 rate instead of the copy rate.
+        # "gemm": the kernel the launcher picks for this shape (CTA pairs); "gemm_one_cta": the 128 x 256 kernel
         M, N, K = 8192, 4096, 4096
         a = (torch.randn(M, K, device="cuda") * 0.1).bfloat16()
         b = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
         err = torch.zeros(1, dtype=torch.int32, device="cuda")
-        ms = timed(lambda: nat.gemm_nt(a, b, err))
+        ms = timed(lambda: nat.gemm(a, b, False, False, None, 0, err, 0 if args.case == "gemm_one_cta" else -1))
         pk = ROOT / "MEASURED_PEAKS.json"
         tf_peak = json.loads(pk.read_text())["bf16_tflops"] if pk.exists() else 1590.0
         tf = 2.0 * M * N * K / (ms * 1e-3) / 1e12
-        print(json.dumps({"case": "gemm", "shape": [M, N, K], "ms": round(ms, 4), "tflops": round(tf, 1),
+        print(json.dumps({"case": args.case, "shape": [M, N, K], "ms": round(ms, 4), "tflops": round(tf, 1),
                           "fraction_of_gemm_peak": round(tf / tf_peak, 3), "peak": label, "err": int(err.item())}))
         return
     elif args.case in ("moe_dispatch", "moe_layer"):
