@@ -178,6 +178,13 @@ def main():
             def step(self, tok, tgt):
                 return trainer.step(tok, tgt)
 
+            # end-to-end loop: the loss of every step is read on the host, one step behind the GPU
+            def step_pipelined(self, tok, tgt):
+                return trainer.step_pipelined(tok, tgt)
+
+            def drain(self):
+                return trainer.drain()
+
             def launches_per_step(self):
                 return trainer.kernels_per_step()
 
@@ -225,9 +232,20 @@ def main():
         f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         f0.record()
         last = 0.0
-        for i in range(args.steps):
-            loss = runner.step(host_tok[i % nbuf], host_tgt[i % nbuf])
-            last = float(loss.item())
+        losses_read = 0
+        if hasattr(runner, "step_pipelined"):
+            # this framework's loop: every step's inputs come from pinned host memory and every step's loss is read on
+            # the host, the read of step i after step i+1 has been queued (all reads inside the timed region)
+            for i in range(args.steps):
+                prev = runner.step_pipelined(host_tok[i % nbuf], host_tgt[i % nbuf])
+                if prev is not None:
+                    last, losses_read = prev, losses_read + 1
+            last, losses_read = runner.drain(), losses_read + 1
+        else:
+            for i in range(args.steps):
+                loss = runner.step(host_tok[i % nbuf], host_tgt[i % nbuf])
+                last = float(loss.item())
+                losses_read += 1
         f1.record()
         barrier()
         e2e_ms = max(f0.elapsed_time(f1), 0.0)
@@ -269,7 +287,9 @@ def main():
         "cuda_graph": (args.impl == "ours" and not args.no_graph),
         "clocks": clk,
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * T * 8,
-                "d2h_bytes_per_step": 4, "ms_per_step": round(max(e2e_ms, wall_ms) / args.steps, 3)},
+                "d2h_bytes_per_step": 4, "ms_per_step": round(max(e2e_ms, wall_ms) / args.steps, 3),
+                "losses_read": losses_read,
+                "loss_read": "one step behind the GPU" if hasattr(runner, "step_pipelined") else "after every step"},
         "gpu_launches": int(runner.launches_per_step() * args.steps) if args.impl == "ours" else 0,
         "first_loss": round(first_loss, 4) if first_loss is not None else None,
         "final_loss": round(last, 4),

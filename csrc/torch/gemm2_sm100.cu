@@ -37,10 +37,14 @@ using namespace fcxmma;
 constexpr int BM = 128;    // accumulator rows per CTA (256 per pair)
 constexpr int BN = 256;    // columns per tile
 constexpr int BNH = 128;   // B columns that one CTA holds
-constexpr int BK = 64, STAGES = 5;
+#ifndef FCX_PAIR_STAGES
+#define FCX_PAIR_STAGES 5
+#endif
+constexpr int BK = 64, STAGES = FCX_PAIR_STAGES;
+constexpr int STG_DEPTH = STAGES >= 6 ? 1 : 2;  // staging blocks per epilogue warp: the sixth stage takes the room of the second block
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BNH * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int STG_BYTES = 32 * 64;                 // staging block: 32 rows x 32 bf16 columns
-constexpr int EPI_BYTES = 8 * 2 * STG_BYTES;        // 8 epilogue warps, two blocks each
+constexpr int EPI_BYTES = 8 * STG_DEPTH * STG_BYTES;  // 8 epilogue warps
 constexpr int BIAS_BYTES = 8 * 128 * 4;  // per epilogue warp: its 128 bias values as fp32
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BIAS_BYTES + 1024 + 256;
 constexpr int THREADS = 384;
@@ -209,7 +213,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
     int buf = 0;
     uint32_t accPhase = 0, chunkNo = 0;
     bool live = true;
-    uint8_t *stgBase = epiStage + (size_t)ew * 2 * STG_BYTES;
+    uint8_t *stgBase = epiStage + (size_t)ew * STG_DEPTH * STG_BYTES;
     float *biasW = biasStage + ew * 128;
     const bool reduce = splitK > 1 || p.accumulate;
     for (int t = pair; t < nTiles; t += nPairs) {
@@ -235,8 +239,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
           if (colBase + c0 >= p.N || row0 >= p.M) break;
           uint32_t r[32];
           tmemLd32(tmemBase + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + half * 128 + c0), r);
-          // the staging block used two blocks ago must have been read out by the TMA unit
-          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          // the staging block about to be refilled must have been read out by the TMA unit
+          if (lane == 0) {
+            if (STG_DEPTH == 2) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            else asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          }
           __syncwarp();
           tmemLdWait();
           if (addBias) {
@@ -250,7 +257,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
               r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + f.w);
             }
           }
-          uint4 *stg = (uint4 *)(stgBase + (chunkNo & 1) * STG_BYTES);
+          uint4 *stg = (uint4 *)(stgBase + (chunkNo % STG_DEPTH) * STG_BYTES);
 #pragma unroll
           for (int v = 0; v < 4; v++) {
             uint4 o;

@@ -132,6 +132,8 @@ class DataParallelTrainer:
         self.tail_ctas = int(os.environ.get("FLAGCX_DDP_TAIL_CTAS", "64"))
         self._budget_now = getattr(self, "cta_budget", 0)
 
+        self._loss_host = None
+        self._loss_pending = None
         self.snapshot_grads = False
         self.grad_snapshot = None
         self.use_graph = use_graph
@@ -248,6 +250,31 @@ class DataParallelTrainer:
             loss = self.static_loss
         self.step_no += 1
         return loss
+
+    def step_pipelined(self, tokens: torch.Tensor, targets: torch.Tensor):
+        """``step`` for a training loop that reads every loss on the host without stalling the GPU: the step is
+        queued, its loss is copied into pinned host memory behind it, and the call returns the loss of the PREVIOUS
+        step as a float (None on the first call) - by then that copy has long finished, so the host is back at
+        once to queue the next step while this one runs.  ``drain()`` returns the loss of the last step."""
+        if self._loss_host is None:
+            self._loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
+            self._loss_event = [torch.cuda.Event(), torch.cuda.Event()]
+            self._loss_pending = None
+        loss = self.step(tokens, targets)  # queued; the host does not wait for it
+        slot = 0 if self._loss_pending == 1 else 1
+        self._loss_host[slot].copy_(loss.detach().reshape(1).float(), non_blocking=True)
+        self._loss_event[slot].record(torch.cuda.current_stream(self.device))
+        prev = self.drain()  # the step before this one: finished (or about to) while this one is already queued
+        self._loss_pending = slot
+        return prev
+
+    def drain(self):
+        """Loss of the most recent ``step_pipelined`` call that has not been handed out yet (None if there is none)."""
+        if self._loss_host is None or self._loss_pending is None:
+            return None
+        slot, self._loss_pending = self._loss_pending, None
+        self._loss_event[slot].synchronize()
+        return float(self._loss_host[slot][0])
 
     def kernels_per_step(self) -> int:
         """Launches of this framework's own kernels in one step: per layer 2

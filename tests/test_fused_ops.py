@@ -122,6 +122,36 @@ def test_tiny_gpt2_trains_and_graph_matches_eager(nat):
         assert abs(a - b) < 5e-2, (losses[False], losses[True])
 
 
+def test_pipelined_step_hands_out_every_loss_one_step_late(nat):
+    """step_pipelined from pinned host inputs: the same loss sequence as step + item, each loss one call later."""
+    from flagcx_b200.models.gpt2 import GPT2, GPT2Config
+    from flagcx_b200.parallel.ddp import DataParallelTrainer
+    cfg = GPT2Config.tiny()
+    g = torch.Generator().manual_seed(3)
+    toks = [torch.randint(0, cfg.vocab, (4, cfg.seq_len), generator=g).pin_memory() for _ in range(3)]
+    tgts = [torch.randint(0, cfg.vocab, (4, cfg.seq_len), generator=g).pin_memory() for _ in range(3)]
+    seqs = []
+    for pipelined in (False, True):
+        torch.manual_seed(5)
+        tr = DataParallelTrainer(GPT2(cfg), use_graph=True, lr=1e-3)
+        got = []
+        for i in range(7):
+            if pipelined:
+                prev = tr.step_pipelined(toks[i % 3], tgts[i % 3])
+                assert (prev is None) == (i == 0)
+                if prev is not None:
+                    got.append(prev)
+            else:
+                got.append(float(tr.step(toks[i % 3], tgts[i % 3]).item()))
+        if pipelined:
+            got.append(tr.drain())
+            assert tr.drain() is None
+        seqs.append(got)
+    assert len(seqs[0]) == len(seqs[1]) == 7
+    for a, b in zip(*seqs):
+        assert abs(a - b) < 5e-2, seqs
+
+
 def test_gpt2_matches_plain_torch_forward(nat):
     """Loss of the fused model equals the loss of the same weights run through plain PyTorch ops."""
     from flagcx_b200.models.gpt2 import GPT2, GPT2Config
