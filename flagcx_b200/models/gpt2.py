@@ -125,10 +125,10 @@ class GPT2(nn.Module):
         return sum(p.numel() for p in self.parameters())
 
     def direct_grad_parameters(self):
-        """``(parameter, counted)`` pairs for ``flagcx_b200.ops.enable_direct_grad``: parameters whose gradient this
-        model's fused ops can add straight into ``.grad``.  ``counted`` is False for the token embedding: it is tied
+        """``(parameter, single_use)`` pairs for ``flagcx_b200.ops.enable_direct_grad``: parameters whose gradient this
+        model's fused ops can add straight into ``.grad``.  ``single_use`` is False for the token embedding: it is tied
         to the output projection, whose weight gradient is added in place early in the backward pass, while the
-        embedding lookup's own gradient still arrives through autograd at the very end and announces the parameter."""
+        embedding lookup's own gradient arrives through autograd at the very end."""
         out = []
         for p in self.parameters():
             if p is self.wpe:

@@ -12,9 +12,11 @@ def _n():
 def enable_direct_grad(param: torch.Tensor, ready=None) -> None:
     """Let this library's backward kernels add a parameter's gradient straight into ``param.grad`` (which must
     exist, e.g. as a view of a flat gradient buffer that the optimizer zeroes) instead of returning a temporary
-    that autograd then adds with a kernel of its own.  ``ready(param)`` is called once the contribution has been
-    queued: autograd's post-accumulate hooks do not fire for a gradient that never passes through autograd.
-    Only for parameters that enter the graph through exactly one of this module's ops."""
+    that autograd then adds with a kernel of its own.  The backward function returns None for such a parameter;
+    autograd still runs the parameter's accumulation node, so hooks registered with
+    ``register_post_accumulate_grad_hook`` keep firing, after the kernel that wrote the gradient has been queued.
+    ``ready(param)`` is for callers without such hooks: it is called once per contribution (do not use both, the
+    parameter would be announced twice)."""
     param._fcx_direct_grad = True
     param._fcx_grad_ready = ready
 

@@ -107,14 +107,15 @@ class DataParallelTrainer:
                 cur_params = []
         for i, p in enumerate(params):
             p.register_post_accumulate_grad_hook(self._make_hook(i))
-        # Gradients that the fused backward kernels add straight into the flat buffer never pass through autograd:
-        # those parameters announce themselves through the same bucket bookkeeping.
+        # Gradients that the fused backward kernels add straight into the flat buffer come back from the backward
+        # functions as None.  Autograd still runs the parameter's accumulation node then (with nothing to add) and
+        # with it the post-accumulate hook above, after the kernel that wrote the gradient has been queued: the
+        # bucket bookkeeping needs no second signal (a second one would close buckets early).
         self.direct_grads = 0
         if os.environ.get("FLAGCX_DDP_DIRECT_GRAD", "1") != "0" and hasattr(model, "direct_grad_parameters"):
             from flagcx_b200.ops import enable_direct_grad
-            index = {id(p): i for i, p in enumerate(params)}
-            for p, counted in model.direct_grad_parameters():
-                enable_direct_grad(p, self._make_hook(index[id(p)]) if counted else None)
+            for p, _counted in model.direct_grad_parameters():
+                enable_direct_grad(p)
                 self.direct_grads += 1
         # Side stream: a bucket's all-reduce and its share of the optimizer step run here, beside the rest of
         # the backward pass.  A parameter whose gradient is complete is no longer read by this step's backward
