@@ -23,7 +23,7 @@ static void checkBf16Mat(const at::Tensor &t, const char *name) {
 // Route this rank's tokens to their experts.  All heap tensors belong to one buffer set; epoch is that set's 1-based use count.
 static void moeDispatch(uint64_t comm, const at::Tensor &x, const at::Tensor &topkIdx, at::Tensor &countMat, at::Tensor &countFlags,
                         at::Tensor &recv, at::Tensor &info, at::Tensor &done, int64_t epoch, at::Tensor &slot, at::Tensor &localCounts,
-                        at::Tensor &recvTotal, at::Tensor &err, int64_t ctas) {
+                        at::Tensor &recvTotal, at::Tensor &err, int64_t ctas, int64_t expertsPerRank) {
   checkBf16Mat(x, "x");
   TORCH_CHECK(x.is_contiguous() && topkIdx.is_contiguous() && topkIdx.scalar_type() == at::kInt && topkIdx.dim() == 2, "topk_idx must be int32 [T, K]");
   TORCH_CHECK(topkIdx.size(0) == x.size(0), "topk_idx and x disagree on the token count");
@@ -36,9 +36,11 @@ static void moeDispatch(uint64_t comm, const at::Tensor &x, const at::Tensor &to
   p.H = (int)x.size(1);
   p.K = (int)topkIdx.size(1);
   p.cap = (int)recv.size(0);
-  TORCH_CHECK(recv.size(1) == p.H && info.numel() >= (int64_t)p.cap * 4 && countMat.numel() >= dc.nranks * dc.nranks &&
+  p.L = (int)expertsPerRank;
+  TORCH_CHECK(p.L >= 1 && dc.nranks * p.L <= 64 && p.cap % p.L == 0, "experts_per_rank: 1..64/nranks, dividing the buffer rows");
+  TORCH_CHECK(recv.size(1) == p.H && info.numel() >= (int64_t)p.cap * 4 && countMat.numel() >= (int64_t)dc.nranks * dc.nranks * p.L &&
                   countFlags.numel() >= dc.nranks && done.numel() >= dc.nranks && slot.numel() >= (int64_t)p.T * p.K &&
-                  localCounts.numel() >= dc.nranks,
+                  localCounts.numel() >= dc.nranks * p.L && recvTotal.numel() >= p.L,
               "workspace too small");
   p.countMatOff = heapOffset(comm, countMat);
   p.countFlagOff = heapOffset(comm, countFlags);
@@ -107,7 +109,9 @@ static void moeCombine(uint64_t comm, const at::Tensor &combine, const at::Tenso
 }
 
 void bindMoe(py::module &m) {
-  m.def("moe_dispatch", &moeDispatch);
+  m.def("moe_dispatch", &moeDispatch, py::arg("comm"), py::arg("x"), py::arg("topk_idx"), py::arg("count_mat"), py::arg("count_flags"),
+        py::arg("recv"), py::arg("info"), py::arg("done"), py::arg("epoch"), py::arg("slot"), py::arg("local_counts"), py::arg("recv_total"),
+        py::arg("err"), py::arg("ctas"), py::arg("experts_per_rank") = 1);
   m.def("silu_mul", &siluMul, py::arg("gu"), py::arg("h"), py::arg("rows") = py::none());
   m.def("gemm_dyn_m", &gemmDynM);
   m.def("gemm_rowmap", &gemmRowMap);

@@ -1,5 +1,5 @@
 // Expert-parallel mixture-of-experts: dispatch and combine without a host
-// round trip (one expert per rank).
+// round trip (one or several experts per rank).
 //
 //   fcxMoeDispatch  one cooperative kernel: counts the tokens bound for every
 //                   expert, exchanges the count matrix with all ranks through
@@ -37,7 +37,7 @@ constexpr int THREADS = 512;
 
 __global__ void __launch_bounds__(THREADS, 1) moeDispatchKernel(const FcxDevComm dc, const FcxMoeParams p) {
   cg::grid_group grid = cg::this_grid();
-  const int n = dc.nranks, me = dc.rank, E = n;
+  const int n = dc.nranks, me = dc.rank, L = p.L, E = n * L, capL = p.cap / L;
   const int entries = p.T * p.K;
   __shared__ int warpTotals[THREADS / 32];
   __shared__ int running;
@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(THREADS, 1) moeDispatchKernel(const FcxDevComm
     __threadfence_system();
     fcxdev::stRelease((uint64_t *)(dc.heap[r] + p.countFlagOff) + me, p.epoch);
   }
-  __shared__ int baseOf[FCX_MAX_RANKS];  // where this rank's tokens start in expert e's buffer
+  __shared__ int baseOf[64];  // where this rank's tokens start in expert e's segment
   {
     bool ok = true;
     if ((int)threadIdx.x < n)
@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(THREADS, 1) moeDispatchKernel(const FcxDevComm
         tot += c;
       }
       baseOf[threadIdx.x] = b;
-      if (tot > p.cap && blockIdx.x == 0) *err = 2;  // an expert's buffer would overflow: tokens beyond the capacity are dropped
+      if (tot > capL && blockIdx.x == 0) *err = 2;  // an expert's segment would overflow: tokens beyond the capacity are dropped
     }
     __syncthreads();
   }
@@ -108,18 +108,19 @@ __global__ void __launch_bounds__(THREADS, 1) moeDispatchKernel(const FcxDevComm
     for (int i = gw; i < entries; i += warpsPerGrid) {
       const int e = p.topkIdx[i];
       if (e < 0 || e >= E) continue;
-      const int pos = baseOf[e] + p.slot[i];
-      if (pos >= p.cap) continue;
+      const int inSeg = baseOf[e] + p.slot[i];
+      if (inSeg >= capL) continue;
+      const int dstRank = e / L, pos = (e % L) * capL + inSeg;
       const int t = i / p.K, k = i % p.K;
       const uint4 *src = (const uint4 *)((const __nv_bfloat16 *)p.x + (size_t)t * p.H);
-      uint4 *dst = (uint4 *)(dc.heap[e] + p.recvOff + (size_t)pos * p.H * 2);
+      uint4 *dst = (uint4 *)(dc.heap[dstRank] + p.recvOff + (size_t)pos * p.H * 2);
       int v = lane;
       for (; v + 96 < vecs; v += 128) {
         uint4 a = src[v], b = src[v + 32], c = src[v + 64], d = src[v + 96];
         dst[v] = a; dst[v + 32] = b; dst[v + 64] = c; dst[v + 96] = d;
       }
       for (; v < vecs; v += 32) dst[v] = src[v];
-      if (lane == 0) ((int4 *)(dc.heap[e] + p.infoOff))[pos] = make_int4(me, t, k, 0);
+      if (lane == 0) ((int4 *)(dc.heap[dstRank] + p.infoOff))[pos] = make_int4(me, t, k, 0);
     }
   }
   __threadfence_system();
@@ -132,11 +133,11 @@ __global__ void __launch_bounds__(THREADS, 1) moeDispatchKernel(const FcxDevComm
     if ((int)threadIdx.x < n)
       ok = fcxdev::waitGe(dc, (const uint64_t *)(dc.heap[me] + p.doneOff) + threadIdx.x, p.epoch, threadIdx.x, FCX_WAIT_DEVAPI, 0, p.epoch);
     if (!__syncthreads_and(ok)) { if (threadIdx.x == 0) *err = 1; }
-    if (threadIdx.x == 0) {
+    if ((int)threadIdx.x < L) {
       const int *mat = (const int *)(dc.heap[me] + p.countMatOff);
       int tot = 0;
-      for (int r = 0; r < n; r++) tot += mat[r * E + me];
-      *p.recvTotal = min(tot, p.cap);
+      for (int r = 0; r < n; r++) tot += mat[r * E + me * L + threadIdx.x];
+      p.recvTotal[threadIdx.x] = min(tot, capL);
     }
   }
 }
@@ -199,11 +200,11 @@ __global__ void __launch_bounds__(256) moeCombineKernel(const FcxDevComm dc, con
 }  // namespace
 
 extern "C" cudaError_t fcxMoeDispatch(const FcxDevComm *dc, const FcxMoeParams *p, int ctas, cudaStream_t s) {
-  if (p->H % 8 || p->K < 1 || dc->nranks > FCX_MAX_RANKS) return cudaErrorInvalidValue;
+  if (p->H % 8 || p->K < 1 || dc->nranks > FCX_MAX_RANKS || p->L < 1 || dc->nranks * p->L > 64 || p->cap % p->L) return cudaErrorInvalidValue;
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  ctas = std::max(dc->nranks, std::min(ctas, sms));  // all CTAs must be resident: the kernel synchronises the grid
+  ctas = std::max(dc->nranks * p->L, std::min(ctas, sms));  // one CTA per expert at least; all resident: the kernel synchronises the grid
   void *args[] = {(void *)dc, (void *)p};
   return cudaLaunchCooperativeKernel((const void *)moeDispatchKernel, dim3(ctas), dim3(THREADS), args, 0, s);
 }

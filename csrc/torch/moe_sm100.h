@@ -6,20 +6,22 @@
 
 struct FcxMoeParams {
   const void *x;        // bf16 [T, H] tokens of this rank
-  const int *topkIdx;   // int32 [T, K] expert (= rank) of every choice; values outside [0, nranks) are skipped
+  const int *topkIdx;   // int32 [T, K] expert of every choice (expert e lives on rank e / L as its local expert e % L);
+                        // values outside [0, nranks * L) are skipped
   int T, H, K;
-  int cap;              // rows of the expert input buffer on every rank
+  int L;                // experts per rank (>= 1; nranks * L <= 64)
+  int cap;              // rows of the expert input buffer on every rank: L segments of cap / L rows, one per local expert
   // Offsets into the symmetric heap, equal on every rank.  The caller alternates between two sets of buffers from
   // call to call (a rank may start the next dispatch while a peer still reads what the previous one left).
-  size_t countMatOff;   // int32 [nranks][nranks]: tokens from source s for expert e
+  size_t countMatOff;   // int32 [nranks][nranks * L]: tokens from source s for expert e
   size_t countFlagOff;  // u64 [nranks]: source s has written its row of the matrix (value = epoch)
-  size_t recvOff;       // bf16 [cap][H]: expert input rows, grouped by source rank
+  size_t recvOff;       // bf16 [cap][H]: expert input rows; inside a local expert's segment grouped by source rank
   size_t infoOff;       // int4 [cap]: (source rank, token, choice, 0) of every row
   size_t doneOff;       // u64 [nranks]: source s has finished pushing (value = epoch)
   uint64_t epoch;       // 1-based use count of this buffer set
   int *slot;            // local scratch int32 [T*K]
-  int *localCounts;     // local scratch int32 [nranks]
-  int *recvTotal;       // out, device int32: rows received by this rank's expert
+  int *localCounts;     // local scratch int32 [nranks * L]
+  int *recvTotal;       // out, device int32 [L]: rows received by each of this rank's experts
   int *errFlag;         // device int32: 1 = a bounded wait gave up, 2 = an expert's buffer overflowed (extra tokens dropped)
 };
 

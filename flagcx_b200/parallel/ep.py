@@ -1,11 +1,13 @@
-"""Expert-parallel mixture-of-experts layer (one expert per rank, top-k routing).
+"""Expert-parallel mixture-of-experts layer (one or several experts per rank, top-k routing).
 
 Fused path (``ExpertParallelContext.forward``), five launches and no host
 round trip:
 
 1. ``moe_dispatch``  one cooperative kernel: per-expert counts, count-matrix
    exchange through the symmetric heap, token push over NVLink into the
-   expert rank's input buffer; the received row count stays on the device.
+   expert's segment of its rank's input buffer; the received row counts
+   (one per local expert) stay on the device.  Steps 2-4 run once per
+   local expert.
 2. up/gate GEMM      tcgen05 GEMM whose row count is read on the device.
 3. ``silu_mul``
 4. down GEMM         tcgen05 GEMM in ROWMAP mode: the epilogue stores every
@@ -52,19 +54,23 @@ def moe_reference(x, topk_idx, topk_w, w_gate_up, w_down, expert: int | None = N
 
 class ExpertParallelContext:
     def __init__(self, comm: int, nranks: int, rank: int, tokens: int, hidden: int, ffn: int, topk: int = 2,
-                 capacity_factor: float = 1.25, dispatch_ctas: int = 64, device=None):
-        """``tokens``: tokens per rank; ``capacity_factor`` x the balanced load bounds the rows an expert accepts."""
+                 capacity_factor: float = 1.25, dispatch_ctas: int = 64, device=None, experts_per_rank: int = 1):
+        """``tokens``: tokens per rank; ``capacity_factor`` x the balanced load bounds the rows an expert accepts;
+        ``experts_per_rank``: expert e lives on rank ``e // experts_per_rank`` (at most 64 experts in all)."""
         self.nat = flagcx_b200.native()
         self.comm, self.n, self.rank = comm, nranks, rank
         self.T, self.H, self.F, self.K = tokens, hidden, ffn, topk
+        self.L = experts_per_rank
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.dispatch_ctas = dispatch_ctas
-        balanced = tokens * topk  # n ranks x T x K choices over n experts
-        cap = min(nranks * tokens * topk, int(balanced * capacity_factor)) if nranks > 1 else balanced
-        self.cap = (cap + 127) // 128 * 128
+        total = nranks * tokens * topk          # routed (token, choice) entries of the whole job
+        balanced = -(-total // (nranks * self.L))  # ... spread evenly over the experts
+        cap_l = min(total, int(balanced * capacity_factor)) if nranks * self.L > 1 else balanced
+        self.cap_l = (cap_l + 127) // 128 * 128  # rows of one local expert's segment
+        self.cap = self.cap_l * self.L
         ht = self.nat.heap_tensor
         i32, i64, bf = torch.int32, torch.int64, torch.bfloat16
-        self.count_mat = [ht(comm, [nranks * nranks], i32).zero_() for _ in range(2)]
+        self.count_mat = [ht(comm, [nranks * nranks * self.L], i32).zero_() for _ in range(2)]
         self.count_flags = [ht(comm, [8], i64).zero_() for _ in range(2)]
         self.recv = [ht(comm, [self.cap, hidden], bf) for _ in range(2)]
         self.info = [ht(comm, [self.cap, 4], i32).zero_() for _ in range(2)]
@@ -73,8 +79,8 @@ class ExpertParallelContext:
         self.comb_done = [ht(comm, [2], i64).zero_() for _ in range(2)]
         dev = self.device
         self.slot = torch.zeros(tokens * topk, dtype=i32, device=dev)
-        self.local_counts = torch.zeros(nranks, dtype=i32, device=dev)
-        self.recv_total = torch.zeros(1, dtype=i32, device=dev)
+        self.local_counts = torch.zeros(nranks * self.L, dtype=i32, device=dev)
+        self.recv_total = torch.zeros(self.L, dtype=i32, device=dev)  # rows received per local expert
         self.err = torch.zeros(1, dtype=i32, device=dev)
         self.gu = torch.empty(self.cap, 2 * ffn, dtype=bf, device=dev)
         self.h = torch.empty(self.cap, ffn, dtype=bf, device=dev)
@@ -87,20 +93,28 @@ class ExpertParallelContext:
             torch.cuda.synchronize()
 
     def forward(self, x, topk_idx, topk_w, w_gate_up, w_down, out=None):
-        """x bf16 [T, H]; topk_idx int32 [T, K] (expert = rank id); topk_w fp32 [T, K];
-        w_gate_up bf16 [2F, H] and w_down bf16 [H, F] of THIS rank's expert.  Returns bf16 [T, H]."""
+        """x bf16 [T, H]; topk_idx int32 [T, K] (global expert ids); topk_w fp32 [T, K]; w_gate_up bf16 [2F, H] and
+        w_down bf16 [H, F] of THIS rank's expert, or lists / stacked tensors of ``experts_per_rank`` of them.
+        Returns bf16 [T, H]."""
         nat, par = self.nat, self.calls & 1
         epoch = (self.calls >> 1) + 1
         self.calls += 1
         if out is None:
             out = torch.empty_like(x)
+        if self.L == 1 and torch.is_tensor(w_gate_up) and w_gate_up.dim() == 2:
+            w_gate_up, w_down = [w_gate_up], [w_down]
+        assert len(w_gate_up) == self.L and len(w_down) == self.L, "one weight pair per local expert"
         nat.moe_dispatch(self.comm, x, topk_idx, self.count_mat[par], self.count_flags[par], self.recv[par], self.info[par],
-                         self.disp_done[par], epoch, self.slot, self.local_counts, self.recv_total, self.err, self.dispatch_ctas)
-        nat.gemm_dyn_m(self.recv[par], w_gate_up, self.gu, self.recv_total, self.err)
-        nat.silu_mul(self.gu, self.h, self.recv_total)
-        grid = nat.gemm_rowmap(self.comm, self.h, w_down, self.recv_total, self.info[par], self.combine[par], self.comb_done[par],
-                               self.K, self.err)
-        self.comb_want[par] += grid * self.n  # every rank launches the same grid
+                         self.disp_done[par], epoch, self.slot, self.local_counts, self.recv_total, self.err, self.dispatch_ctas,
+                         self.L)
+        for l in range(self.L):  # every local expert works on its own segment, sized on the device by its row count
+            seg = slice(l * self.cap_l, (l + 1) * self.cap_l)
+            rows = self.recv_total[l:l + 1]
+            nat.gemm_dyn_m(self.recv[par][seg], w_gate_up[l], self.gu[seg], rows, self.err)
+            nat.silu_mul(self.gu[seg], self.h[seg], rows)
+            grid = nat.gemm_rowmap(self.comm, self.h[seg], w_down[l], rows, self.info[par][seg], self.combine[par], self.comb_done[par],
+                                   self.K, self.err)
+            self.comb_want[par] += grid * self.n  # every rank launches the same grids
         nat.moe_combine(self.comm, self.combine[par], topk_w, out, self.comb_done[par], self.comb_want[par], self.err)
         return out
 

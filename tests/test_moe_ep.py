@@ -82,3 +82,29 @@ def test_fused_layer_on_one_rank(nat, comm1):
         un = ep.unfused_forward(x, idx.clamp(min=0), wts, w1, w2)
         e = (un.float() - ref).abs().max() / ref.abs().max()
         assert e < 3e-2, ("unfused", rep, float(e))
+
+
+def test_fused_layer_with_four_experts_on_one_rank(nat, comm1):
+    """Several experts per rank: the dispatch kernel sorts the rows into one segment per local expert and every
+    expert's GEMMs size themselves from their own device-resident row count."""
+    from flagcx_b200.parallel.ep import ExpertParallelContext, moe_reference
+    lib, comm = comm1
+    T, H, F, K, L = 768, 512, 768, 2, 4
+    ep = ExpertParallelContext(comm.value, 1, 0, T, H, F, K, dispatch_ctas=8, experts_per_rank=L, capacity_factor=1.5)
+    torch.manual_seed(5)
+    w1 = [(torch.randn(2 * F, H, device="cuda") * 0.05).bfloat16() for _ in range(L)]
+    w2 = [(torch.randn(H, F, device="cuda") * 0.05).bfloat16() for _ in range(L)]
+    for rep in range(3):
+        x = torch.randn(T, H, device="cuda").bfloat16()
+        first = torch.randint(0, L, (T,), device="cuda")
+        idx = torch.stack([first, (first + 1 + torch.randint(0, L - 1, (T,), device="cuda")) % L], dim=1).int().contiguous()
+        idx[rep::11, 1] = -1  # a choice that is not dispatched
+        wts = torch.rand(T, K, device="cuda")
+        wts[idx < 0] = 0
+        out = ep.forward(x, idx, wts, w1, w2)
+        torch.cuda.synchronize()
+        ep.check()
+        assert ep.recv_total.tolist() == [int((idx == e).sum().item()) for e in range(L)]
+        ref = moe_reference(x, idx, wts, w1, w2)
+        e = (out.float() - ref).abs().max() / ref.abs().max()
+        assert e < 3e-2, (rep, float(e))
