@@ -173,8 +173,52 @@ __global__ void __launch_bounds__(256) moeCombineKernel(const FcxDevComm dc, con
     if (!ok) *errFlag = 1;
   }
   if (!__syncthreads_and(ok)) return;
-  const size_t vecPerRow = H / 8, total = (size_t)T * vecPerRow;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+  const size_t vecPerRow = H / 8, total = (size_t)T * vecPerRow, stride = (size_t)gridDim.x * blockDim.x;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (K <= 4) {
+    // two output vectors per thread and step, every choice's row loaded before the first is used: up to eight
+    // 16-byte loads in flight per thread (the kernel is bound by load latency, not by bytes)
+    for (; i < total; i += 2 * stride) {
+      const size_t pos[2] = {i, i + stride};
+      uint4 v[2][4];
+      float wk[2][4];
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+        const bool live = pos[u] < total;
+        const size_t t = live ? pos[u] / vecPerRow : 0, c = live ? pos[u] % vecPerRow : 0;
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+          wk[u][k] = (live && k < K) ? w[t * K + k] : 0.f;
+          // a choice that was not dispatched (expert id out of range, capacity overflow) has weight 0 and no row
+          v[u][k] = wk[u][k] != 0.f ? *(const uint4 *)(ret + ((t * K + k) * H) + c * 8) : make_uint4(0, 0, 0, 0);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+          const __nv_bfloat162 *h2 = (const __nv_bfloat162 *)&v[u][k];
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            float2 f = __bfloat1622float2(h2[j]);
+            acc[2 * j] += wk[u][k] * f.x;
+            acc[2 * j + 1] += wk[u][k] * f.y;
+          }
+        }
+        uint4 o;
+        __nv_bfloat162 *o2 = (__nv_bfloat162 *)&o;
+#pragma unroll
+        for (int j = 0; j < 4; j++) o2[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+        if (pos[u] < total) {
+          const size_t t = pos[u] / vecPerRow, c = pos[u] % vecPerRow;
+          *(uint4 *)(out + t * H + c * 8) = o;
+        }
+      }
+    }
+    return;
+  }
+  for (; i < total; i += stride) {
     const size_t t = i / vecPerRow, c = i % vecPerRow;
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int k = 0; k < K; k++) {
