@@ -821,6 +821,25 @@ flagcxResult_t flagcxTunerPriorPlan(flagcxCommOp_t op, size_t bytes, flagcxDataT
   return flagcxSuccess;
 }
 
+// The same with the caller's buffers taken as peer-visible (zero-copy kinds allowed) and a CTA budget (0 = none).
+flagcxResult_t flagcxTunerPriorPlanEx(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, int nranks, int multicast, int zeroCopy,
+                                      int ctaBudget, char *kindOut, size_t kindOutBytes, int *nctas, double *estimate) {
+  if (nranks < 1 || nranks > FCX_MAX_RANKS) return flagcxInvalidArgument;
+  TunerCaps caps;
+  caps.nranks = nranks;
+  caps.multicast = multicast != 0;
+  caps.stageBytes = (size_t)envInt("STAGE_BYTES", 512ll << 20);
+  caps.maxCtas = (int)std::min<int64_t>(envInt("MAX_CTAS", 128), FCX_MAX_CTAS);
+  caps.pipeBytes = (size_t)envInt("PIPE_BYTES", 16ll << 20);
+  Tuner t(nullptr, caps);
+  if (ctaBudget > 0) t.setCtaBudget(ctaBudget);
+  Plan p = t.peek(op, bytes, dt, flagcxSum, false, zeroCopy != 0);
+  if (kindOut && kindOutBytes) snprintf(kindOut, kindOutBytes, "%s", kindName(p.kind));
+  if (nctas) *nctas = p.nctas;
+  if (estimate) *estimate = t.estimate(p, op, bytes, dt);
+  return flagcxSuccess;
+}
+
 flagcxResult_t flagcxCommWaitTest(flagcxComm_t comm, flagcxStream_t stream) {
   if (!validComm(comm) || comm->hostOnly || !comm->heap.bytes) return flagcxInvalidArgument;
   return cudaToResult(fcxLaunchWaitTest(&comm->dev, ~0ull, streamOf(stream)), "wait test launch");

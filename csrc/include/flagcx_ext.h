@@ -111,6 +111,10 @@ flagcxResult_t flagcxTunerQueryEx(flagcxComm_t comm, flagcxCommOp_t op, size_t b
 /* The plan the cost-model prior picks for a machine of `nranks` GPUs; needs neither a communicator nor a GPU. */
 flagcxResult_t flagcxTunerPriorPlan(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, int nranks, int multicast, char *kindOut,
                                     size_t kindOutBytes, int *nctas, double *estimateUs);
+// The same with the caller's buffers taken as peer-visible (zeroCopy != 0: the zero-copy kinds may be chosen) and
+// under a CTA budget (0 = none).
+flagcxResult_t flagcxTunerPriorPlanEx(flagcxCommOp_t op, size_t bytes, flagcxDataType_t dt, int nranks, int multicast, int zeroCopy,
+                                      int ctaBudget, char *kindOut, size_t kindOutBytes, int *nctas, double *estimate);
 
 /* Failure handling.  Device waits are bounded by this many milliseconds
  * (default FLAGCX_KERNEL_TIMEOUT_MS or 30000). */

@@ -225,6 +225,8 @@ _SIGNATURES = {
     "flagcxTunerPin": (_R, [flagcxComm_t, ctypes.c_char_p, ctypes.c_int]),
     "flagcxTunerPriorPlan": (_R, [ctypes.c_int, _sz, flagcxDataType_t, ctypes.c_int, ctypes.c_int, ctypes.c_char_p, _sz,
                                   ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_double)]),
+    "flagcxTunerPriorPlanEx": (_R, [ctypes.c_int, _sz, flagcxDataType_t, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                    ctypes.c_char_p, _sz, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_double)]),
     "flagcxTunerQuery": (_R, [flagcxComm_t, ctypes.c_int, _sz, flagcxDataType_t, flagcxRedOp_t, ctypes.c_char_p, _sz,
                               ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_double)]),
     "flagcxEmuCreate": (_R, [ctypes.POINTER(_vp), ctypes.c_int, _sz]),
@@ -465,6 +467,15 @@ class FLAGCXLibrary:
         buf = ctypes.create_string_buffer(64)
         nctas, us = ctypes.c_int(), ctypes.c_double()
         self.call("flagcxTunerPriorPlan", op, nbytes, dtype, nranks, int(multicast), buf, 64, ctypes.byref(nctas), ctypes.byref(us))
+        return buf.value.decode(), nctas.value, us.value
+
+    def tuner_prior_plan_ex(self, op: int, nbytes: int, dtype: int, nranks: int, multicast: bool = True, zero_copy: bool = True,
+                            cta_budget: int = 0):
+        """Like ``tuner_prior_plan`` for peer-visible buffers (zero-copy kinds allowed) and under a CTA budget."""
+        buf = ctypes.create_string_buffer(64)
+        nctas, us = ctypes.c_int(), ctypes.c_double()
+        self.call("flagcxTunerPriorPlanEx", op, nbytes, dtype, nranks, int(multicast), int(zero_copy), cta_budget, buf, 64,
+                  ctypes.byref(nctas), ctypes.byref(us))
         return buf.value.decode(), nctas.value, us.value
 
     def tuner_pin(self, comm, kind: Optional[str], nctas: int = 16):

@@ -39,3 +39,16 @@ def test_prior_rejects_bad_world():
     lib = FLAGCXLibrary()
     with pytest.raises(Exception):
         lib.tuner_prior_plan(6, 1024, FP32, 9, True)
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+def test_prior_sends_peer_visible_buffers_to_zero_copy_kinds(n):
+    """What the multi-GPU tests rely on: for buffers every rank can see, the cost model picks the zero-copy kinds from a
+    megabyte up, with and without the switch, and respects a CTA budget."""
+    lib = FLAGCXLibrary()
+    for mc in (True, False):
+        for op, want in ((OPS["allreduce"], "ar_zc"), (OPS["reducescatter"], "rs_zc"), (OPS["allgather"], "move_zc")):
+            kind, ctas, us = lib.tuner_prior_plan_ex(op, 300007 * 4, FP32, n, mc, True, 8)
+            assert kind == want and 1 <= ctas <= 8 and us > 0, (n, mc, op, kind, ctas)
+        kind, ctas, _ = lib.tuner_prior_plan_ex(OPS["allreduce"], 64, FP32, n, mc, True, 8)
+        assert kind in LL_KINDS, kind
