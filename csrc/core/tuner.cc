@@ -11,6 +11,13 @@
 
 namespace fcx {
 
+// The copy-engine form of the movers has passed its multi-GPU test on two GPUs only: from three ranks on the tuner offers
+// it (and accepts it from a measured table) when FLAGCX_COPY_ENGINE=1; a pinned plan still reaches it.
+static bool ceOffered(int n) {
+  static const bool on = envInt("COPY_ENGINE", 0) != 0;
+  return n == 2 || (n > 2 && on);
+}
+
 static const char *kKindNames[FCX_K_NUM] = {"barrier", "ar_ll", "ar_oneshot", "ar_twoshot", "ar_nvls", "rs", "rs_nvls", "ag",
                                             "ag_nvls", "bcast", "reduce", "gather", "scatter", "a2a", "a2av", "move_ll", "rs_ll", "reduce_ll",
                                             "ar_zc", "rs_zc", "reduce_zc", "move_zc", "move_ce"};
@@ -186,7 +193,7 @@ std::vector<Plan> Tuner::candidates(flagcxCommOp_t op, size_t bytes, flagcxDataT
       addCtas(out, FCX_K_AG, {2, 8, 16, 32, 64, 128}, units, mx);
       if (caps_.multicast && n > 1 && bytes >= 4096) addCtas(out, FCX_K_AG_NVLS, {8, 16, 32, 64, 128}, units, mx);
       if (zc && n > 1) addCtas(out, FCX_K_MOVE_ZC, {1, 2, 4, 8, 16, 24, 32, 48, 64, 96}, units, mx);
-      if (zc && n > 1 && bytes >= (256u << 10)) out.push_back({FCX_K_MOVE_CE, 1});
+      if (zc && ceOffered(n) && bytes >= (256u << 10)) out.push_back({FCX_K_MOVE_CE, 1});
       break;
     case flagcxCommOpReduce:
       if (!cast && bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_REDUCE_LL, {1, 2, 4}, units, mx);
@@ -197,7 +204,7 @@ std::vector<Plan> Tuner::candidates(flagcxCommOp_t op, size_t bytes, flagcxDataT
       if (bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_MOVE_LL, {1, 2, 4}, units, mx);
       addCtas(out, FCX_K_BCAST, {1, 4, 16, 32, 64, 128}, units, mx);
       if (zc && n > 1) addCtas(out, FCX_K_MOVE_ZC, {1, 2, 4, 8, 16, 24, 32, 48, 64, 96}, units, mx);
-      if (zc && n > 1 && bytes >= (256u << 10)) out.push_back({FCX_K_MOVE_CE, 1});
+      if (zc && ceOffered(n) && bytes >= (256u << 10)) out.push_back({FCX_K_MOVE_CE, 1});
       break;
     case flagcxCommOpGather:
       if (bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_MOVE_LL, {1, 2, 4}, units, mx);
@@ -208,13 +215,13 @@ std::vector<Plan> Tuner::candidates(flagcxCommOp_t op, size_t bytes, flagcxDataT
       if (bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_MOVE_LL, {1, 2, 4}, units, mx);
       addCtas(out, FCX_K_SCATTER, {1, 4, 16, 64, 128}, units, mx);
       if (zc && n > 1) addCtas(out, FCX_K_MOVE_ZC, {1, 2, 4, 8, 16, 24, 32, 48, 64, 96}, units, mx);
-      if (zc && n > 1 && bytes >= (256u << 10)) out.push_back({FCX_K_MOVE_CE, 1});
+      if (zc && ceOffered(n) && bytes >= (256u << 10)) out.push_back({FCX_K_MOVE_CE, 1});
       break;
     case flagcxCommOpAlltoAll:
       if (bytes <= FCX_LL_MAX_PAYLOAD) addCtas(out, FCX_K_MOVE_LL, {1, 2, 4}, units, mx);
       addCtas(out, FCX_K_A2A, {2, 8, 16, 32, 64, 128}, units, mx);
       if (zc && n > 1) addCtas(out, FCX_K_MOVE_ZC, {1, 2, 4, 8, 16, 24, 32, 48, 64, 96}, units, mx);
-      if (zc && n > 1 && bytes >= (256u << 10)) out.push_back({FCX_K_MOVE_CE, 1});
+      if (zc && ceOffered(n) && bytes >= (256u << 10)) out.push_back({FCX_K_MOVE_CE, 1});
       break;
     case flagcxCommOpAlltoAllv:
       addCtas(out, FCX_K_A2AV, {2, 8, 16, 32, 64, 128}, units, mx);
@@ -409,6 +416,7 @@ flagcxResult_t Tuner::load(const std::string &path) {
                &nr, kind, &nctas, &us) == 6) {
       int k = kindFromName(kind);
       if (nr != caps_.nranks || k < 0) continue;
+      if (k == FCX_K_MOVE_CE && !ceOffered(caps_.nranks)) continue;
       if ((k == FCX_K_AR_NVLS || k == FCX_K_RS_NVLS || k == FCX_K_AG_NVLS) && !caps_.multicast) continue;
       Key key{op, l2, isZcKind(k) ? 1 : 0, -1};
       unsigned int pipe = 0;
