@@ -482,18 +482,23 @@ extern "C" cudaError_t fcxGemmBf16(const void *a, const void *b, void *c, int M,
 
 // Pieces to cut K into.  requested > 0: that many (at most one per K block, and no piece may be empty).  Otherwise: few
 // tiles and a long K (the weight-gradient GEMMs: K = tokens) are cut so that the pieces fill whole waves; a split into
-// s pieces takes ceil(units * s / slots) waves of 1/s the length, and every extra piece costs some atomic traffic,
-// counted as 4 % of a tile.
+// s pieces takes ceil(units * s / slots) waves of 1/s the length, and every extra piece costs some reduction traffic,
+// counted as 3 % of a tile (1 % when K is very long).
 extern "C" int fcxGemmPickSplitK(int requested, int units, int slots, int nK, int N) {
   int splitK = requested;
   if (splitK <= 0) {
     splitK = 1;
-    if (units < slots && nK >= 32) {
+    const bool few = units < slots && nK >= 32;
+    // more tiles than slots but a poor last wave and a very long K (the LM head's input gradient: 128 tiles on 74
+    // pairs, K = 50304): zeroing C is noise against such a K, and the pieces stay long
+    const bool longK = units >= slots && nK >= 256;
+    if (few || longK) {
+      const double base = (double)((units + slots - 1) / slots), piece = few ? 0.03 : 0.01;
       double best = 1.0;
       for (int sk = 2; sk <= 8 && nK / sk >= 8; sk++) {
         const double waves = (double)((units * sk + slots - 1) / slots);
-        const double cost = waves / sk + 0.04 * (sk - 1);
-        if (cost < best - 0.05) { best = cost; splitK = sk; }
+        const double cost = waves / (sk * base) + piece * (sk - 1);
+        if (cost < best - (splitK == 1 ? 0.05 : 0.0)) { best = cost; splitK = sk; }  // a first cut must pay clearly
       }
     }
   }
