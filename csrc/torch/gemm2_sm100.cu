@@ -105,9 +105,19 @@ __device__ __forceinline__ void tileCoord2(int group, int nM, int nN, int t, int
   }
 }
 
+// tanh-form GELU, the same arithmetic as the stand-alone bias+GELU kernel of the training ops
+__device__ __forceinline__ float geluTanh(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(k0 * (x + k1 * x * x * x)));
+  return 0.5f * x * (1.f + t);
+}
+
+// GELU = true: two outputs per tile: C = A B^T (kept for the backward pass) and C2 = gelu(A B^T + bias).
+template <bool GELU>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
     fcxGemmPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
-                      const FcxGemmParams p) {
+                      const __grid_constant__ CUtensorMap tmC2, const FcxGemmParams p) {
   extern __shared__ uint8_t smemRaw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int *err = p.errFlag;
@@ -239,6 +249,52 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
           if (colBase + c0 >= p.N || row0 >= p.M) break;
           uint32_t r[32];
           tmemLd32(tmemBase + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + half * 128 + c0), r);
+          if (GELU) {
+            // both staging blocks of this warp are used per step: the product goes into the first, the activation
+            // into the second, and one thread hands both to the TMA unit
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            __syncwarp();
+            tmemLdWait();
+            uint4 *stgPre = (uint4 *)stgBase, *stgAct = (uint4 *)(stgBase + STG_BYTES);
+#pragma unroll
+            for (int v = 0; v < 4; v++) {
+              uint4 o;
+              o.x = pack2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+              o.y = pack2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+              o.z = pack2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+              o.w = pack2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+              stgPre[lane * 4 + (v ^ ((lane >> 1) & 3))] = o;
+            }
+            const float4 *bv = (const float4 *)(biasW + c0);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+              const float4 f = addBias ? bv[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+              r[4 * j + 0] = __float_as_uint(geluTanh(__uint_as_float(r[4 * j + 0]) + f.x));
+              r[4 * j + 1] = __float_as_uint(geluTanh(__uint_as_float(r[4 * j + 1]) + f.y));
+              r[4 * j + 2] = __float_as_uint(geluTanh(__uint_as_float(r[4 * j + 2]) + f.z));
+              r[4 * j + 3] = __float_as_uint(geluTanh(__uint_as_float(r[4 * j + 3]) + f.w));
+            }
+#pragma unroll
+            for (int v = 0; v < 4; v++) {
+              uint4 o;
+              o.x = pack2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+              o.y = pack2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+              o.z = pack2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+              o.w = pack2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+              stgAct[lane * 4 + (v ^ ((lane >> 1) & 3))] = o;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+                           ::"l"(&tmC), "r"(colBase + c0), "r"(row0), "r"(smemAddr(stgPre)) : "memory");
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+                           ::"l"(&tmC2), "r"(colBase + c0), "r"(row0), "r"(smemAddr(stgAct)) : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+            chunkNo++;
+            continue;
+          }
           // the staging block about to be refilled must have been read out by the TMA unit
           if (lane == 0) {
             if (STG_DEPTH == 2) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
@@ -332,13 +388,20 @@ extern "C" int fcxGemmPairSuits(int M, int N, int K) {
 }
 
 extern "C" cudaError_t fcxGemmPairBf16(const void *a, const void *b, void *c, int M, int N, int K, int lda, int ldb, int ldc, int aMN, int bMN,
-                                       const void *bias, int splitK, int accumulate, int group, int *errFlag, cudaStream_t s, char *detail,
-                                       size_t detailLen) {
+                                       const void *bias, int splitK, int accumulate, void *geluOut, int group, int *errFlag, cudaStream_t s,
+                                       char *detail, size_t detailLen) {
   CUtensorMap ma, mb;
   const bool okA = aMN ? makeTileMap(&ma, a, K, M, lda, BK, 2) : makeTileMap(&ma, a, M, K, lda, BM, 2);
   const bool okB = bMN ? makeTileMap(&mb, b, K, N, ldb, BK, 2) : makeTileMap(&mb, b, N, K, ldb, BNH, 2);
-  CUtensorMap mc;
-  const bool okC = makeStoreMap(&mc, c, M, N, ldc);
+  CUtensorMap mc, mc2;
+  bool okC = makeStoreMap(&mc, c, M, N, ldc);
+  if (geluOut) {
+    if (accumulate || ((uintptr_t)geluOut & 15)) return cudaErrorInvalidValue;
+    okC = okC && makeStoreMap(&mc2, geluOut, M, N, ldc);
+    splitK = 1;  // the activation needs the whole sum
+  } else {
+    mc2 = mc;
+  }
   if (!okA || !okB || !okC) {
     if (detail)
       snprintf(detail, detailLen, "tensor map of %s refused (pair kernel, M %d N %d K %d)", !okA ? "operand A" : !okB ? "operand B" : "C", M, N, K);
@@ -346,7 +409,8 @@ extern "C" cudaError_t fcxGemmPairBf16(const void *a, const void *b, void *c, in
   }
   static bool attr = false;
   if (!attr) {
-    cudaError_t e = cudaFuncSetAttribute(fcxGemmPairKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(fcxGemmPairKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(fcxGemmPairKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return e;
     attr = true;
   }
@@ -361,7 +425,8 @@ extern "C" cudaError_t fcxGemmPairBf16(const void *a, const void *b, void *c, in
     if (e != cudaSuccess) return e;
   }
   const int grid = 2 * std::min(units * p.splitK, pairs);
-  fcxGemmPairKernel<<<grid, THREADS, SMEM_BYTES, s>>>(ma, mb, mc, p);
+  if (geluOut) fcxGemmPairKernel<true><<<grid, THREADS, SMEM_BYTES, s>>>(ma, mb, mc, mc2, p);
+  else fcxGemmPairKernel<false><<<grid, THREADS, SMEM_BYTES, s>>>(ma, mb, mc, mc2, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess && detail)
     snprintf(detail, detailLen, "pair kernel launch: %s (M %d N %d K %d splitK %d grid %d)", cudaGetErrorString(e), M, N, K, p.splitK, grid);

@@ -66,6 +66,29 @@ static at::Tensor gemmEx(const at::Tensor &a, const at::Tensor &b, bool aMN, boo
   return c;
 }
 
+// (pre, act) = (a w^T, gelu_tanh(a w^T + bias)) in one kernel: the CTA-pair GEMM writes both from its epilogue.  pre is what
+// the backward pass of bias + GELU needs; a [M,K], w [N,K], bias [N] or None.
+static std::tuple<at::Tensor, at::Tensor> gemmBiasGelu(const at::Tensor &a, const at::Tensor &w, const c10::optional<at::Tensor> &bias,
+                                                       at::Tensor &err) {
+  checkMat(a, "a");
+  checkMat(w, "w");
+  const int64_t M = a.size(0), K = a.size(1), N = w.size(0);
+  TORCH_CHECK(w.size(1) == K, "inner dimensions differ: ", K, " vs ", w.size(1));
+  const void *biasPtr = nullptr;
+  if (bias.has_value() && bias->defined()) {
+    TORCH_CHECK(bias->is_cuda() && bias->scalar_type() == at::kBFloat16 && bias->is_contiguous() && bias->numel() == N, "bias must be bf16 [N]");
+    biasPtr = bias->data_ptr();
+  }
+  c10::cuda::CUDAGuard g(a.device());
+  auto pre = at::empty({M, N}, a.options()), act = at::empty({M, N}, a.options());
+  FcxGemmOpts o{};
+  o.bias = biasPtr; o.splitK = 1; o.pair = 1; o.geluOut = act.data_ptr();
+  auto e = fcxGemmBf16Opts(a.data_ptr(), w.data_ptr(), pre.data_ptr(), (int)M, (int)N, (int)K, (int)a.stride(0), (int)w.stride(0),
+                           (int)pre.stride(0), &o, err.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(e == cudaSuccess, "tcgen05 GEMM + GELU failed: ", cudaGetErrorString(e), ": ", fcxGemmLastDetail());
+  return {pre, act};
+}
+
 // y[M,N] = all_gather(x_local)[M,K] @ w[N,K]^T.  gathered: heap tensor [M,K]; flags: heap int64 tensor [M/128];
 // epoch: 1-based use count of this (gathered, flags) pair.
 static at::Tensor agGemm(uint64_t comm, const at::Tensor &xLocal, at::Tensor &gathered, at::Tensor &flags, const at::Tensor &w,
@@ -157,6 +180,8 @@ void bindGemm(py::module &m) {
         "out: write the result there; accumulate: add it to what out holds (a gradient that collects contributions). "
         "bf16 GEMM on tcgen05 with either operand read K-major or MN-major, optional bias row; pair: -1 kernel chosen by shape, "
         "0 one-CTA kernel (128 x 256 tiles), 1 CTA-pair kernel (cta_group::2, 256 x 256 tiles)");
+  m.def("gemm_bias_gelu", &gemmBiasGelu, py::arg("a"), py::arg("w"), py::arg("bias"), py::arg("err"),
+        "(a w^T, gelu_tanh(a w^T + bias)) from one CTA-pair GEMM launch");
   m.def("ag_gemm", &agGemm);
   m.def("gemm_rs", &gemmRs);
 }

@@ -522,9 +522,9 @@ extern "C" cudaError_t fcxGemmBf16Opts(const void *a, const void *b, void *c, in
   if ((aMN && M % 8) || (bMN && N % 8) || (bias && ((uintptr_t)bias & 1)) || (accumulate && N % 2)) return cudaErrorInvalidValue;
   gGemmDetail[0] = 0;
   cudaGetLastError();  // an error left behind by an earlier, unrelated call of this thread is not this launch's
-  if (o->pair >= 0 ? o->pair > 0 : fcxGemmPairSuits(M, N, K) != 0)  // CTA pairs on 256 x 256 tiles (gemm2_sm100.cu)
-    return fcxGemmPairBf16(a, b, c, M, N, K, lda, ldb, ldc, aMN, bMN, bias, splitK, accumulate, tileGroup((N + 255) / 256) / 2, errFlag, s,
-                           gGemmDetail, sizeof gGemmDetail);
+  if (o->geluOut || (o->pair >= 0 ? o->pair > 0 : fcxGemmPairSuits(M, N, K) != 0))  // CTA pairs on 256 x 256 tiles (gemm2_sm100.cu)
+    return fcxGemmPairBf16(a, b, c, M, N, K, lda, ldb, ldc, aMN, bMN, bias, splitK, accumulate, o->geluOut, tileGroup((N + 255) / 256) / 2,
+                           errFlag, s, gGemmDetail, sizeof gGemmDetail);
   CUtensorMap ma, mb;
   const int bn = pickBn(M, N, smCount());
   // K-major operand: rows = M (or N), box of 128 (bn) rows x 64 K; MN-major operand: rows = K, box of 64 lines x 64 columns

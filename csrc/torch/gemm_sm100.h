@@ -60,6 +60,7 @@ typedef struct FcxGemmOpts {
   int aMN, bMN;
   const void *bias;
   int splitK, accumulate, pair;
+  void *geluOut;  // when set: C receives A B^T and geluOut (same shape and row stride) gelu_tanh(A B^T + bias); CTA-pair kernel only
 } FcxGemmOpts;
 cudaError_t fcxGemmBf16Opts(const void *a, const void *b, void *c, int M, int N, int K, int lda, int ldb, int ldc, const FcxGemmOpts *o,
                             int *errFlag, cudaStream_t s);
@@ -67,8 +68,8 @@ int fcxGemmPickSplitK(int requested, int units, int slots, int nK, int N);
 int fcxGemmPairMode();
 int fcxGemmPairSuits(int M, int N, int K);
 cudaError_t fcxGemmPairBf16(const void *a, const void *b, void *c, int M, int N, int K, int lda, int ldb, int ldc, int aMN, int bMN,
-                            const void *bias, int splitK, int accumulate, int group, int *errFlag, cudaStream_t s, char *detail,
-                            size_t detailLen);
+                            const void *bias, int splitK, int accumulate, void *geluOut, int group, int *errFlag, cudaStream_t s,
+                            char *detail, size_t detailLen);
 const char *fcxGemmLastDetail();  // what the calling thread's last failed fcxGemmBf16Ex call tripped over
 // c[Mmax,N] = a[*mPtr rows, K] @ b^T with the row count read on the device.
 cudaError_t fcxGemmBf16DynM(const void *a, const void *b, void *c, int Mmax, const int *mPtr, int N, int K, int lda, int ldb, int ldc,

@@ -28,7 +28,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from flagcx_b200.ops import add_layernorm, bias_gelu, cross_entropy, linear
+from flagcx_b200.ops import add_layernorm, bias_gelu, cross_entropy, linear, linear_bias_gelu
 
 
 def _linear_fn():
@@ -91,7 +91,10 @@ class Block(nn.Module):
         att = att.transpose(1, 2).reshape(B, T, C)
         a = lin(att, self.proj_w, self.proj_b)
         x, h = add_layernorm(x, a, self.ln2_w, self.ln2_b)
-        f = bias_gelu(lin(h, self.fc_w), self.fc_b)
+        if lin is linear and os.environ.get("FLAGCX_MODEL_FUSED_GELU", "1") != "0":
+            f = linear_bias_gelu(h, self.fc_w, self.fc_b)  # the activation comes out of the GEMM's epilogue
+        else:
+            f = bias_gelu(lin(h, self.fc_w), self.fc_b)
         return x, lin(f, self.out_w, self.out_b)
 
 

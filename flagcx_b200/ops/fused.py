@@ -192,6 +192,55 @@ class _Linear(torch.autograd.Function):
         return dx, dw, db
 
 
+class _LinearBiasGelu(torch.autograd.Function):
+    """gelu_tanh(x w^T + bias) with the activation computed in the GEMM's epilogue: one kernel writes the product
+    (kept for the backward pass) and the activation.  Backward: bias+GELU gradient kernel, then the input and
+    weight gradients on the tcgen05 GEMMs."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        pre, act = _n().gemm_bias_gelu(x2, w, bias, _err_flag(x2.device))
+        ctx.save_for_backward(x2, w, pre, bias)
+        ctx.in_shape = x.shape
+        ctx.params = (w, bias)
+        return act.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, pre, bias = ctx.saved_tensors
+        pw, pb = ctx.params
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        db = None
+        gb = _direct(pb)
+        if gb is not None:
+            dpre, _ = _n().bias_gelu_bwd(dy2, pre, bias, gb)
+            _done(pb)
+        else:
+            dpre, db = _n().bias_gelu_bwd(dy2, pre, bias)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dpre, w, False, True).view(ctx.in_shape)
+        if ctx.needs_input_grad[1]:
+            gw = _direct(pw)
+            if gw is not None and gw.shape[1] % 2 == 0:
+                _n().gemm(dpre, x2, True, True, None, 0, _err_flag(dpre.device), -1, gw, True)
+                _done(pw)
+            else:
+                dw = gemm(dpre, x2, True, True)
+        return dx, dw, db
+
+
+def linear_bias_gelu(x, w, bias):
+    """``gelu_tanh(linear(x, w, bias))`` for bf16 CUDA tensors with the activation fused into the GEMM's epilogue
+    (forward) and the usual fused kernels in the backward pass."""
+    return _LinearBiasGelu.apply(x, w, bias)
+
+
 def linear(x, w, bias=None):
     """``torch.nn.functional.linear`` for bf16 CUDA tensors on the library's tcgen05 GEMM (forward and backward).
     Shapes the kernel cannot take (inner sizes that are not multiples of 8) raise; there is no silent fallback."""

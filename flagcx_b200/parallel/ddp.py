@@ -287,6 +287,8 @@ class DataParallelTrainer:
         all when the optimizer is not overlapped)."""
         L = len(getattr(self.model, "blocks", []))
         own = L * (2 + 4 + 1 + 2) + (1 + 2) + 1
+        if os.environ.get("FLAGCX_MODEL_GEMM", "own") != "library" and os.environ.get("FLAGCX_MODEL_FUSED_GELU", "1") != "0":
+            own -= L  # the GELU of the forward pass runs in the epilogue of the up-projection GEMM
         if os.environ.get("FLAGCX_MODEL_GEMM", "own") != "library":
             # tcgen05 GEMMs: four projections per layer and the LM head, each forward + input gradient + weight
             # gradient; the three biased projections' bias gradients take one column-sum kernel each

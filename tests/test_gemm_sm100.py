@@ -257,3 +257,31 @@ def test_direct_gradients_match_autograd(nat):
     for d, r in zip(direct, ref):
         want = 2 * r.grad.float()
         assert (d.grad.float() - want).abs().max() <= 3e-2 * want.abs().max() + 1e-3
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 1024, 256), (8192, 4096, 1024), (300, 200, 136)])
+def test_gemm_with_gelu_epilogue(nat, M, N, K):
+    """One launch writes a w^T and gelu_tanh(a w^T + bias); the autograd op on it matches PyTorch."""
+    from flagcx_b200.ops import gemm_error, linear_bias_gelu
+    torch.manual_seed(11)
+    a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+    b = torch.randn(N, device="cuda").bfloat16()
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    pre, act = nat.gemm_bias_gelu(a, w, b, err)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    ref = _ref(a, w)
+    _close(pre, ref, K)
+    want = torch.nn.functional.gelu(ref + b.float(), approximate="tanh")
+    assert (act.float() - want).abs().max() < 3e-2 * (want.abs().max() + 1.0)
+    if N % 8 == 0 and M % 8 == 0:
+        x = a.clone().requires_grad_(True)
+        wp, bp = w.clone().requires_grad_(True), b.clone().requires_grad_(True)
+        g = (torch.randn(M, N, device="cuda") * 0.1).bfloat16()
+        linear_bias_gelu(x, wp, bp).backward(g)
+        xr, wr, br = (t.detach().float().requires_grad_(True) for t in (a, w, b))
+        torch.nn.functional.gelu(torch.nn.functional.linear(xr, wr, br), approximate="tanh").backward(g.float())
+        assert gemm_error() == 0
+        for got, refg, k in ((x.grad, xr.grad, N), (wp.grad, wr.grad, M), (bp.grad, br.grad, M)):
+            _close(got, refg, k)
