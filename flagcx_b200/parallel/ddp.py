@@ -252,6 +252,30 @@ class DataParallelTrainer:
         self.step_no += 1
         return loss
 
+    # ---- checkpoint / resume (the reference, a communication library, holds no training state and has no counterpart)
+    def state_dict(self) -> dict:
+        """Everything the next step depends on, as CPU tensors: fp32 master weights, both AdamW moments, the step
+        count, and the layout of the flat buffers (name, offset, count per parameter) to check a resume against."""
+        torch.cuda.synchronize(self.device)
+        return {"master": self.master.detach().cpu(), "m": self.m.detach().cpu(), "v": self.v.detach().cpu(),
+                "step": int(self.step_no), "specs": [tuple(s) for s in self.specs],
+                "hyper": {"lr": self.lr, "betas": tuple(self.betas), "eps": self.eps, "weight_decay": self.wd}}
+
+    def load_state_dict(self, state: dict) -> None:
+        """Resume from ``state_dict()`` of a trainer over the same model (same parameter layout).  Every rank loads the
+        same state; the bf16 working weights are re-derived from the fp32 master copy."""
+        if [tuple(s) for s in state["specs"]] != [tuple(s) for s in self.specs]:
+            raise ValueError("the checkpoint was written for a different parameter layout")
+        torch.cuda.synchronize(self.device)
+        self.master.copy_(state["master"])
+        self.m.copy_(state["m"])
+        self.v.copy_(state["v"])
+        self.flat_params.copy_(self.master)  # fp32 -> bf16
+        self.flat_grads.zero_()
+        self.step_no = int(state["step"])
+        self.step_dev.fill_(self.step_no)
+        torch.cuda.synchronize(self.device)
+
     def step_pipelined(self, tokens: torch.Tensor, targets: torch.Tensor):
         """``step`` for a training loop that reads every loss on the host without stalling the GPU: the step is
         queued, its loss is copied into pinned host memory behind it, and the call returns the loss of the PREVIOUS

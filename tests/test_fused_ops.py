@@ -152,6 +152,31 @@ def test_pipelined_step_hands_out_every_loss_one_step_late(nat):
         assert abs(a - b) < 5e-2, seqs
 
 
+def test_trainer_checkpoint_resume(nat):
+    """A trainer resumed from state_dict() continues like the one that wrote it."""
+    from flagcx_b200.models.gpt2 import GPT2, GPT2Config
+    from flagcx_b200.parallel.ddp import DataParallelTrainer
+    cfg = GPT2Config.tiny()
+    tok = torch.randint(0, cfg.vocab, (4, cfg.seq_len), device="cuda", generator=torch.Generator("cuda").manual_seed(1))
+    tgt = torch.randint(0, cfg.vocab, (4, cfg.seq_len), device="cuda", generator=torch.Generator("cuda").manual_seed(2))
+    torch.manual_seed(5)
+    a = DataParallelTrainer(GPT2(cfg), use_graph=False, lr=1e-3)
+    for _ in range(3):
+        a.step(tok, tgt)
+    state = a.state_dict()
+    assert state["step"] == 3 and state["master"].device.type == "cpu"
+    cont = [float(a.step(tok, tgt).item()) for _ in range(3)]
+    torch.manual_seed(99)  # different initial weights: everything must come from the checkpoint
+    b = DataParallelTrainer(GPT2(cfg), use_graph=False, lr=1e-3)
+    b.load_state_dict(state)
+    resumed = [float(b.step(tok, tgt).item()) for _ in range(3)]
+    for x, y in zip(cont, resumed):
+        assert abs(x - y) < 2e-3, (cont, resumed)
+    bad = dict(state, specs=state["specs"][:-1])
+    with pytest.raises(ValueError):
+        b.load_state_dict(bad)
+
+
 def test_gpt2_matches_plain_torch_forward(nat):
     """Loss of the fused model equals the loss of the same weights run through plain PyTorch ops."""
     from flagcx_b200.models.gpt2 import GPT2, GPT2Config
