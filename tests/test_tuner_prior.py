@@ -52,3 +52,20 @@ def test_prior_sends_peer_visible_buffers_to_zero_copy_kinds(n):
             assert kind == want and 1 <= ctas <= 8 and us > 0, (n, mc, op, kind, ctas)
         kind, ctas, _ = lib.tuner_prior_plan_ex(OPS["allreduce"], 64, FP32, n, mc, True, 8)
         assert kind in LL_KINDS, kind
+
+
+def test_copy_engine_kind_is_offered_on_two_ranks_only():
+    """The copy-engine movers passed their multi-GPU test on two GPUs only: beyond that the prior must not pick them
+    (FLAGCX_COPY_ENGINE=1 lifts the restriction; it is read once per process and is not set here)."""
+    import os
+    assert os.environ.get("FLAGCX_COPY_ENGINE") in (None, "0")
+    lib = FLAGCXLibrary()
+    seen = {n: set() for n in (2, 3, 4, 8)}
+    for n in seen:
+        for op in (OPS["bcast"], OPS["scatter"], OPS["allgather"], OPS["a2a"]):
+            for lg in range(10, 33):
+                for budget in (0, 8, 16):
+                    seen[n].add(lib.tuner_prior_plan_ex(op, 1 << lg, FP32, n, True, True, budget)[0])
+    assert "move_ce" in seen[2]
+    for n in (3, 4, 8):
+        assert "move_ce" not in seen[n], n
