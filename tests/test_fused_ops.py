@@ -16,7 +16,7 @@ def _bf(*shape, scale=1.0):
     return (torch.randn(*shape, device="cuda") * scale).bfloat16()
 
 
-@pytest.mark.parametrize("M,C", [(64, 256), (1000, 1024), (4096, 1024), (33, 2048)])
+@pytest.mark.parametrize("M,C", [(64, 256), (1000, 1024), (4096, 1024), (33, 2048), (300, 768), (40, 1536)])
 @pytest.mark.parametrize("with_delta", [False, True])
 def test_add_layernorm(nat, M, C, with_delta):
     from flagcx_b200.ops import add_layernorm
